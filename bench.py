@@ -1,0 +1,425 @@
+"""Benchmark of the quantized-weight linear path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens M] [--wtype e5m2|fp4] [--impl reference]
+
+Workload (N=1): the linears of one decode token of a Qwen3-8B-shaped model with FP8_E5M2 weights
+and BF16 activations: 36 layers x (q 4096<-4096, k 1024<-4096, v 1024<-4096, o 4096<-4096,
+gate 12288<-4096, up 12288<-4096, down 4096<-12288) plus lm_head 151936<-4096, batch M tokens
+(default 1).  A step is one pass over all 253 linears, each through the library's C-ABI
+(cuda_gemm_wq_bf16); 7.57 GB of distinct weights are resident in HBM, so every step streams far
+more than the L2 holds.  The metric is algorithmic bytes per second (weights + scales +
+activations in + out, each counted once per linear).
+
+With N>1 (launched under torchrun, one rank per GPU) the same token is computed tensor-parallel:
+q/k/v/gate/up/lm_head split by output feature, o/down split by input feature with an NCCL
+all-reduce, logits all-gathered; `value` stays whole-job bytes of the unsharded model per second.
+
+`--impl reference` times the CPU form of the path (dequantise to float, then sgemm) on the host
+cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HIDDEN, QDIM, KVDIM, FFN, VOCAB, LAYERS = 4096, 4096, 1024, 12288, 151936, 36
+LLAMA = dict(HIDDEN=4096, QDIM=4096, KVDIM=1024, FFN=14336, VOCAB=128256, LAYERS=32)
+W_STD = 0.02
+
+
+def model_dims(wtype: str):
+    if wtype == "fp4":
+        return LLAMA["HIDDEN"], LLAMA["QDIM"], LLAMA["KVDIM"], LLAMA["FFN"], LLAMA["VOCAB"], LLAMA["LAYERS"]
+    return HIDDEN, QDIM, KVDIM, FFN, VOCAB, LAYERS
+
+
+def layer_linears(dims):
+    """(name, N_out, K, source buffer, kind) for one layer; kind: col = split N, row = split K."""
+    hidden, qdim, kvdim, ffn, _, _ = dims
+    return [
+        ("q", qdim, hidden, "x", "col"), ("k", kvdim, hidden, "x", "col"), ("v", kvdim, hidden, "x", "col"),
+        ("o", hidden, qdim, "q", "row"), ("gate", ffn, hidden, "o", "col"), ("up", ffn, hidden, "o", "col"),
+        ("down", hidden, ffn, "gate", "row"),
+    ]
+
+
+def algorithmic_bytes(N, K, M, wtype):
+    w = N * K // 2 + N * K // 16 if wtype == "fp4" else N * K
+    return w + 2 * M * K + 2 * M * N
+
+
+def step_bytes(dims, M, wtype):
+    total = 0
+    for _, N, K, _, _ in layer_linears(dims):
+        total += algorithmic_bytes(N, K, M, wtype)
+    return total * dims[5] + algorithmic_bytes(dims[4], dims[0], M, wtype)
+
+
+# ---- clocks ------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        clocks, reasons, mx = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                clocks.append(float(s[1]))
+                mx = float(s[2])
+            except ValueError:
+                continue
+            for name, val in zip(names, s[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        med = clocks[len(clocks) // 2] if clocks else None
+        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+# ---- the GPU arm ----------------------------------------------------------------------------------
+def build_model(torch, capi, dims, M, wtype, rank, world, dev):
+    """Random weights of the model's shapes, already in the quantised byte format, resident in HBM.
+    E5M2 bytes drawn so that values look like N(0, 0.02) magnitudes (exponent field 5..10), FP4
+    nibbles uniform with E4M3 block scales near 0.0067: the kernels' time does not depend on the
+    values, and parity is the tests' job."""
+    hidden, qdim, kvdim, ffn, vocab, layers = dims
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    wt = capi.FP4_E2M1 if wtype == "fp4" else capi.FP8_E5M2
+
+    def weight(N, K):
+        if wtype == "fp4":
+            nib = torch.randint(0, 256, (N * K // 2,), dtype=torch.uint8, device=dev, generator=g)
+            sc = torch.randint(1, 8, (N * K // 16,), dtype=torch.uint8, device=dev, generator=g)  # subnormal E4M3
+            return nib, sc, 1.0
+        e = torch.randint(5, 11, (N * K,), dtype=torch.uint8, device=dev, generator=g) << 2
+        e |= torch.randint(0, 4, (N * K,), dtype=torch.uint8, device=dev, generator=g)
+        e |= torch.randint(0, 2, (N * K,), dtype=torch.uint8, device=dev, generator=g) << 7
+        return e, None, 1.0
+
+    def shard(N, K, kind):
+        if world == 1:
+            return N, K
+        return (N // world, K) if kind == "col" else (N, K // world)
+
+    lin = []
+    for _ in range(layers):
+        for name, N, K, src, kind in layer_linears(dims):
+            n, k = shard(N, K, kind)
+            W, S, inv = weight(n, k)
+            lin.append(dict(name=name, N=n, K=k, W=W, S=S, inv=inv, src=src, kind=kind, fullN=N, fullK=K))
+    n, k = shard(vocab, hidden, "col")
+    W, S, inv = weight(n, k)
+    lin.append(dict(name="lm_head", N=n, K=k, W=W, S=S, inv=inv, src="x", kind="col", fullN=vocab, fullK=hidden))
+    bufs = {
+        "x": torch.zeros(M, hidden, dtype=torch.bfloat16, device=dev),
+        "q": torch.zeros(M, qdim // world, dtype=torch.bfloat16, device=dev),
+        "k": torch.zeros(M, kvdim // world, dtype=torch.bfloat16, device=dev),
+        "v": torch.zeros(M, kvdim // world, dtype=torch.bfloat16, device=dev),
+        "o": torch.zeros(M, hidden, dtype=torch.bfloat16, device=dev),
+        "gate": torch.zeros(M, ffn // world, dtype=torch.bfloat16, device=dev),
+        "up": torch.zeros(M, ffn // world, dtype=torch.bfloat16, device=dev),
+        "down": torch.zeros(M, hidden, dtype=torch.bfloat16, device=dev),
+        "logits": torch.zeros(M, vocab // world, dtype=torch.bfloat16, device=dev),
+        "logits_all": torch.zeros(world, M, vocab // world, dtype=torch.bfloat16, device=dev),
+    }
+    return wt, lin, bufs
+
+
+def run_step(torch, dist, capi, wt, lin, bufs, M, world, flags):
+    """One token's linears.  alpha keeps activation magnitudes steady through the random layers."""
+    import math
+
+    n_launch = 0
+    for L in lin:
+        name = L["name"]
+        src = bufs[L["src"]] if name != "lm_head" else bufs["x"]
+        dst = bufs["logits"] if name == "lm_head" else bufs[name]
+        alpha = 1.0 / (W_STD * math.sqrt(L["fullK"]))
+        if wt == capi.FP4_E2M1:
+            alpha = 1.0 / (0.02 * math.sqrt(L["fullK"]))
+        rc = capi.gemm_wq_bf16(wt, L["W"], L["S"], L["inv"], src, dst, L["N"], M, L["K"], alpha=alpha, flags=flags)
+        if rc != 0:
+            raise RuntimeError(f"cuda_gemm_wq_bf16 failed on {name}: {rc}")
+        n_launch += 1
+        if world > 1 and L["kind"] == "row":
+            dist.all_reduce(dst)
+        if name == "down":
+            bufs["x"].copy_(dst) if False else None  # next layer reads "down" through the alias below
+    if world > 1:
+        dist.all_gather_into_tensor(bufs["logits_all"], bufs["logits"])
+    return n_launch
+
+
+def gpu_arm(args):
+    import torch
+
+    from __graft_entry__ import load_package
+
+    capi = load_package().capi
+    capi.lib()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    M = args.tokens
+    dims = model_dims(args.wtype)
+    wt, lin, bufs = build_model(torch, capi, dims, M, args.wtype, rank, world, dev)
+    # the layer chain: "down" of a layer is the next layer's "x"
+    bufs["down"] = bufs["x"]
+    flags = capi.FLAG_PDL if args.pdl else 0
+
+    x_host = torch.randn(M, dims[0]).to(torch.bfloat16).pin_memory()
+    logits_host = torch.empty(world, M, dims[4] // world, dtype=torch.bfloat16).pin_memory()
+    stream = torch.cuda.Stream(device=dev)
+    bytes_per_step = step_bytes(dims, M, args.wtype)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    with torch.cuda.stream(stream):
+        bufs["x"].copy_(x_host, non_blocking=True)
+        launches_per_step = run_step(torch, dist, capi, wt, lin, bufs, M, world, flags)  # first call: workspace
+        stream.synchronize()
+        assert capi.check_error("bench warmup") == 0
+        graph = None
+        if not args.no_graph:
+            graph = torch.cuda.CUDAGraph()
+            bufs["x"].copy_(x_host, non_blocking=True)
+            with torch.cuda.graph(graph, stream=stream):
+                run_step(torch, dist, capi, wt, lin, bufs, M, world, flags)
+
+        def one_step():
+            if graph is not None:
+                graph.replay()
+            else:
+                run_step(torch, dist, capi, wt, lin, bufs, M, world, flags)
+
+        # ---- device-resident arm ----
+        for _ in range(args.warmup):
+            bufs["x"].copy_(x_host, non_blocking=True)
+            one_step()
+        barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            one_step()
+        e1.record(stream)
+        barrier()
+        ms = max_over_ranks(e0.elapsed_time(e1))
+        clocks = sampler.stop() if rank == 0 else None
+
+        # ---- end to end: host activations in, host logits out, every step ----
+        src_logits = bufs["logits_all"] if world > 1 else bufs["logits"]
+        for _ in range(max(1, args.warmup // 2)):
+            bufs["x"].copy_(x_host, non_blocking=True)
+            one_step()
+            logits_host.view(-1)[:src_logits.numel()].copy_(src_logits.view(-1), non_blocking=True)
+        barrier()
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2.record(stream)
+        for _ in range(args.steps):
+            bufs["x"].copy_(x_host, non_blocking=True)
+            one_step()
+            logits_host.view(-1)[:src_logits.numel()].copy_(src_logits.view(-1), non_blocking=True)
+            stream.synchronize()  # the caller reads the logits before it can issue the next token
+        e3.record(stream)
+        barrier()
+        ms_e2e = max_over_ranks(e2.elapsed_time(e3))
+        assert capi.check_error("bench") == 0
+
+    ms_per_step = ms / args.steps
+    value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
+    e2e_value = bytes_per_step / (ms_e2e / args.steps * 1e-3) / 1e9
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
+    per_gpu = value / world
+    out = {
+        "metric": "decode_linear_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x fp8_e5m2 -> f32 acc" if args.wtype != "fp4"
+        else "bf16 x fp4_e2m1(block16,e4m3 scales) -> f32 acc", "data": "synthetic",
+        "config": {
+            "workload": f"{'llama-3.1-8b w4a16' if args.wtype == 'fp4' else 'qwen3-8b w8a16'} decode linears: "
+                        f"{dims[5]} layers x (q,k,v,o,gate,up,down) + lm_head, M={M}",
+            "tokens": M, "bytes_per_step": bytes_per_step, "l2": "7.5 GB of distinct weights per step (> L2)",
+            "cuda_graph": graph is not None, "pdl": bool(args.pdl), "parallelism": f"tp{world}",
+            "tok_per_s": round(M / (ms_per_step * 1e-3), 1),
+        },
+        "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": x_host.numel() * 2,
+                "d2h_bytes_per_step": src_logits.numel() * 2, "tok_per_s": round(M / (ms_e2e / args.steps * 1e-3), 1)},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"bound": "hbm", "achieved": round(per_gpu, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(per_gpu / peak, 4), "traffic": None, "peak_source": peak_src,
+                     "kernel": "gemv_wq_kernel", "launches_per_step": launches_per_step,
+                     "avg_launch_us": round(ms_per_step * 1e3 / launches_per_step, 3)},
+        "clocks": clocks,
+    }
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            out["cpu_baseline"] = cpu_baseline(args, budget_s=12.0)
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ---- the CPU arm -------------------------------------------------------------------------------------
+def cpu_baseline(args, budget_s: float):
+    """The CPU form of the path (dequantise to float, then sgemm; oracle port) on a bounded sample:
+    whole layers of the same workload until the time budget is used."""
+    import numpy as np
+
+    from oracle import oracle as O
+
+    dims = model_dims(args.wtype)
+    M = args.tokens
+    wt = O.FP4_E2M1 if args.wtype == "fp4" else O.FP8_E5M2
+    rng = np.random.default_rng(0)
+    shapes = [(N, K) for _, N, K, _, _ in layer_linears(dims)]
+    mats = {}
+    for N, K in set(shapes):
+        if wt == O.FP4_E2M1:
+            mats[(N, K)] = (rng.integers(0, 256, N * K // 2, dtype=np.uint8), rng.integers(1, 8, N * K // 16, dtype=np.uint8))
+        else:
+            mats[(N, K)] = (rng.integers(0x14, 0x2C, N * K, dtype=np.uint8), None)
+    wf = np.empty(max(N * K for N, K in shapes), np.float32)
+    xs = {K: rng.standard_normal((M, K)).astype(np.float32) for _, K in shapes}
+    done_bytes, t_deq, t_gemm, layers = 0, 0.0, 0.0, 0
+    t0 = time.perf_counter()
+    while time.perf_counter() - t0 < budget_s and layers < dims[5]:
+        for N, K in shapes:
+            W, S = mats[(N, K)]
+            _, td, tg = O.cpu_path_dequant_sgemm(wt, W, S, 1.0, xs[K], N, M, K, wf=wf[:N * K])
+            t_deq += td
+            t_gemm += tg
+            done_bytes += algorithmic_bytes(N, K, M, args.wtype)
+        layers += 1
+    el = t_deq + t_gemm
+    return {"value": round(done_bytes / el / 1e9, 3), "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
+            "sample": f"{layers} of {dims[5]} layers (7 linears each), M={M}; dequant {t_deq:.2f} s + sgemm {t_gemm:.2f} s",
+            "ms_per_layer": round(el / max(layers, 1) * 1e3, 2)}
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    dims = model_dims(args.wtype)
+    M = args.tokens
+    # each "step" is a bounded sample: one layer's seven linears
+    per_step_budget = 1.0
+    vals = []
+    for i in range(args.warmup + args.steps):
+        cb = cpu_baseline(args, budget_s=per_step_budget * 0.0 + 1e-9)  # exactly one layer per step
+        if i >= args.warmup:
+            vals.append(cb)
+    value = sum(v["value"] for v in vals) / len(vals)
+    ms_layer = sum(v["ms_per_layer"] for v in vals) / len(vals)
+    bytes_per_step = step_bytes(dims, M, args.wtype)
+    out = {
+        "impl": "reference", "metric": "decode_linear_hbm_gbs", "value": round(value, 3), "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(bytes_per_step / (value * 1e9) * 1e3, 2), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32 (dequantised) sgemm", "data": "synthetic",
+        "config": {"workload": f"{'llama-3.1-8b w4a16' if args.wtype == 'fp4' else 'qwen3-8b w8a16'} decode linears: "
+                               f"{dims[5]} layers x (q,k,v,o,gate,up,down) + lm_head, M={M}", "tokens": M,
+                   "bytes_per_step": bytes_per_step,
+                   "note": "each timed step is one layer's seven linears on the host cores; ms_per_step is scaled to the whole token"},
+        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": vals[0]["cores"], "kind": "port",
+                         "sample": f"one layer (7 linears) per step, {ms_layer:.1f} ms per layer"},
+        "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--tokens", type=int, default=1)
+    ap.add_argument("--wtype", default="e5m2", choices=["e5m2", "fp4"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--pdl", type=int, default=1)
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,102 @@
+"""ctypes binding of the C-ABI declared in include/cccc_cuda_b200.h.
+
+The library is the product; this module only loads it and passes device pointers through.
+There is no fallback: if the shared library is missing or a symbol is absent, loading fails.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libcccc-cuda-b200.so")
+
+# cccc::DataType (cccc/types.h:24-34)
+FLOAT, DOUBLE, HALF, BFLOAT16, FP8_E4M3, FP8_E5M2, FP4_E2M1 = range(7)
+
+PLAN_PLAIN, PLAN_DECODE, PLAN_PREFILL = 0, 1, 2
+FLAG_PDL = 1
+
+_vp, _u, _f, _i = C.c_void_p, C.c_uint, C.c_float, C.c_int
+
+# name -> (restype, argtypes): every symbol include/cccc_cuda_b200.h declares
+SYMBOLS = {
+    "cuda_convert": (_i, [_vp, _i, _vp, _i, _u, _f]),
+    "cuda_fp4_blockscale_to_bf16": (_i, [_vp, _vp, _vp, _u, _u]),
+    "cuda_float_to_fp4_blockscale": (_i, [_vp, _vp, _vp, _u, _u]),
+    "cuda_check_error": (_i, [C.c_char_p]),
+    "cuda_clear_last_error": (None, []),
+    "cuda_gemm_wq_bf16": (_i, [_i, _vp, _vp, _f, _vp, _vp, _u, _u, _u, _u, _u, _u, _u, _f, _f, _vp, _u]),
+    "cuda_gemm_wq_bf16_plan": (_i, [_i, _vp, _vp, _vp, _vp, _u, _u, _u, _u, _u, _u, _u]),
+    "cuda_b200_launch_count": (C.c_ulonglong, []),
+    "cuda_b200_version": (C.c_char_p, []),
+}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded library.  Raises if it has not been built (python cccc-lite_b200/build.py)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python cccc-lite_b200/build.py`")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(L, name)  # AttributeError if the export is missing
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    return t.data_ptr()
+
+
+def convert(src, src_type: int, dst, dst_type: int, n: int, scale: float = 1.0) -> int:
+    return lib().cuda_convert(_ptr(src), src_type, _ptr(dst), dst_type, n, scale)
+
+
+def fp4_blockscale_to_bf16(nibbles, scales, dst, n: int, block: int = 16) -> int:
+    return lib().cuda_fp4_blockscale_to_bf16(_ptr(nibbles), _ptr(scales), _ptr(dst), n, block)
+
+
+def float_to_fp4_blockscale(src, nibbles, scales, n: int, block: int = 16) -> int:
+    return lib().cuda_float_to_fp4_blockscale(_ptr(src), _ptr(nibbles), _ptr(scales), n, block)
+
+
+def check_error(label: str = "cuda") -> int:
+    return lib().cuda_check_error(label.encode())
+
+
+def gemm_wq_bf16(w_type: int, W, blk, inv_scale: float, X, Y, N: int, M: int, K: int, *, ldw: int | None = None,
+                 ldx: int | None = None, ldy_m: int | None = None, ldy_n: int = 1, alpha: float = 1.0,
+                 beta: float = 0.0, stream: int | None = None, flags: int = 0) -> int:
+    """Asynchronous fused linear on `stream` (a raw cudaStream_t value; None = torch's current stream)."""
+    if stream is None:
+        import torch
+
+        stream = torch.cuda.current_stream().cuda_stream
+    return lib().cuda_gemm_wq_bf16(w_type, _ptr(W), _ptr(blk), inv_scale, _ptr(X), _ptr(Y), N, M, K,
+                                   K if ldw is None else ldw, K if ldx is None else ldx,
+                                   N if ldy_m is None else ldy_m, ldy_n, alpha, beta, stream, flags)
+
+
+def gemm_wq_bf16_plan(w_type: int, W, blk, X, Y, N: int, M: int, K: int, *, ldw=None, ldx=None, ldy_m=None,
+                      ldy_n: int = 1) -> int:
+    return lib().cuda_gemm_wq_bf16_plan(w_type, _ptr(W), _ptr(blk), _ptr(X), _ptr(Y), N, M, K,
+                                        K if ldw is None else ldw, K if ldx is None else ldx,
+                                        N if ldy_m is None else ldy_m, ldy_n)
+
+
+def launch_count() -> int:
+    return int(lib().cuda_b200_launch_count())
+
+
+def version() -> str:
+    return lib().cuda_b200_version().decode()

@@ -1,0 +1,94 @@
+/*
+ * C-ABI of the B200 (sm_100a) quantized-weight linear library for cccc.
+ *
+ * The shared library built from cccc-lite_b200/csrc is a drop-in for the part of the
+ * reference's `cccc-cuda` plug-in library that the quantized-weight linear path uses, plus
+ * the fused entry points that replace the dequantise-then-cuBLAS sequence of
+ * cccc/cublas_real.h.  Plain pointers and sizes only; every pointer is a DEVICE pointer
+ * unless a comment says otherwise.  `type` integers are cccc::DataType values
+ * (cccc/types.h:24-34): 0 float, 1 double, 2 half, 3 bfloat16, 4 fp8_e4m3, 5 fp8_e5m2,
+ * 6 fp4_e2m1 (two nibbles per byte, low nibble = even element).
+ *
+ * Return convention (cccc-cuda/cuda_functions.cu:26-40, :3086-3088): 0 = ok, 1 = CUDA
+ * error (a line "<label> kernel launch failed: <message>" goes to stderr), -1 = unsupported
+ * type pair or argument.
+ */
+#pragma once
+
+#ifndef C_EXPORT
+#ifdef _WIN32
+#define C_EXPORT extern "C" __declspec(dllexport)
+#else
+#define C_EXPORT extern "C" __attribute__((visibility("default")))
+#endif
+#endif
+
+/* ---- entry points that exist in the reference (same names, same arguments) -------------- */
+
+/* Replaces cuda_convert, cccc-cuda/cuda_functions.h:224 (cuda_functions.cu:3066-3090).
+ * Converts n elements src_type -> dst_type, multiplying by `scale` where the reference's
+ * kernel for that pair does.  Same 7x7 table of supported pairs; same-type with scale 1
+ * copies n BYTES (as the reference does).  Synchronous like the reference (device sync
+ * before returning). */
+C_EXPORT int cuda_convert(const void* src, int src_type, void* dst, int dst_type, unsigned int n, float scale);
+
+/* Replaces cuda_fp4_blockscale_to_bf16, cuda_functions.h:232 (cuda_functions.cu:2926-2960).
+ * src_scales holds one E4M3 byte per `block_size` consecutive elements (a dequant multiplier). */
+C_EXPORT int cuda_fp4_blockscale_to_bf16(const void* src_nibbles, const void* src_scales, void* dst,
+    unsigned int n_elems, unsigned int block_size);
+
+/* Replaces cuda_float_to_fp4_blockscale, cuda_functions.h:230 (cuda_functions.cu:2896-2950). */
+C_EXPORT int cuda_float_to_fp4_blockscale(const void* src, void* dst_nibbles, void* dst_scales,
+    unsigned int n_elems, unsigned int block_size);
+
+/* Replaces cuda_check_error, cuda_functions.h:200 (cuda_functions.cu:48-51): device sync, report
+ * any pending CUDA error or any error status raised by this library's kernels (a bounded wait
+ * that ran out); 0 = clean. */
+C_EXPORT int cuda_check_error(const char* label);
+
+/* Replaces cuda_clear_last_error, cuda_functions.h:198 (cuda_functions.cu:42-45). */
+C_EXPORT void cuda_clear_last_error(void);
+
+/* ---- additions: the fused linear -------------------------------------------------------- */
+
+/* Replaces the sequence at cccc/cublas_real.h:943-964 (and its mirror :1066-1087, and the typed
+ * overloads :673-684, :740-751): grow workspace, dequantise the whole weight to BF16,
+ * cublasGemmEx BF16xBF16->BF16 with FP32 compute, device sync.
+ *
+ *   Y[m*ldy_m + n*ldy_n] = bf16( alpha * sum_k dq(W[n*ldw + k]) * X[m*ldx + k] + beta * Y[...] )
+ *
+ * W  : [N_out, K] quantised weight, K contiguous (cccc stores (K, N_out) column-major, which is
+ *      the same bytes), w_type 4, 5 or 6; ldw in ELEMENTS.
+ * dq : types 4/5: rne_bf16(decode(byte) * inv_scale).  Type 6 with blk_scales != NULL:
+ *      rne_bf16(table[nibble] * e4m3(blk_scales[(n*ldw+k)/16])), inv_scale ignored, as the
+ *      reference does (block size 16 is fixed at its call sites, cublas_real.h:953); type 6
+ *      with blk_scales == NULL: rne_bf16(table[nibble] * inv_scale).
+ * X  : [M_tokens, K] BF16, ldx in elements.  Y: BF16; ldy_m / ldy_n are the element strides of
+ *      the token and output-feature index (cccc's layout is ldy_m = N_out (ldc), ldy_n = 1; the
+ *      mirrored operand order, weight as B, gives ldy_m = 1, ldy_n = ldc).
+ * stream : a cudaStream_t (NULL = legacy default stream).  The call is ASYNCHRONOUS on that
+ *      stream; cuda_check_error() or any synchronising call makes the result visible, which
+ *      is where the reference's own wrappers synchronise too.
+ * Any shape, stride or alignment is accepted: aligned shapes take the TMA-fed kernels, the rest
+ * a plain kernel.  The first call on a device allocates that device's workspace (a few MB);
+ * make it before any stream capture.  Calls that share a device must be ordered on one stream
+ * (they share the workspace), as the reference's single `Cublas` instance requires too.
+ * flags: bit 0 = launch with programmatic dependent launch so that this call's weight prefetch
+ * overlaps the tail of the previous kernel on the stream (X, Y are only touched after that
+ * kernel has finished). */
+C_EXPORT int cuda_gemm_wq_bf16(int w_type, const void* W, const void* blk_scales, float inv_scale, const void* X,
+    void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx,
+    unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta, void* stream, unsigned int flags);
+
+/* Tuning/diagnostic: returns which kernel cuda_gemm_wq_bf16 would pick for a shape
+ * (0 = plain kernel, 1 = decode GEMV (M<=32), 2 = prefill tcgen05 GEMM) without launching. */
+C_EXPORT int cuda_gemm_wq_bf16_plan(int w_type, const void* W, const void* blk_scales, const void* X,
+    const void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx,
+    unsigned int ldy_m, unsigned int ldy_n);
+
+/* Number of kernels this library has launched in the calling process since load (all entry
+ * points).  Used by the benchmark to report its launch count. */
+C_EXPORT unsigned long long cuda_b200_launch_count(void);
+
+/* Library identification: returns a static string "cccc-cuda-b200 <version> sm_100a". */
+C_EXPORT const char* cuda_b200_version(void);
