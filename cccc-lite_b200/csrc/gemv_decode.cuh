@@ -1,12 +1,15 @@
 // Decode-side quantized-weight linear (M <= 32 tokens): an HBM-bound GEMV.
 //
-// One persistent CTA per SM.  A producer warp streams the weight bytes (and FP4 block scales)
-// from HBM into a shared-memory ring with bulk asynchronous copies (cp.async.bulk + mbarrier),
-// one copy per weight row segment, and stages the matching slice of the BF16 activations.
+// One persistent CTA per SM.  A producer lane streams the weight bytes (and FP4 block scales)
+// and the matching slice of the BF16 activations from HBM/L2 into a shared-memory ring with
+// tiled TMA copies (cp.async.bulk.tensor + mbarrier): one copy per operand per stage, because
+// the copy engine takes on the order of a hundred cycles per instruction whatever its size.
 // Eight consumer warps dequantise to BF16 in registers and feed m16n8k16 BF16 MMAs with FP32
 // accumulators: the weight tile is the A operand (16 output features x 16 k), the tokens are
 // the 8 columns of B.  The k order inside a fragment is permuted so that every lane converts
-// the 16 bytes it loaded itself; the activation slice is staged in the same permutation.
+// the 16 bytes it loaded itself; the activation fragment is loaded in the same order.
+// A CTA takes at most half of an SM, so that under programmatic dependent launch the next
+// linear of the stream is already resident and prefetching its weights while this one ends.
 //
 // Work is cut stream-K style: the (row block, k stage) items of the whole matrix are dealt to
 // the CTAs in equal contiguous runs, so every SM streams the same number of bytes whatever the
@@ -19,6 +22,8 @@
 #pragma once
 
 #include "common.cuh"
+
+#include <cuda.h>
 
 namespace b200
 {
@@ -39,11 +44,10 @@ struct GemvParams
     float alpha, beta;
     float post_scale;           // exact power of two folded out of the weights (applied with alpha)
     unsigned int n_row_blocks, n_kstages, total_items;
+    unsigned int gran;          // items are dealt to CTAs in groups of `gran`: 1 = stream-K, n_kstages = whole row blocks
     unsigned int n_stages;      // ring depth
 };
 
-constexpr int kConsumerWarps = 8;
-constexpr int kGemvThreads = 32 * (kConsumerWarps + 1);
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;    // 2 s
 
 enum : unsigned int
@@ -109,7 +113,11 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void consumer_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory"); }
+template <int THREADS>
+__device__ __forceinline__ void consumer_bar_sync()
+{
+    asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory");
+}
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
 {
@@ -132,7 +140,7 @@ __device__ __forceinline__ uint32_t lds_u16(uint32_t addr)
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
     uint32_t b1)
 {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -220,65 +228,94 @@ __device__ __forceinline__ void fp4_block_multipliers(uint32_t two, uint32_t& m0
 // ---- geometry ------------------------------------------------------------------------------------
 // MT  : token groups of 8 (tokens <= 8*MT)
 // RT  : 16-row MMA tiles per warp along N
-// WR  : consumer warps along N (the other kConsumerWarps/WR warps split the k steps of a stage)
+// WR  : consumer warps along N
+// WK  : consumer warps along k (they split the k steps of a stage)
 // SKS : k steps per stage; one k step is 64 bytes of every weight row
-template <int WT_, int MT_, int RT_, int WR_, int SKS_>
+// XB  : token rows in the activation box (2: M <= 2, plain layout; else 8*MT, 128-byte swizzle)
+// OCC : CTAs that may share an SM (2 lets the next kernel of the stream prefetch its weights
+//       while this one finishes)
+//
+// Shared-memory layout of a stage, each part written by ONE tiled TMA copy:
+//   weights  [k step][row][64 B]            rows 2q and 2q+1 are adjacent 64-byte runs, so the eight
+//                                           lanes of a 128-bit read phase cover 128 contiguous bytes
+//   scales   [k step pair][row][16 B]       FP4 only: 8 E4M3 bytes per row per k step
+//   acts     [128-byte slab][token][128 B]  64 BF16 per slab row, 16-byte chunks XOR-swizzled by
+//                                           (token & 7) when XB is a multiple of 8
+template <int WT_, int MT_, int RT_, int WR_, int WK_, int SKS_, int XB_, int OCC_>
 struct GemvCfg
 {
-    static constexpr int WT = WT_, MT = MT_, RT = RT_, WR = WR_, SKS = SKS_;
-    static constexpr int WK = kConsumerWarps / WR;
+    static constexpr int WT = WT_, MT = MT_, RT = RT_, WR = WR_, WK = WK_, SKS = SKS_, XB = XB_, OCC = OCC_;
+    static constexpr int NCW = WR * WK;                           // consumer warps
+    static constexpr int THREADS = 32 * (NCW + 1);                // + the producer warp
     static constexpr int R = 16 * RT * WR;                        // rows per row block
     static constexpr int KSTEP = (WT == DT_FP4) ? 128 : 64;       // elements per k step
-    static constexpr int SKB = 64 * SKS;                          // weight bytes per row per stage
     static constexpr int SKE = KSTEP * SKS;                       // elements per stage along k
-    static constexpr int WPITCH = SKB + 64;                       // pitch % 128 == 64: conflict-free 128-bit reads
-    static constexpr int SPITCH = (WT == DT_FP4) ? (SKE / 16 + 16) : 0;
-    static constexpr int XPITCH = SKE * 2 + 16;
-    static constexpr int W_BYTES = R * WPITCH;
-    static constexpr int S_BYTES = R * SPITCH;
+    static constexpr int XSLABS = SKE / 64;                       // 128-byte activation slabs per stage
+    static constexpr bool XSWZ = (XB % 8) == 0;
+    static constexpr int W_BYTES = SKS * R * 64;
+    static constexpr int S_BYTES = (WT == DT_FP4) ? (SKS / 2) * R * 16 : 0;
+    static constexpr int X_BYTES = XSLABS * XB * 128;
+    static constexpr int STAGE_BYTES = ((W_BYTES + S_BYTES + X_BYTES + 1023) / 1024) * 1024;
+    static constexpr int X_OFFSET = ((W_BYTES + S_BYTES + 1023) / 1024) * 1024;    // swizzle needs 1 KB alignment
     static constexpr int RED_BYTES = WK * R * 8 * MT * 4;
-    __host__ __device__ static constexpr int x_bytes(int m) { return ((m * XPITCH + 127) / 128) * 128; }
-    __host__ __device__ static constexpr int stage_bytes(int m) { return W_BYTES + S_BYTES + x_bytes(m); }
-    // barriers (2 * 16 * 8 B) + flags, padded to 512 B
-    static constexpr int HEADER_BYTES = 512;
+    static constexpr int HEADER_BYTES = 1024;                     // barriers and flags
     static constexpr int kMaxStages = 16;
+    static_assert(WT != DT_FP4 || (SKS % 2) == 0, "FP4 stages hold whole scale chunks");
+    static_assert(X_OFFSET + X_BYTES <= STAGE_BYTES + 1024, "layout");
 };
 
 struct ItemRange
 {
     unsigned int beg, end;
 };
-__host__ __device__ inline ItemRange cta_items(unsigned int cta, unsigned int grid, unsigned int total)
+// CTA c owns the item groups [floor(c*G/grid), floor((c+1)*G/grid)), G = total/gran groups.
+__host__ __device__ inline ItemRange cta_items(unsigned int cta, unsigned int grid, unsigned int total, unsigned int gran)
 {
+    const unsigned long long groups = total / gran;
     ItemRange r;
-    r.beg = (unsigned int)(((unsigned long long)cta * total) / grid);
-    r.end = (unsigned int)(((unsigned long long)(cta + 1) * total) / grid);
+    r.beg = (unsigned int)(((unsigned long long)cta * groups) / grid) * gran;
+    r.end = (unsigned int)(((unsigned long long)(cta + 1) * groups) / grid) * gran;
     return r;
 }
-// The CTA whose run contains item i: the largest c with floor(c*total/grid) <= i.
-__host__ __device__ inline unsigned int cta_of_item(unsigned int i, unsigned int grid, unsigned int total)
+// The CTA whose run contains item i: the largest c with floor(c*G/grid) <= i/gran.
+__host__ __device__ inline unsigned int cta_of_item(unsigned int i, unsigned int grid, unsigned int total, unsigned int gran)
 {
-    return (unsigned int)((((unsigned long long)i + 1) * grid - 1) / total);
+    const unsigned long long groups = total / gran;
+    return (unsigned int)((((unsigned long long)(i / gran) + 1) * grid - 1) / groups);
+}
+
+// 3-D tiled TMA load, completion counted on an mbarrier.  c0 is always 0 here (the inner extent is
+// one whole 16-byte-aligned run), so the 16-byte rule on the inner coordinate holds by construction.
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
+        : "memory");
 }
 
 // ---- the kernel ------------------------------------------------------------------------------------
 template <class Cfg, bool SCALED>
-__global__ void __launch_bounds__(kGemvThreads, 1) gemv_wq_kernel(const GemvParams p)
+__global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
+    gemv_wq_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
+        const __grid_constant__ CUtensorMap tmX, const GemvParams p)
 {
     constexpr int WT = Cfg::WT, MT = Cfg::MT, RT = Cfg::RT, WK = Cfg::WK, R = Cfg::R;
+    constexpr int kConsumerWarps = Cfg::NCW;
+    constexpr int CT = Cfg::NCW * 32;    // consumer threads
     constexpr int AREGS = (WT == DT_FP4) ? 16 : 8;    // bf16x2 registers per weight row per k step
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty_bar = full_bar + Cfg::kMaxStages;
     // sh_flags[0] = abort, sh_flags[1] = "this CTA reduces the row block"
     volatile unsigned int* sh_flags = reinterpret_cast<volatile unsigned int*>(smem + 2 * Cfg::kMaxStages * 8);
-    float* red = reinterpret_cast<float*>(smem + Cfg::HEADER_BYTES);
-    unsigned char* stages = smem + Cfg::HEADER_BYTES + Cfg::RED_BYTES;
-    const unsigned int stage_bytes = (unsigned int)Cfg::stage_bytes((int)p.M);
+    unsigned char* stages = smem + Cfg::HEADER_BYTES;
+    float* red = reinterpret_cast<float*>(smem + Cfg::HEADER_BYTES + (size_t)p.n_stages * Cfg::STAGE_BYTES);
     const unsigned int NS = p.n_stages;
 
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const ItemRange items = cta_items(blockIdx.x, gridDim.x, p.total_items);
+    const ItemRange items = cta_items(blockIdx.x, gridDim.x, p.total_items, p.gran);
     const unsigned int n_items = items.end - items.beg;
 
     if (threadIdx.x == 0)
@@ -297,84 +334,32 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_wq_kernel(const GemvPara
 
     if (warp == kConsumerWarps)
     {
-        // =========================== producer warp ===========================
+        // =========================== producer: one elected lane ===========================
+        if (lane != 0) { return; }
         auto issue_weights = [&](unsigned int it) {
             const unsigned int item = items.beg + it;
             const unsigned int rb = item / p.n_kstages, ks = item % p.n_kstages;
             const unsigned int s = it % NS;
-            unsigned char* st = stages + (size_t)s * stage_bytes;
-            const unsigned int k0 = ks * Cfg::SKE;
-            const unsigned int kval = min((unsigned int)Cfg::SKE, p.K - k0);    // valid elements along k
-            const unsigned int wbytes = (WT == DT_FP4) ? kval / 2 : kval;
-            const unsigned int sbytes = (WT == DT_FP4) ? kval / 16 : 0;
-            const unsigned int n0 = rb * R;
-            const unsigned int rows = min((unsigned int)R, p.N - n0);
-            if (lane == 0) { mbar_expect_tx(full_bar + s, rows * (wbytes + sbytes)); }
-            __syncwarp();
-            for (unsigned int r = lane; r < rows; r += 32)
-            {
-                const size_t e = (size_t)(n0 + r) * p.ldw + k0;    // element index of the row segment
-                bulk_g2s(st + r * Cfg::WPITCH, p.W + ((WT == DT_FP4) ? e / 2 : e), wbytes, full_bar + s);
-                if (WT == DT_FP4) { bulk_g2s(st + Cfg::W_BYTES + r * Cfg::SPITCH, p.blk + e / 16, sbytes, full_bar + s); }
-            }
+            unsigned char* st = stages + (size_t)s * Cfg::STAGE_BYTES;
+            mbar_expect_tx(full_bar + s, Cfg::W_BYTES + Cfg::S_BYTES);
+            tma_load_3d(st, &tmW, 0, (int)(rb * R), (int)(ks * Cfg::SKS), full_bar + s);
+            if (WT == DT_FP4) { tma_load_3d(st + Cfg::W_BYTES, &tmS, 0, (int)(rb * R), (int)(ks * (Cfg::SKS / 2)), full_bar + s); }
         };
-        auto stage_x = [&](unsigned int it) {
+        auto issue_acts = [&](unsigned int it) {
             const unsigned int item = items.beg + it;
             const unsigned int ks = item % p.n_kstages;
             const unsigned int s = it % NS;
-            unsigned char* xt = stages + (size_t)s * stage_bytes + Cfg::W_BYTES + Cfg::S_BYTES;
-            const unsigned int k0 = ks * Cfg::SKE;
-            const unsigned int kval = min((unsigned int)Cfg::SKE, p.K - k0);
-            const unsigned int chunks = kval / 8;    // 16-byte chunks per token row
-            const unsigned int total = chunks * p.M;
-            for (unsigned int base = 0; base < total; base += 32 * 4)
-            {
-                uint4 v[4];
-                unsigned int cidx[4], midx[4];
-#pragma unroll
-                for (int u = 0; u < 4; u++)
-                {
-                    const unsigned int q = base + u * 32 + lane;
-                    midx[u] = q / chunks;
-                    cidx[u] = q - midx[u] * chunks;
-                    v[u] = make_uint4(0, 0, 0, 0);
-                    if (q < total)
-                    {
-                        v[u] = *reinterpret_cast<const uint4*>(p.X + (size_t)midx[u] * p.ldx + k0 + cidx[u] * 8);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < 4; u++)
-                {
-                    const unsigned int q = base + u * 32 + lane;
-                    if (q < total)
-                    {
-                        uint4 o = v[u];
-                        unsigned int c = cidx[u];
-                        if (WT == DT_FP4)
-                        {
-                            // (x0..x7) -> (x0,x4)(x1,x5)(x2,x6)(x3,x7); chunks swizzled so that the four
-                            // 16-byte reads of a lane (64 bytes apart across lanes) hit distinct banks
-                            o.x = prmt(v[u].x, v[u].z, 0x5410u);
-                            o.y = prmt(v[u].x, v[u].z, 0x7632u);
-                            o.z = prmt(v[u].y, v[u].w, 0x5410u);
-                            o.w = prmt(v[u].y, v[u].w, 0x7632u);
-                            c ^= ((c >> 3) & 1u) << 1;
-                        }
-                        *reinterpret_cast<uint4*>(xt + midx[u] * Cfg::XPITCH + c * 16) = o;
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) { mbar_arrive(full_bar + s); }
+            unsigned char* st = stages + (size_t)s * Cfg::STAGE_BYTES;
+            mbar_expect_tx(full_bar + s, Cfg::X_BYTES);
+            tma_load_3d(st + Cfg::X_OFFSET, &tmX, 0, 0, (int)(ks * Cfg::XSLABS), full_bar + s);
+            mbar_arrive(full_bar + s);
         };
-
         // Weights do not depend on the previous kernel of the stream: prefetch the first ring of
         // stages before waiting for it; activations only after.
         const unsigned int pre = min(NS, n_items);
         for (unsigned int it = 0; it < pre; it++) { issue_weights(it); }
         pdl_wait();
-        for (unsigned int it = 0; it < pre; it++) { stage_x(it); }
+        for (unsigned int it = 0; it < pre; it++) { issue_acts(it); }
         bool ok = true;
         unsigned int issued = pre;
         for (unsigned int it = pre; it < n_items; it++)
@@ -383,15 +368,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_wq_kernel(const GemvPara
             if (sh_flags[0] != 0 || !mbar_wait_bounded(empty_bar + s, ((it / NS) - 1) & 1u))
             {
                 ok = false;
-                if (lane == 0)
-                {
-                    atomicMax(p.status, (unsigned int)ST_TIMEOUT_EMPTY);
-                    sh_flags[0] = 1;
-                }
+                atomicMax(p.status, (unsigned int)ST_TIMEOUT_EMPTY);
+                sh_flags[0] = 1;
                 break;
             }
             issue_weights(it);
-            stage_x(it);
+            issue_acts(it);
             issued = it + 1;
         }
         // Do not leave while copies are in flight.  Normally the consumers' last "empty" arrivals
@@ -403,7 +385,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_wq_kernel(const GemvPara
             uint64_t* bar = ok ? empty_bar + (it % NS) : full_bar + (it % NS);
             if (!mbar_wait_bounded(bar, (it / NS) & 1u))
             {
-                if (ok && sh_flags[0] == 0 && lane == 0) { atomicMax(p.status, (unsigned int)ST_TIMEOUT_EMPTY); }
+                if (ok && sh_flags[0] == 0) { atomicMax(p.status, (unsigned int)ST_TIMEOUT_EMPTY); }
                 ok = false;
             }
         }
@@ -414,7 +396,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_wq_kernel(const GemvPara
     pdl_wait();
     const unsigned int g = lane >> 2, t = lane & 3;
     const unsigned int wr = warp / WK, wk = warp % WK;
-    const unsigned int ctid = threadIdx.x;    // 0 .. 255: the consumer threads come first
+    const unsigned int ctid = threadIdx.x;    // the consumer threads come first
     constexpr unsigned int TILE = R * 8 * MT;  // floats in one [token][row] tile
     bool ok = true;
 
@@ -452,11 +434,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_wq_kernel(const GemvPara
             if (!ok) { continue; }
             const unsigned int ks = ks0 + j;
             const unsigned int kval = min((unsigned int)Cfg::SKE, p.K - ks * Cfg::SKE);
-            const unsigned int nsteps = kval / Cfg::KSTEP;
-            const uint32_t st = smem_u32(stages + (size_t)s * stage_bytes);
-            const uint32_t xt = st + Cfg::W_BYTES + Cfg::S_BYTES;
-            for (unsigned int step = wk; step < nsteps; step += WK)
-            {
+            const unsigned int nsteps = kval / Cfg::KSTEP;    // beyond K the TMA fills zeros; skip them
+            const uint32_t st = smem_u32(stages + (size_t)s * Cfg::STAGE_BYTES);
+            const uint32_t xt = st + Cfg::X_OFFSET;
+            auto do_step = [&](unsigned int step) {
                 // ---- weights: rows (g, g+8) of each of my RT tiles, 16 bytes per row ----
                 uint32_t A[RT][2][AREGS];
 #pragma unroll
@@ -466,12 +447,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_wq_kernel(const GemvPara
                     for (int h = 0; h < 2; h++)
                     {
                         const unsigned int row = (wr * RT + rt) * 16 + h * 8 + g;
-                        const uint4 wv = lds128(st + row * Cfg::WPITCH + step * 64 + t * 16);
+                        const uint4 wv = lds128(st + (step * R + row) * 64 + t * 16);
                         const uint32_t w[4] = { wv.x, wv.y, wv.z, wv.w };
                         if (WT == DT_FP4)
                         {
                             uint32_t m01[2];
-                            fp4_block_multipliers(lds_u16(st + Cfg::W_BYTES + row * Cfg::SPITCH + step * 8 + t * 2), m01[0], m01[1]);
+                            fp4_block_multipliers(
+                                lds_u16(st + Cfg::W_BYTES + ((step >> 1) * R + row) * 16 + (step & 1u) * 8 + t * 2), m01[0], m01[1]);
 #pragma unroll
                             for (int i = 0; i < 4; i++)
                             {
@@ -496,16 +478,24 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_wq_kernel(const GemvPara
                 for (int mt = 0; mt < MT; mt++)
                 {
                     const unsigned int token = mt * 8 + g;
-                    const bool live = token < p.M;
+                    // token rows past M were zero-filled by the TMA; rows past the box do not exist
+                    const bool live = token < (unsigned int)Cfg::XB;
+                    const unsigned int swz = Cfg::XSWZ ? (token & 7u) : 0u;
                     if (WT == DT_FP4)
                     {
-                        uint4 XB[4];
+                        uint4 XBr[4];
+                        const uint32_t xrow = xt + ((step * 2 + (t >> 1)) * Cfg::XB + token) * 128;
 #pragma unroll
                         for (int i = 0; i < 4; i++)
                         {
-                            unsigned int c = step * 16 + t * 4 + i;
-                            c ^= ((c >> 3) & 1u) << 1;
-                            XB[i] = live ? lds128(xt + token * Cfg::XPITCH + c * 16) : make_uint4(0, 0, 0, 0);
+                            // eight activations (x0..x7) -> (x0,x4)(x1,x5)(x2,x6)(x3,x7), the pairing of the
+                            // dequantised nibbles
+                            const unsigned int c = (t & 1u) * 4 + i;
+                            const uint4 v = live ? lds128(xrow + ((c ^ swz) << 4)) : make_uint4(0, 0, 0, 0);
+                            XBr[i].x = prmt(v.x, v.z, 0x5410u);
+                            XBr[i].y = prmt(v.x, v.z, 0x7632u);
+                            XBr[i].z = prmt(v.y, v.w, 0x5410u);
+                            XBr[i].w = prmt(v.y, v.w, 0x7632u);
                         }
 #pragma unroll
                         for (int rt = 0; rt < RT; rt++)
@@ -514,17 +504,17 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_wq_kernel(const GemvPara
                             for (int i = 0; i < 4; i++)
                             {
                                 mma_bf16_16816(acc[rt][mt][0], A[rt][0][(4 * i) % AREGS], A[rt][1][(4 * i) % AREGS],
-                                    A[rt][0][(4 * i + 1) % AREGS], A[rt][1][(4 * i + 1) % AREGS], XB[i].x, XB[i].y);
+                                    A[rt][0][(4 * i + 1) % AREGS], A[rt][1][(4 * i + 1) % AREGS], XBr[i].x, XBr[i].y);
                                 mma_bf16_16816(acc[rt][mt][1], A[rt][0][(4 * i + 2) % AREGS], A[rt][1][(4 * i + 2) % AREGS],
-                                    A[rt][0][(4 * i + 3) % AREGS], A[rt][1][(4 * i + 3) % AREGS], XB[i].z, XB[i].w);
+                                    A[rt][0][(4 * i + 3) % AREGS], A[rt][1][(4 * i + 3) % AREGS], XBr[i].z, XBr[i].w);
                             }
                         }
                     }
                     else
                     {
-                        const uint32_t xa = xt + token * Cfg::XPITCH + (step * 64 + t * 16) * 2;
-                        const uint4 x0 = live ? lds128(xa) : make_uint4(0, 0, 0, 0);
-                        const uint4 x1 = live ? lds128(xa + 16) : make_uint4(0, 0, 0, 0);
+                        const uint32_t xrow = xt + (step * Cfg::XB + token) * 128;
+                        const uint4 x0 = live ? lds128(xrow + (((2 * t) ^ swz) << 4)) : make_uint4(0, 0, 0, 0);
+                        const uint4 x1 = live ? lds128(xrow + (((2 * t + 1) ^ swz) << 4)) : make_uint4(0, 0, 0, 0);
                         const uint32_t B[8] = { x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w };
 #pragma unroll
                         for (int rt = 0; rt < RT; rt++)
@@ -538,6 +528,21 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_wq_kernel(const GemvPara
                         }
                     }
                 }
+                        };
+            constexpr int SPW = (Cfg::SKS + WK - 1) / WK;    // k steps per warp in a full stage
+            if (nsteps == (unsigned int)Cfg::SKS)
+            {
+                // full stage: unrolled, so that the loads of all my steps are in flight together
+#pragma unroll
+                for (int u = 0; u < SPW; u++)
+                {
+                    const unsigned int step = wk + u * WK;
+                    if ((Cfg::SKS % WK) == 0 || step < (unsigned int)Cfg::SKS) { do_step(step); }
+                }
+            }
+            else
+            {
+                for (unsigned int step = wk; step < nsteps; step += WK) { do_step(step); }
             }
             __syncwarp();
             if (lane == 0) { mbar_arrive(empty_bar + s); }
@@ -559,7 +564,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_wq_kernel(const GemvPara
                 myred[(tok + 1) * R + row + 8] = acc[rt][mt][0][3] + acc[rt][mt][1][3];
             }
         }
-        consumer_bar_sync();
+        consumer_bar_sync<CT>();
         const unsigned int n_out = p.M * R;    // live [token][row] entries
         const bool full = (ks0 == 0 && seg == p.n_kstages);
         const unsigned int n0 = rb * R;
@@ -578,7 +583,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_wq_kernel(const GemvPara
         {
             if (ok)
             {
-                for (unsigned int e = ctid; e < n_out; e += kConsumerWarps * 32)
+                for (unsigned int e = ctid; e < n_out; e += CT)
                 {
                     float v = 0.f;
 #pragma unroll
@@ -592,7 +597,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_wq_kernel(const GemvPara
             float* mine = p.partials + ((size_t)blockIdx.x * 2 + (first_segment ? 0 : 1)) * TILE;
             if (ok)
             {
-                for (unsigned int e = ctid; e < n_out; e += kConsumerWarps * 32)
+                for (unsigned int e = ctid; e < n_out; e += CT)
                 {
                     float v = 0.f;
 #pragma unroll
@@ -601,9 +606,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_wq_kernel(const GemvPara
                 }
             }
             __threadfence();
-            consumer_bar_sync();
-            const unsigned int c_first = cta_of_item(rb * p.n_kstages, gridDim.x, p.total_items);
-            const unsigned int c_last = cta_of_item(rb * p.n_kstages + p.n_kstages - 1, gridDim.x, p.total_items);
+            consumer_bar_sync<CT>();
+            const unsigned int c_first = cta_of_item(rb * p.n_kstages, gridDim.x, p.total_items, p.gran);
+            const unsigned int c_last = cta_of_item(rb * p.n_kstages + p.n_kstages - 1, gridDim.x, p.total_items, p.gran);
             if (ctid == 0)
             {
                 unsigned int last = 0;
@@ -614,16 +619,16 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_wq_kernel(const GemvPara
                 }
                 sh_flags[1] = last;
             }
-            consumer_bar_sync();
+            consumer_bar_sync<CT>();
             if (sh_flags[1] != 0)
             {
                 __threadfence();
-                for (unsigned int e = ctid; e < n_out; e += kConsumerWarps * 32)
+                for (unsigned int e = ctid; e < n_out; e += CT)
                 {
                     float v = 0.f;
                     for (unsigned int c = c_first; c <= c_last; c++)
                     {
-                        const unsigned int slot = (cta_items(c, gridDim.x, p.total_items).beg / p.n_kstages == rb) ? 0u : 1u;
+                        const unsigned int slot = (cta_items(c, gridDim.x, p.total_items, p.gran).beg / p.n_kstages == rb) ? 0u : 1u;
                         v += __ldcg(p.partials + ((size_t)c * 2 + slot) * TILE + e);
                     }
                     store_out(e, v);
@@ -631,7 +636,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_wq_kernel(const GemvPara
                 if (ctid == 0) { p.counters[c_first] = 0; }
             }
         }
-        consumer_bar_sync();    // `red` and sh_flags[1] are reused by the next segment
+        consumer_bar_sync<CT>();    // `red` and sh_flags[1] are reused by the next segment
     }
 }
 

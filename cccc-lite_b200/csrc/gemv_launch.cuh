@@ -1,0 +1,322 @@
+// Host-side launch logic of the quantized-weight linear: kernel choice, tensor maps, schedule.
+// Shared by every translation unit that launches these kernels; what differs between them is
+// only where the scratch memory (FP32 partial tiles, arrival counters, status word) lives.
+#pragma once
+
+#include "common.cuh"
+#include "gemv_decode.cuh"
+#include "gemm_prefill.cuh"
+
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+
+namespace b200
+{
+
+constexpr int kMaxDevices = 64;
+
+// Where a launch finds its scratch memory, and the device facts the launch logic needs.
+struct GemvScratch
+{
+    float* partials = nullptr;           // FP32 partial tiles of the split-k schedule
+    size_t partial_bytes = 0;
+    unsigned int* counters = nullptr;    // arrival counters, zero between launches
+    unsigned int n_counters = 0;
+    unsigned int* status = nullptr;      // error word, 0 = clean
+    int device = 0;
+    int sm_count = 0;
+    int max_smem = 0;       // largest dynamic shared memory one CTA may ask for
+    int smem_per_sm = 0;    // shared memory of one SM
+};
+
+// ---- launch helpers ---------------------------------------------------------------------------------
+static bool is_pow2_scale(float s)
+{
+    if (!(s > 0.f) || std::isinf(s)) { return false; }
+    int e = 0;
+    const float m = std::frexp(s, &e);
+    return m == 0.5f && e >= -39 && e <= 41;    // 2^-40 .. 2^40
+}
+
+// ---- tensor maps -------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+    CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried)
+    {
+        tried = true;
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess
+            && q == cudaDriverEntryPointSuccess)
+        {
+            fn = (EncodeTiledFn)sym;
+        }
+        else { cudaGetLastError(); }
+    }
+    return fn;
+}
+
+// A 3-D view (inner run, rows, runs along k) of a row-major [rows, k] operand: dimension 1 walks
+// the rows (stride = the leading dimension), dimension 2 walks the 'inner'-sized runs of one row.
+// A box {inner, box_rows, box_runs} therefore lands in shared memory as [run][row][inner].
+static bool make_map(CUtensorMap* map, CUtensorMapDataType dt, unsigned int elem_bytes, const void* base, unsigned int inner,
+    unsigned long long rows, unsigned long long runs, unsigned long long row_stride_bytes, unsigned int box_rows,
+    unsigned int box_runs, bool swizzle128)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) { return false; }
+    const cuuint64_t gdim[3] = { inner, rows, runs };
+    const cuuint64_t gstride[2] = { row_stride_bytes, (cuuint64_t)inner * elem_bytes };
+    const cuuint32_t box[3] = { inner, box_rows, box_runs };
+    const cuuint32_t estr[3] = { 1, 1, 1 };
+    const CUresult r = fn(map, dt, 3, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+static int tuning_align()
+{
+    static int v = -2;
+    if (v == -2)
+    {
+        const char* e = getenv("CCCC_B200_GEMV_ALIGN");
+        v = e ? atoi(e) : -1;
+    }
+    return v;
+}
+
+static int tuning_variant()
+{
+    static int v = -1;
+    if (v < 0)
+    {
+        const char* e = getenv("CCCC_B200_GEMV_VARIANT");
+        v = e ? atoi(e) : 0;
+    }
+    return v;
+}
+
+template <class Cfg, bool SCALED>
+static int launch_gemv_cfg(GemvParams p, const GemvScratch* ws, cudaStream_t stream, bool pdl)
+{
+    constexpr int WT = Cfg::WT;
+    // two CTAs per SM share the SM's shared memory (each also reserves 1 KB for the system)
+    const int budget = (Cfg::OCC == 2) ? (ws->smem_per_sm / 2 - 1024) : ws->max_smem;
+    int ns = (budget - Cfg::HEADER_BYTES - Cfg::RED_BYTES) / Cfg::STAGE_BYTES;
+    if (ns > Cfg::kMaxStages) { ns = Cfg::kMaxStages; }
+    if (ns < 2) { return -2; }
+    p.n_row_blocks = (p.N + Cfg::R - 1) / Cfg::R;
+    p.n_kstages = (p.K + Cfg::SKE - 1) / Cfg::SKE;
+    const unsigned long long total = (unsigned long long)p.n_row_blocks * p.n_kstages;
+    if (total == 0 || total > 0x7FFFFFFFull) { return -2; }
+    p.total_items = (unsigned int)total;
+    p.n_stages = (unsigned int)ns;
+    // With at least one row block per SM, whole row blocks are dealt out: no CTA shares a row block,
+    // so nothing is exchanged between CTAs.  With fewer, the k range is split as well (stream-K).
+    // Measured on B200: the exchange costs about 5 us of serial latency, one SM alone streams about
+    // 45 GB/s; so the k range is only split when whole row blocks would leave most SMs idle for long.
+    const int align_mode = tuning_align();
+    bool whole_blocks = true;
+    {
+        const double block_bytes = (double)Cfg::R * (double)((WT == DT_FP4) ? p.K / 2 + p.K / 16 : p.K);
+        const double sms = (double)ws->sm_count;
+        const double rounds = (double)((p.n_row_blocks + ws->sm_count - 1) / ws->sm_count);
+        const double t_whole = rounds * block_bytes / 45e9;
+        const double t_split = 5e-6 + (double)p.n_row_blocks * block_bytes / (sms * 40e9);
+        whole_blocks = t_whole <= t_split || Cfg::MT > 1;    // large partial tiles make the exchange far dearer
+    }
+    if (align_mode >= 0) { whole_blocks = align_mode == 1; }
+    p.gran = whole_blocks ? p.n_kstages : 1u;
+    const unsigned long long groups = total / p.gran;
+    const unsigned int grid = (unsigned int)(groups < (unsigned long long)ws->sm_count ? groups : ws->sm_count);
+    if ((size_t)grid * 2 * Cfg::R * 8 * Cfg::MT * sizeof(float) > ws->partial_bytes || grid > ws->n_counters) { return -2; }
+
+    CUtensorMap tmW, tmS, tmX;
+    const unsigned long long kbytes = (WT == DT_FP4) ? p.K / 2 : p.K;
+    const unsigned long long ldw_bytes = (WT == DT_FP4) ? p.ldw / 2 : p.ldw;
+    bool ok = make_map(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.W, 64, p.N, kbytes / 64, ldw_bytes, Cfg::R, Cfg::SKS, false);
+    if (ok && WT == DT_FP4)
+    {
+        ok = make_map(&tmS, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.blk, 16, p.N, p.K / 256, p.ldw / 16, Cfg::R, Cfg::SKS / 2, false);
+    }
+    else { tmS = tmW; }
+    ok = ok && make_map(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.X, 64, p.M, p.K / 64, (unsigned long long)p.ldx * 2, Cfg::XB,
+                   Cfg::XSLABS, Cfg::XSWZ);
+    if (!ok)
+    {
+        static bool told = false;
+        if (!told)
+        {
+            told = true;
+            fprintf(stderr, "gemm_wq_bf16: tensor map encoding failed; using the plain kernel\n");
+        }
+        return -2;
+    }
+
+    const size_t smem = (size_t)Cfg::HEADER_BYTES + (size_t)ns * Cfg::STAGE_BYTES + Cfg::RED_BYTES;
+    auto kernel = gemv_wq_kernel<Cfg, SCALED>;
+    static bool attr_set[kMaxDevices] = {};    // per instantiation, per device
+    if (!attr_set[ws->device])
+    {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        {
+            report_launch("gemm_wq_bf16");
+            return 1;
+        }
+        attr_set[ws->device] = true;
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(Cfg::THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    count_launch();
+    if (cudaLaunchKernelEx(&cfg, kernel, tmW, tmS, tmX, p) != cudaSuccess)
+    {
+        report_launch("gemm_wq_bf16");
+        return 1;
+    }
+    return 0;
+}
+
+template <int WT, bool SCALED>
+static int launch_gemv(const GemvParams& p, const GemvScratch* ws, cudaStream_t stream, bool pdl)
+{
+    //                                                        WT MT RT WR WK SKS XB OCC
+    if (tuning_variant() == 1 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 1, 8, 32, 2, 1>, SCALED>(p, ws, stream, pdl); }
+    if (tuning_variant() == 3 && p.M <= 1) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 1, 8, 64, 1, 1>, SCALED>(p, ws, stream, pdl); }
+    if (tuning_variant() == 6 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 8, 8, 2, 1>, SCALED>(p, ws, stream, pdl); }
+    if (tuning_variant() == 7 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 1, 8, 16, 2, 1>, SCALED>(p, ws, stream, pdl); }
+    if (tuning_variant() == 8 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 1, 8, 32, 2, 1>, SCALED>(p, ws, stream, pdl); }
+    if (tuning_variant() == 4 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 8, 16, 2, 1>, SCALED>(p, ws, stream, pdl); }
+    if (tuning_variant() == 5 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 8, 32, 2, 1>, SCALED>(p, ws, stream, pdl); }
+    if (tuning_variant() == 2 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 1, 8, 16, 2, 2>, SCALED>(p, ws, stream, pdl); }
+    if (tuning_variant() == 9 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 7, 14, 2, 2>, SCALED>(p, ws, stream, pdl); }
+    if (tuning_variant() == 10 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 1, 7, 14, 2, 2>, SCALED>(p, ws, stream, pdl); }
+    if (p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 8, 32, 2, 1>, SCALED>(p, ws, stream, pdl); }
+    if (p.M <= 8) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 8, 16, 8, 1>, SCALED>(p, ws, stream, pdl); }
+    if (p.M <= 16) { return launch_gemv_cfg<GemvCfg<WT, 2, 2, 2, 4, 4, 16, 1>, SCALED>(p, ws, stream, pdl); }
+    return launch_gemv_cfg<GemvCfg<WT, 4, 2, 4, 2, 2, 32, 1>, SCALED>(p, ws, stream, pdl);
+}
+
+template <int WT>
+static int launch_plain(const GemvParams& p, cudaStream_t stream)
+{
+    const unsigned int grid = (p.N + 7) / 8;
+    linear_wq_plain_kernel<WT><<<grid, 256, 0, stream>>>(p);
+    count_launch();
+    return report_launch("gemm_wq_bf16");
+}
+
+enum
+{
+    PLAN_PLAIN = 0,
+    PLAN_DECODE = 1,
+    PLAN_PREFILL = 2
+};
+
+static inline bool al16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
+
+static int plan_for(int w_type, const void* W, const void* blk, const void* X, const void* Y, unsigned int N, unsigned int M,
+    unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m, unsigned int ldy_n)
+{
+    (void)Y;
+    (void)ldy_m;
+    (void)ldy_n;
+    if (N == 0 || M == 0 || K == 0) { return PLAN_PLAIN; }
+    if (!al16(W) || !al16(X) || (ldx % 8) != 0) { return PLAN_PLAIN; }
+    if (w_type == DT_FP4)
+    {
+        if (!blk || !al16(blk) || (K % 256) != 0 || (ldw % 256) != 0) { return PLAN_PLAIN; }
+    }
+    else
+    {
+        if ((K % 64) != 0 || (ldw % 16) != 0) { return PLAN_PLAIN; }
+    }
+    if (M <= 32) { return PLAN_DECODE; }
+    if (prefill_supported(w_type, N, M, K, ldw, ldx, ldy_m, ldy_n)) { return PLAN_PREFILL; }
+    return PLAN_PLAIN;
+}
+
+
+// The whole entry: argument checks done by the caller; picks the kernel and launches it on
+// `st`.  Returns the C-ABI code (0 ok, 1 CUDA error, -1 bad argument).
+static int run_linear_wq(const GemvScratch* ws, int w_type, const void* W, const void* blk_scales, float inv_scale, const void* X,
+    void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m,
+    unsigned int ldy_n, float alpha, float beta, cudaStream_t st, unsigned int flags, bool decode_only = false)
+{
+    GemvParams p;
+    memset(&p, 0, sizeof(p));
+    p.W = (const uint8_t*)W;
+    p.blk = (w_type == DT_FP4) ? (const uint8_t*)blk_scales : nullptr;
+    p.X = (const uint16_t*)X;
+    p.Y = (uint16_t*)Y;
+    p.partials = ws->partials;
+    p.counters = ws->counters;
+    p.status = ws->status;
+    p.N = N_out;
+    p.M = M_tokens;
+    p.K = K;
+    p.ldw = ldw;
+    p.ldx = ldx;
+    p.ldy_m = ldy_m;
+    p.ldy_n = ldy_n;
+    p.w_scale = inv_scale;
+    p.alpha = alpha;
+    p.beta = beta;
+    p.post_scale = 1.0f;
+    const bool pdl = (flags & 1u) != 0;
+
+    int plan = plan_for(w_type, W, blk_scales, X, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n);
+    if (decode_only && plan != PLAN_DECODE) { return -1; }
+    if (plan == PLAN_DECODE)
+    {
+        int r;
+        if (w_type == DT_FP4)
+        {
+            p.post_scale = 65536.0f;    // the FP4 dequantiser leaves 2^-16 in every weight
+            r = launch_gemv<DT_FP4, false>(p, ws, st, pdl);
+        }
+        else if (is_pow2_scale(inv_scale))
+        {
+            // A power-of-two multiplier commutes exactly with the BF16 rounding and the FP32 sums.
+            p.post_scale = inv_scale;
+            p.w_scale = 1.0f;
+            r = (w_type == DT_E5M2) ? launch_gemv<DT_E5M2, false>(p, ws, st, pdl) : launch_gemv<DT_E4M3, false>(p, ws, st, pdl);
+        }
+        else { r = (w_type == DT_E5M2) ? launch_gemv<DT_E5M2, true>(p, ws, st, pdl) : launch_gemv<DT_E4M3, true>(p, ws, st, pdl); }
+        if (r != -2) { return r; }
+        if (decode_only) { return -1; }
+        p.post_scale = 1.0f;
+        p.w_scale = inv_scale;
+        plan = PLAN_PLAIN;
+    }
+    if (plan == PLAN_PREFILL)
+    {
+        const int r = launch_prefill(w_type, p, ws->sm_count, ws->max_smem, st);
+        if (r != -2) { return r; }
+        plan = PLAN_PLAIN;
+    }
+    switch (w_type)
+    {
+    case DT_E4M3: return launch_plain<DT_E4M3>(p, st);
+    case DT_E5M2: return launch_plain<DT_E5M2>(p, st);
+    default: return launch_plain<DT_FP4>(p, st);
+    }
+}
+
+}    // namespace b200
