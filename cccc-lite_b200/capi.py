@@ -16,6 +16,7 @@ FLOAT, DOUBLE, HALF, BFLOAT16, FP8_E4M3, FP8_E5M2, FP4_E2M1 = range(7)
 
 PLAN_PLAIN, PLAN_DECODE, PLAN_PREFILL = 0, 1, 2
 FLAG_PDL = 1
+FLAG_CHECKED = 2  # cuda_gemm_wq_bf16_static only
 
 _vp, _u, _f, _i = C.c_void_p, C.c_uint, C.c_float, C.c_int
 
@@ -27,6 +28,7 @@ SYMBOLS = {
     "cuda_check_error": (_i, [C.c_char_p]),
     "cuda_clear_last_error": (None, []),
     "cuda_gemm_wq_bf16": (_i, [_i, _vp, _vp, _f, _vp, _vp, _u, _u, _u, _u, _u, _u, _u, _f, _f, _vp, _u]),
+    "cuda_gemm_wq_bf16_static": (_i, [_i, _vp, _vp, _f, _vp, _vp, _u, _u, _u, _u, _u, _u, _u, _f, _f, _vp, _u]),
     "cuda_gemm_wq_bf16_plan": (_i, [_i, _vp, _vp, _vp, _vp, _u, _u, _u, _u, _u, _u, _u]),
     "cuda_b200_launch_count": (C.c_ulonglong, []),
     "cuda_b200_version": (C.c_char_p, []),
@@ -85,6 +87,19 @@ def gemm_wq_bf16(w_type: int, W, blk, inv_scale: float, X, Y, N: int, M: int, K:
     return lib().cuda_gemm_wq_bf16(w_type, _ptr(W), _ptr(blk), inv_scale, _ptr(X), _ptr(Y), N, M, K,
                                    K if ldw is None else ldw, K if ldx is None else ldx,
                                    N if ldy_m is None else ldy_m, ldy_n, alpha, beta, stream, flags)
+
+
+def gemm_wq_bf16_static(w_type: int, W, blk, inv_scale: float, X, Y, N: int, M: int, K: int, *, ldw: int | None = None,
+                        ldx: int | None = None, ldy_m: int | None = None, ldy_n: int = 1, alpha: float = 1.0,
+                        beta: float = 0.0, stream: int | None = None, flags: int = 0) -> int:
+    """The allocation-free variant (fixed scratch inside the library, M <= 8); same arguments."""
+    if stream is None:
+        import torch
+
+        stream = torch.cuda.current_stream().cuda_stream
+    return lib().cuda_gemm_wq_bf16_static(w_type, _ptr(W), _ptr(blk), inv_scale, _ptr(X), _ptr(Y), N, M, K,
+                                          K if ldw is None else ldw, K if ldx is None else ldx,
+                                          N if ldy_m is None else ldy_m, ldy_n, alpha, beta, stream, flags)
 
 
 def gemm_wq_bf16_plan(w_type: int, W, blk, X, Y, N: int, M: int, K: int, *, ldw=None, ldx=None, ldy_m=None,

@@ -80,6 +80,28 @@ C_EXPORT int cuda_gemm_wq_bf16(int w_type, const void* W, const void* blk_scales
     void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx,
     unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta, void* stream, unsigned int flags);
 
+/* No counterpart in the reference.  The same linear as cuda_gemm_wq_bf16 for callers that cannot
+ * allocate when they issue it: hosts that plan every byte of device memory up front (or have already
+ * committed all of it) and hand the library no allocator, and latency-critical loops that may not take
+ * the allocator's locks or the device-wide synchronisation a cudaMalloc/cudaFree can imply.  cuda_gemm_wq_bf16 allocates its per-device workspace on first use; this entry point
+ * calls no cudaMalloc/cudaFree and no allocating library routine: its scratch (FP32 partial tiles of
+ * the split-k schedule, arrival counters, a status word) is a fixed 520 KB device array inside the
+ * library, held by every GPU that loads it until the process ends.
+ * Limits: M_tokens <= 8, a device with at most 256 SMs, and operands the TMA kernel takes (16-byte
+ * aligned pointers, K % 64 == 0, ldw % 16 == 0, ldx % 8 == 0; FP4: block scales given, K % 256 == 0,
+ * ldw % 256 == 0).  Anything else returns -1 with a line on stderr saying which limit was hit.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and the
+ * device's attributes; make that first call outside any stream capture.
+ * All calls on a device share the one array: order them on one stream.  Two calls that overlap on the
+ * GPU (different streams, or the same buffers from two threads) race on it.  The array keeps the
+ * previous call's contents; the counters that must start at zero are cleared on the stream by every call.
+ * Arguments and result as cuda_gemm_wq_bf16.  flags bit 0: programmatic dependent launch, as there.
+ * flags bit 1: checked call - synchronise the stream after the launch and return 1 if one of the
+ * kernel's bounded waits ran out (without it such a failure is not reported by this entry point). */
+C_EXPORT int cuda_gemm_wq_bf16_static(int w_type, const void* W, const void* blk_scales, float inv_scale, const void* X,
+    void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx,
+    unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta, void* stream, unsigned int flags);
+
 /* Tuning/diagnostic: returns which kernel cuda_gemm_wq_bf16 would pick for a shape
  * (0 = plain kernel, 1 = decode GEMV (M<=32), 2 = prefill tcgen05 GEMM) without launching. */
 C_EXPORT int cuda_gemm_wq_bf16_plan(int w_type, const void* W, const void* blk_scales, const void* X,
