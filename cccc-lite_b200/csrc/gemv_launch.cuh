@@ -5,6 +5,7 @@
 
 #include "common.cuh"
 #include "gemv_decode.cuh"
+#include "tensor_map.cuh"
 #include "gemm_prefill.cuh"
 
 #include <cmath>
@@ -37,49 +38,6 @@ static bool is_pow2_scale(float s)
     int e = 0;
     const float m = std::frexp(s, &e);
     return m == 0.5f && e >= -39 && e <= 41;    // 2^-40 .. 2^40
-}
-
-// ---- tensor maps -------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-    CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn()
-{
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried)
-    {
-        tried = true;
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess
-            && q == cudaDriverEntryPointSuccess)
-        {
-            fn = (EncodeTiledFn)sym;
-        }
-        else { cudaGetLastError(); }
-    }
-    return fn;
-}
-
-// A 3-D view (inner run, rows, runs along k) of a row-major [rows, k] operand: dimension 1 walks
-// the rows (stride = the leading dimension), dimension 2 walks the 'inner'-sized runs of one row.
-// A box {inner, box_rows, box_runs} therefore lands in shared memory as [run][row][inner].
-static bool make_map(CUtensorMap* map, CUtensorMapDataType dt, unsigned int elem_bytes, const void* base, unsigned int inner,
-    unsigned long long rows, unsigned long long runs, unsigned long long row_stride_bytes, unsigned int box_rows,
-    unsigned int box_runs, bool swizzle128)
-{
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (!fn) { return false; }
-    const cuuint64_t gdim[3] = { inner, rows, runs };
-    const cuuint64_t gstride[2] = { row_stride_bytes, (cuuint64_t)inner * elem_bytes };
-    const cuuint32_t box[3] = { inner, box_rows, box_runs };
-    const cuuint32_t estr[3] = { 1, 1, 1 };
-    const CUresult r = fn(map, dt, 3, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
 }
 
 static int tuning_align()
@@ -239,6 +197,11 @@ static int plan_for(int w_type, const void* W, const void* blk, const void* X, c
     (void)ldy_n;
     if (N == 0 || M == 0 || K == 0) { return PLAN_PLAIN; }
     if (!al16(W) || !al16(X) || (ldx % 8) != 0) { return PLAN_PLAIN; }
+    if (M > 32)
+    {
+        if (w_type == DT_FP4 && !blk) { return PLAN_PLAIN; }
+        return prefill_supported(w_type, N, M, K, ldw, ldx, ldy_m, ldy_n) ? PLAN_PREFILL : PLAN_PLAIN;
+    }
     if (w_type == DT_FP4)
     {
         if (!blk || !al16(blk) || (K % 256) != 0 || (ldw % 256) != 0) { return PLAN_PLAIN; }
@@ -307,7 +270,7 @@ static int run_linear_wq(const GemvScratch* ws, int w_type, const void* W, const
     }
     if (plan == PLAN_PREFILL)
     {
-        const int r = launch_prefill(w_type, p, ws->sm_count, ws->max_smem, st);
+        const int r = launch_prefill(w_type, p, ws->device, st);
         if (r != -2) { return r; }
         plan = PLAN_PLAIN;
     }
