@@ -36,10 +36,14 @@ LLAMA = dict(HIDDEN=4096, QDIM=4096, KVDIM=1024, FFN=14336, VOCAB=128256, LAYERS
 W_STD = 0.02
 
 
-def model_dims(wtype: str):
+def model_dims(wtype: str, layers: int | None = None):
     if wtype == "fp4":
-        return LLAMA["HIDDEN"], LLAMA["QDIM"], LLAMA["KVDIM"], LLAMA["FFN"], LLAMA["VOCAB"], LLAMA["LAYERS"]
-    return HIDDEN, QDIM, KVDIM, FFN, VOCAB, LAYERS
+        d = [LLAMA["HIDDEN"], LLAMA["QDIM"], LLAMA["KVDIM"], LLAMA["FFN"], LLAMA["VOCAB"], LLAMA["LAYERS"]]
+    else:
+        d = [HIDDEN, QDIM, KVDIM, FFN, VOCAB, LAYERS]
+    if layers:
+        d[5] = layers
+    return tuple(d)
 
 
 def layer_linears(dims):
@@ -214,7 +218,7 @@ def gpu_arm(args):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     M = args.tokens
-    dims = model_dims(args.wtype)
+    dims = model_dims(args.wtype, args.layers)
     wt, lin, bufs = build_model(torch, capi, dims, M, args.wtype, rank, world, dev)
     # the layer chain: "down" of a layer is the next layer's "x"
     bufs["down"] = bufs["x"]
@@ -324,12 +328,56 @@ def gpu_arm(args):
                      "avg_launch_us": round(ms_per_step * 1e3 / launches_per_step, 3)},
         "clocks": clocks,
     }
+    if rank == 0 and world == 1 and not args.no_prefill:
+        del graph
+        out["prefill"] = prefill_probe(torch, capi, dims, args.wtype, dev, peaks)
+        out["gpu_launches"] += out["prefill"]["launches"]
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline(args, budget_s=12.0)
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def prefill_probe(torch, capi, dims, wtype, dev, peaks):
+    """BASELINE config 4 in brief: M=2048 tokens through one layer's seven linears (tcgen05 kernel),
+    timed with CUDA events; reported next to the decode line as TFLOP/s of 2*M*N*K."""
+    M = 2048
+    wt = capi.FP4_E2M1 if wtype == "fp4" else capi.FP8_E5M2
+    g = torch.Generator(device=dev).manual_seed(7)
+    mats = []
+    flops = 0.0
+    for name, N, K, _, _ in layer_linears(dims):
+        nb = N * K // 2 if wtype == "fp4" else N * K
+        W = torch.randint(0, 120, (nb,), dtype=torch.uint8, device=dev, generator=g)
+        S = torch.randint(1, 8, (N * K // 16,), dtype=torch.uint8, device=dev, generator=g) if wtype == "fp4" else None
+        X = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+        Y = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+        mats.append((N, K, W, S, X, Y))
+        flops += 2.0 * M * N * K
+
+    def layer():
+        for N, K, W, S, X, Y in mats:
+            if capi.gemm_wq_bf16(wt, W, S, 0.37, X, Y, N, M, K) != 0:
+                raise RuntimeError("prefill linear failed")
+
+    for _ in range(3):
+        layer()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 10
+    e0.record()
+    for _ in range(reps):
+        layer()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / reps
+    tf = flops / ms / 1e9
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    return {"workload": "one layer's seven linears, M=2048 tokens", "ms_per_layer": round(ms, 4), "tflops": round(tf, 1),
+            "peak_tflops": peak, "frac": round(tf / peak, 4), "peak_source": "measured" if "bf16_tflops" in peaks else "fallback",
+            "kernel": "gemm_wq_prefill_kernel (tcgen05)", "launches": 7 * (reps + 3)}
 
 
 # ---- the CPU arm -------------------------------------------------------------------------------------
@@ -340,7 +388,7 @@ def cpu_baseline(args, budget_s: float):
 
     from oracle import oracle as O
 
-    dims = model_dims(args.wtype)
+    dims = model_dims(args.wtype, args.layers)
     M = args.tokens
     wt = O.FP4_E2M1 if args.wtype == "fp4" else O.FP8_E5M2
     rng = np.random.default_rng(0)
@@ -374,7 +422,7 @@ def reference_arm(args):
     if rank != 0:
         return
     world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
-    dims = model_dims(args.wtype)
+    dims = model_dims(args.wtype, args.layers)
     M = args.tokens
     # each "step" is a bounded sample: one layer's seven linears
     per_step_budget = 1.0
@@ -413,6 +461,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (small cases for profiling)")
+    ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
