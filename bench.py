@@ -167,12 +167,15 @@ def build_model(torch, capi, dims, M, wtype, rank, world, dev):
         "down": torch.zeros(M, hidden, dtype=torch.bfloat16, device=dev),
         "logits": torch.zeros(M, vocab // world, dtype=torch.bfloat16, device=dev),
         "logits_all": torch.zeros(world, M, vocab // world, dtype=torch.bfloat16, device=dev),
+        "partial": torch.zeros(M, hidden, dtype=torch.float32, device=dev),
     }
     return wt, lin, bufs
 
 
 def run_step(torch, dist, capi, wt, lin, bufs, M, world, flags):
-    """One token's linears.  alpha keeps activation magnitudes steady through the random layers."""
+    """One token's linears.  alpha keeps activation magnitudes steady through the random layers.
+    With more than one rank, row-parallel linears (o, down) write FP32 partial sums, which are
+    all-reduced and rounded to BF16 once; the logits are all-gathered."""
     import math
 
     n_launch = 0
@@ -181,19 +184,33 @@ def run_step(torch, dist, capi, wt, lin, bufs, M, world, flags):
         src = bufs[L["src"]] if name != "lm_head" else bufs["x"]
         dst = bufs["logits"] if name == "lm_head" else bufs[name]
         alpha = 1.0 / (W_STD * math.sqrt(L["fullK"]))
-        if wt == capi.FP4_E2M1:
-            alpha = 1.0 / (0.02 * math.sqrt(L["fullK"]))
-        rc = capi.gemm_wq_bf16(wt, L["W"], L["S"], L["inv"], src, dst, L["N"], M, L["K"], alpha=alpha, flags=flags)
+        row_parallel = world > 1 and L["kind"] == "row"
+        out = bufs["partial"] if row_parallel else dst
+        rc = capi.gemm_wq_bf16(wt, L["W"], L["S"], L["inv"], src, out, L["N"], M, L["K"], alpha=alpha,
+                               flags=flags | (capi.FLAG_OUT_F32 if row_parallel else 0))
         if rc != 0:
             raise RuntimeError(f"cuda_gemm_wq_bf16 failed on {name}: {rc}")
         n_launch += 1
-        if world > 1 and L["kind"] == "row":
-            dist.all_reduce(dst)
-        if name == "down":
-            bufs["x"].copy_(dst) if False else None  # next layer reads "down" through the alias below
+        if row_parallel:
+            dist.all_reduce(out)
+            dst.copy_(out)
     if world > 1:
         dist.all_gather_into_tensor(bufs["logits_all"], bufs["logits"])
     return n_launch
+
+
+def start_watchdog(seconds: float):
+    """A benchmark must never hang a GPU box: if the process is still alive after `seconds`, say so
+    on stdout and leave."""
+    def fire():
+        print(json.dumps({"error": f"bench.py watchdog: no result after {seconds:.0f} s", "rank": os.environ.get("RANK", "0")}),
+              flush=True)
+        os._exit(3)
+
+    t = threading.Timer(seconds, fire)
+    t.daemon = True
+    t.start()
+    return t
 
 
 def gpu_arm(args):
@@ -203,6 +220,7 @@ def gpu_arm(args):
 
     capi = load_package().capi
     capi.lib()
+    watchdog = start_watchdog(args.watchdog)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -213,8 +231,10 @@ def gpu_arm(args):
         import torch.distributed as dist_mod
 
         dist = dist_mod
+        import datetime
+
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=120))
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     M = args.tokens
@@ -250,7 +270,7 @@ def gpu_arm(args):
         if not args.no_graph:
             graph = torch.cuda.CUDAGraph()
             bufs["x"].copy_(x_host, non_blocking=True)
-            with torch.cuda.graph(graph, stream=stream):
+            with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
                 run_step(torch, dist, capi, wt, lin, bufs, M, world, flags)
 
         def one_step():
@@ -463,6 +483,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (small cases for profiling)")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--watchdog", type=float, default=420.0, help="seconds after which a stuck run exits by itself")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -17,6 +17,7 @@ FLOAT, DOUBLE, HALF, BFLOAT16, FP8_E4M3, FP8_E5M2, FP4_E2M1 = range(7)
 PLAN_PLAIN, PLAN_DECODE, PLAN_PREFILL = 0, 1, 2
 FLAG_PDL = 1
 FLAG_CHECKED = 2  # cuda_gemm_wq_bf16_static only
+FLAG_OUT_F32 = 4  # Y is float32 (partial sums of a row-parallel shard)
 
 _vp, _u, _f, _i = C.c_void_p, C.c_uint, C.c_float, C.c_int
 

@@ -50,6 +50,7 @@ struct PrefillParams
     unsigned int N, M, K, ldw;
     long long ldy_m, ldy_n;
     float w_scale, alpha, beta, post_scale;
+    unsigned int out_f32;
 };
 
 // ---- tcgen05 wrappers --------------------------------------------------------------------------------
@@ -368,10 +369,20 @@ __global__ void __launch_bounds__(PF_THREADS, 2) gemm_wq_prefill_kernel(const __
                         const unsigned int m = m0 + c0 + j;
                         if (c0 + j < tile_tokens)
                         {
-                            uint16_t* y = p.Y + (long long)m * p.ldy_m + (long long)n * p.ldy_n;
+                            const long long yi = (long long)m * p.ldy_m + (long long)n * p.ldy_n;
                             float o = p.alpha * (__uint_as_float(r[j]) * p.post_scale);
-                            if (p.beta != 0.f) { o += p.beta * bf16_bits_to_float(*y); }
-                            *y = __bfloat16_as_ushort(__float2bfloat16_rn(o));
+                            if (p.out_f32)
+                            {
+                                float* y = reinterpret_cast<float*>(p.Y) + yi;
+                                if (p.beta != 0.f) { o += p.beta * *y; }
+                                *y = o;
+                            }
+                            else
+                            {
+                                uint16_t* y = p.Y + yi;
+                                if (p.beta != 0.f) { o += p.beta * bf16_bits_to_float(*y); }
+                                *y = __bfloat16_as_ushort(__float2bfloat16_rn(o));
+                            }
                         }
                     }
                 }
@@ -438,6 +449,7 @@ static int launch_prefill(int w_type, const GemvParams& p, int device, cudaStrea
     pp.alpha = p.alpha;
     pp.beta = p.beta;
     pp.post_scale = 1.0f;
+    pp.out_f32 = p.out_f32;
     if (w_type == DT_FP4) { return launch_prefill_t<DT_FP4, false>(tmX, pp, device, stream); }
     int e = 0;
     const bool pow2 = p.w_scale > 0.f && !std::isinf(p.w_scale) && std::frexp(p.w_scale, &e) == 0.5f && e >= -39 && e <= 41;

@@ -43,6 +43,7 @@ struct GemvParams
     float w_scale;              // multiplier applied to each decoded weight before BF16 rounding
     float alpha, beta;
     float post_scale;           // exact power of two folded out of the weights (applied with alpha)
+    unsigned int out_f32;       // 1: Y holds float32 (partial sums of a row-parallel shard), 0: BF16
     unsigned int n_row_blocks, n_kstages, total_items;
     unsigned int gran;          // items are dealt to CTAs in groups of `gran`: 1 = stream-K, n_kstages = whole row blocks
     unsigned int n_stages;      // ring depth
@@ -573,10 +574,20 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
             const unsigned int n = n0 + r;
             if (n < p.N)
             {
-                uint16_t* y = p.Y + (long long)m * p.ldy_m + (long long)n * p.ldy_n;
+                const long long yi = (long long)m * p.ldy_m + (long long)n * p.ldy_n;
                 float o = p.alpha * (v * p.post_scale);
-                if (p.beta != 0.f) { o += p.beta * bf16_bits_to_float(*y); }
-                *y = __bfloat16_as_ushort(__float2bfloat16_rn(o));
+                if (p.out_f32)
+                {
+                    float* y = reinterpret_cast<float*>(p.Y) + yi;
+                    if (p.beta != 0.f) { o += p.beta * *y; }
+                    *y = o;
+                }
+                else
+                {
+                    uint16_t* y = p.Y + yi;
+                    if (p.beta != 0.f) { o += p.beta * bf16_bits_to_float(*y); }
+                    *y = __bfloat16_as_ushort(__float2bfloat16_rn(o));
+                }
             }
         };
         if (full)
@@ -675,10 +686,20 @@ __global__ void __launch_bounds__(256) linear_wq_plain_kernel(const GemvParams p
             for (int o = 16; o > 0; o >>= 1) { v += __shfl_xor_sync(0xFFFFFFFFu, v, o); }
             if (lane == 0)
             {
-                uint16_t* y = p.Y + (long long)(m0 + mm) * p.ldy_m + (long long)n * p.ldy_n;
+                const long long yi = (long long)(m0 + mm) * p.ldy_m + (long long)n * p.ldy_n;
                 float o = p.alpha * v;
-                if (p.beta != 0.f) { o += p.beta * bf16_bits_to_float(*y); }
-                *y = __bfloat16_as_ushort(__float2bfloat16_rn(o));
+                if (p.out_f32)
+                {
+                    float* y = reinterpret_cast<float*>(p.Y) + yi;
+                    if (p.beta != 0.f) { o += p.beta * *y; }
+                    *y = o;
+                }
+                else
+                {
+                    uint16_t* y = p.Y + yi;
+                    if (p.beta != 0.f) { o += p.beta * bf16_bits_to_float(*y); }
+                    *y = __bfloat16_as_ushort(__float2bfloat16_rn(o));
+                }
             }
         }
     }

@@ -242,6 +242,7 @@ static int run_linear_wq(const GemvScratch* ws, int w_type, const void* W, const
     p.alpha = alpha;
     p.beta = beta;
     p.post_scale = 1.0f;
+    p.out_f32 = (flags & 4u) ? 1u : 0u;
     const bool pdl = (flags & 1u) != 0;
 
     int plan = plan_for(w_type, W, blk_scales, X, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n);

@@ -75,7 +75,9 @@ C_EXPORT void cuda_clear_last_error(void);
  * (they share the workspace), as the reference's single `Cublas` instance requires too.
  * flags: bit 0 = launch with programmatic dependent launch so that this call's weight prefetch
  * overlaps the tail of the previous kernel on the stream (X, Y are only touched after that
- * kernel has finished). */
+ * kernel has finished).  bit 2 = Y holds float32 instead of BF16 (same strides, in elements): the
+ * unrounded result, which is what a row-parallel (K-split) shard hands to the all-reduce so that
+ * the sum over shards is rounded to BF16 once. */
 C_EXPORT int cuda_gemm_wq_bf16(int w_type, const void* W, const void* blk_scales, float inv_scale, const void* X,
     void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx,
     unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta, void* stream, unsigned int flags);

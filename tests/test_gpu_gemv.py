@@ -196,3 +196,23 @@ def test_full_size_lm_head_rows_against_oracle():
     assert c.convert(Wt, c.FP8_E5M2, wd, c.BFLOAT16, N * K, 1.0) == 0
     ref = (wd.view(N, K).float() @ dX.view(torch.bfloat16).float().view(K, 1)).view(-1).cpu().numpy()
     assert_close(Y.reshape(-1), ref, "lm_head all rows")
+
+
+@pytest.mark.parametrize("wt", WTS)
+@pytest.mark.parametrize("N,K,M", [(640, 1024, 1), (96, 8192, 5), (200, 250 + 6, 3), (256, 512, 70)])
+def test_float32_output_flag(wt, N, K, M):
+    """flags bit 2: Y is float32 (what a row-parallel shard hands to the all-reduce)."""
+    import torch
+
+    c = capi()
+    if wt == O.FP4_E2M1 and K % 16:
+        pytest.skip("FP4 block scales need K % 16 == 0")
+    W, blk, inv, X = O.make_inputs(wt, N, K, M, seed=3, scaled=True)
+    dW, dX = to_dev(W), to_dev(X)
+    dB = to_dev(blk) if blk is not None else None
+    y = torch.full((M, N), 7.0, dtype=torch.float32, device="cuda")
+    assert c.gemm_wq_bf16(wt, dW, dB, inv, dX, y, N, M, K, alpha=0.5, beta=2.0, flags=c.FLAG_OUT_F32) == 0
+    assert c.check_error("f32") == 0
+    _, y32 = O.linear_wq_bf16(wt, W, blk, inv, X, N, M, K)
+    got = (y.cpu().numpy() - 14.0) * 2.0
+    assert np.allclose(got, y32, rtol=2e-4, atol=2e-4 * float(np.sqrt(np.mean(y32.astype(np.float64) ** 2))))

@@ -1,0 +1,79 @@
+"""Tensor-parallel linears on 2 GPUs (NCCL): each rank runs its shard through the C-ABI, shards
+are combined with all-gather / all-reduce, and the result must equal the 1-GPU result within the
+stated tolerance (max relative error 1e-2, cosine >= 0.9999).  Needs at least two GPUs."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+from __graft_entry__ import ROOT
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import importlib
+
+        from __graft_entry__ import load_package
+        from oracle import oracle as O
+        from tests._util import rel_cos
+
+        capi = load_package().capi
+        T = importlib.import_module("cccc_lite_b200.tp")
+        results = []
+        for wt in (O.FP8_E5M2, O.FP4_E2M1):
+            for kind, N, K in (("col", 1024, 4096), ("row", 4096, 2048), ("col", 4096, 1024)):
+                for M in (1, 8):
+                    W, blk, inv, X = O.make_inputs(wt, N, K, M, seed=N + K + M, scaled=True)
+                    s = T.make_shard(kind, N, K, world, rank, wt)
+                    Ws, bs = T.slice_weight(W, blk, s, N, K, wt)
+                    Xs = T.slice_activation(X.reshape(M, K), s)
+                    dW = torch.from_numpy(Ws).cuda()
+                    dB = torch.from_numpy(bs).cuda() if bs is not None else None
+                    dX = torch.from_numpy(Xs.view(np.int16)).cuda()
+                    # row-parallel shards hand FP32 partial sums to the all-reduce (rounded to BF16 once, after)
+                    f32 = kind == "row"
+                    part = torch.zeros(M, s.N, dtype=torch.float32 if f32 else torch.bfloat16, device="cuda")
+                    assert capi.gemm_wq_bf16(wt, dW, dB, inv, dX, part, s.N, M, s.K, flags=capi.FLAG_OUT_F32 if f32 else 0) == 0
+                    assert capi.check_error("tp") == 0
+                    full = T.combine(kind, part, dist, world).to(torch.bfloat16)
+                    _, ref = O.linear_wq_bf16(wt, W, blk, inv, X, N, M, K)
+                    rel, cos = rel_cos(full.float().cpu().numpy(), ref)
+                    results.append((wt, kind, N, K, M, rel <= 1e-2 and cos >= 0.9999 and tuple(full.shape) == (M, N), rel, cos))
+        q.put((rank, results))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_shards_match_unsharded():
+    import torch
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, results in out:
+        bad = [r for r in results if not r[5]]
+        assert not bad, (rank, bad)
