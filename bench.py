@@ -349,15 +349,23 @@ def gpu_arm(args):
         "clocks": clocks,
     }
     if rank == 0 and world == 1 and not args.no_prefill:
-        del graph
+        graph = None
         out["prefill"] = prefill_probe(torch, capi, dims, args.wtype, dev, peaks)
         out["gpu_launches"] += out["prefill"]["launches"]
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline(args, budget_s=12.0)
         print(json.dumps(out), flush=True)
+    watchdog.cancel()
     if world > 1:
-        dist.destroy_process_group()
+        # Leave in an orderly way but without tearing NCCL down under a captured graph, which has
+        # been seen to block: drop the graph, drain the device, meet the other ranks, exit.
+        graph = None
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def prefill_probe(torch, capi, dims, wtype, dev, peaks):

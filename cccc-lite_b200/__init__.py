@@ -5,5 +5,5 @@ The directory name carries a hyphen, so it is loaded by path under the module na
 in the CUDA library (csrc/); this package binds its C-ABI (capi) and, for the benchmark and the
 tests, drives it with torch tensors that only hold device memory.
 """
-from . import capi  # noqa: F401
+from . import capi, hostapi  # noqa: F401
 from .capi import (BFLOAT16, DOUBLE, FLOAT, FP4_E2M1, FP8_E4M3, FP8_E5M2, HALF, lib)  # noqa: F401

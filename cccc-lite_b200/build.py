@@ -36,10 +36,34 @@ def stale() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+HOST_LIB = os.path.join(HERE, "libcccc-b200-host.so")
+HOST_DIR = os.path.join(CSRC, "host")
+
+
+def host_stale() -> bool:
+    if not os.path.exists(HOST_LIB):
+        return True
+    t = os.path.getmtime(HOST_LIB)
+    deps = glob.glob(os.path.join(HOST_DIR, "*")) + glob.glob(os.path.join(HERE, "..", "include", "*.h")) + [LIB]
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
+def build_host(force: bool = False) -> str:
+    """The C++ host layer (Matrix / Cublas / GpuControl mirror) on top of the CUDA library."""
+    if force or host_stale():
+        cuda = os.path.dirname(os.path.dirname(NVCC))
+        cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", f"-I{cuda}/include", "-o", HOST_LIB]
+        cmd += sorted(glob.glob(os.path.join(HOST_DIR, "*.cpp")))
+        cmd += [f"-L{HERE}", "-lcccc-cuda-b200", f"-L{cuda}/lib64", "-lcublas", "-lcudart", "-Wl,-rpath,$ORIGIN"]
+        subprocess.check_call(cmd)
+    return HOST_LIB
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     if force or stale():
         cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + sources()
         subprocess.check_call(cmd)
+    build_host(force)
     return LIB
 
 

@@ -27,3 +27,12 @@ def test_plan_needs_no_gpu():
     assert c.gemm_wq_bf16_plan(c.FP4_E2M1, 0x1000, 0x4000, 0x2000, 0x3000, 4096, 8, 4096) == c.PLAN_DECODE
     assert c.gemm_wq_bf16_plan(c.FP4_E2M1, 0x1000, None, 0x2000, 0x3000, 4096, 8, 4096) == c.PLAN_PLAIN
     assert c.gemm_wq_bf16_plan(3, 0x1000, None, 0x2000, 0x3000, 4096, 8, 4096) == -1
+
+
+def test_host_layer_library_loads():
+    from __graft_entry__ import load_package
+
+    h = load_package().hostapi
+    L = h.lib()
+    for name in h.SYMBOLS:
+        assert getattr(L, name) is not None
