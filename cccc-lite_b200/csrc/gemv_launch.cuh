@@ -167,8 +167,15 @@ static int launch_gemv(const GemvParams& p, const GemvScratch* ws, cudaStream_t 
     if (tuning_variant() == 10 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 1, 7, 14, 2, 2>, SCALED>(p, ws, stream, pdl); }
     if (p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 8, 32, 2, 1>, SCALED>(p, ws, stream, pdl); }
     if (p.M <= 8) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 8, 16, 8, 1>, SCALED>(p, ws, stream, pdl); }
-    if (p.M <= 16) { return launch_gemv_cfg<GemvCfg<WT, 2, 2, 2, 4, 4, 16, 1>, SCALED>(p, ws, stream, pdl); }
-    return launch_gemv_cfg<GemvCfg<WT, 4, 2, 4, 2, 2, 32, 1>, SCALED>(p, ws, stream, pdl);
+    if (tuning_variant() == 11)
+    {
+        if (p.M <= 16) { return launch_gemv_cfg<GemvCfg<WT, 2, 2, 2, 4, 4, 16, 1>, SCALED>(p, ws, stream, pdl); }
+        return launch_gemv_cfg<GemvCfg<WT, 4, 2, 4, 2, 2, 32, 1>, SCALED>(p, ws, stream, pdl);
+    }
+    // more tokens: more rows per CTA, so that the activation slice (re-read from L2 by every CTA) stays
+    // at or below the weight bytes it is multiplied with
+    if (p.M <= 16) { return launch_gemv_cfg<GemvCfg<WT, 2, 4, 1, 8, 16, 16, 1>, SCALED>(p, ws, stream, pdl); }
+    return launch_gemv_cfg<GemvCfg<WT, 4, 2, 2, 4, 8, 32, 1>, SCALED>(p, ws, stream, pdl);
 }
 
 template <int WT>
