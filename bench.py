@@ -172,15 +172,17 @@ def build_model(torch, capi, dims, M, wtype, rank, world, dev):
     return wt, lin, bufs
 
 
-def run_step(torch, dist, capi, wt, lin, bufs, M, world, flags):
+def run_step(torch, dist, capi, wt, lin, bufs, M, world, flags, prefetch=True):
     """One token's linears.  alpha keeps activation magnitudes steady through the random layers.
     With more than one rank, row-parallel linears (o, down) write FP32 partial sums, which are
     all-reduced and rounded to BF16 once; the logits are all-gathered."""
     import math
 
     n_launch = 0
-    for L in lin:
+    for idx, L in enumerate(lin):
         name = L["name"]
+        if prefetch and idx + 1 < len(lin):
+            capi.prefetch_next(lin[idx + 1]["W"])
         src = bufs[L["src"]] if name != "lm_head" else bufs["x"]
         dst = bufs["logits"] if name == "lm_head" else bufs[name]
         alpha = 1.0 / (W_STD * math.sqrt(L["fullK"]))
@@ -263,7 +265,7 @@ def gpu_arm(args):
 
     with torch.cuda.stream(stream):
         bufs["x"].copy_(x_host, non_blocking=True)
-        launches_per_step = run_step(torch, dist, capi, wt, lin, bufs, M, world, flags)  # first call: workspace
+        launches_per_step = run_step(torch, dist, capi, wt, lin, bufs, M, world, flags, not args.no_l2_prefetch)  # first call: workspace
         stream.synchronize()
         assert capi.check_error("bench warmup") == 0
         graph = None
@@ -271,13 +273,13 @@ def gpu_arm(args):
             graph = torch.cuda.CUDAGraph()
             bufs["x"].copy_(x_host, non_blocking=True)
             with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
-                run_step(torch, dist, capi, wt, lin, bufs, M, world, flags)
+                run_step(torch, dist, capi, wt, lin, bufs, M, world, flags, not args.no_l2_prefetch)
 
         def one_step():
             if graph is not None:
                 graph.replay()
             else:
-                run_step(torch, dist, capi, wt, lin, bufs, M, world, flags)
+                run_step(torch, dist, capi, wt, lin, bufs, M, world, flags, not args.no_l2_prefetch)
 
         # ---- device-resident arm ----
         for _ in range(args.warmup):
@@ -336,7 +338,7 @@ def gpu_arm(args):
             "workload": f"{'llama-3.1-8b w4a16' if args.wtype == 'fp4' else 'qwen3-8b w8a16'} decode linears: "
                         f"{dims[5]} layers x (q,k,v,o,gate,up,down) + lm_head, M={M}",
             "tokens": M, "bytes_per_step": bytes_per_step, "l2": "7.5 GB of distinct weights per step (> L2)",
-            "cuda_graph": graph is not None, "pdl": bool(args.pdl), "parallelism": f"tp{world}",
+            "cuda_graph": graph is not None, "pdl": bool(args.pdl), "l2_prefetch_next": not args.no_l2_prefetch, "parallelism": f"tp{world}",
             "tok_per_s": round(M / (ms_per_step * 1e-3), 1),
         },
         "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": x_host.numel() * 2,
@@ -489,6 +491,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-l2-prefetch", action="store_true", help="do not hint the next linear's weights into L2")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (small cases for profiling)")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--watchdog", type=float, default=420.0, help="seconds after which a stuck run exits by itself")

@@ -31,6 +31,7 @@ SYMBOLS = {
     "cuda_gemm_wq_bf16": (_i, [_i, _vp, _vp, _f, _vp, _vp, _u, _u, _u, _u, _u, _u, _u, _f, _f, _vp, _u]),
     "cuda_gemm_wq_bf16_static": (_i, [_i, _vp, _vp, _f, _vp, _vp, _u, _u, _u, _u, _u, _u, _u, _f, _f, _vp, _u]),
     "cuda_gemm_wq_bf16_plan": (_i, [_i, _vp, _vp, _vp, _vp, _u, _u, _u, _u, _u, _u, _u]),
+    "cuda_b200_prefetch_next": (_i, [_vp, C.c_ulonglong]),
     "cuda_b200_launch_count": (C.c_ulonglong, []),
     "cuda_b200_version": (C.c_char_p, []),
 }
@@ -108,6 +109,15 @@ def gemm_wq_bf16_plan(w_type: int, W, blk, X, Y, N: int, M: int, K: int, *, ldw=
     return lib().cuda_gemm_wq_bf16_plan(w_type, _ptr(W), _ptr(blk), _ptr(X), _ptr(Y), N, M, K,
                                         K if ldw is None else ldw, K if ldx is None else ldx,
                                         N if ldy_m is None else ldy_m, ldy_n)
+
+
+def prefetch_next(t, nbytes: int | None = None) -> int:
+    """Arm the one-shot L2 prefetch hint with a tensor (or raw pointer + byte count)."""
+    if t is None:
+        return lib().cuda_b200_prefetch_next(None, 0)
+    if nbytes is None:
+        nbytes = t.numel() * t.element_size()
+    return lib().cuda_b200_prefetch_next(_ptr(t), nbytes)
 
 
 def launch_count() -> int:

@@ -4,6 +4,7 @@
 #include "../../include/cccc_cuda_b200.h"
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 
 namespace b200
@@ -125,6 +126,22 @@ C_EXPORT int cuda_gemm_wq_bf16_plan(int w_type, const void* W, const void* blk_s
 {
     if (w_type != DT_E4M3 && w_type != DT_E5M2 && w_type != DT_FP4) { return -1; }
     return plan_for(w_type, W, blk_scales, X, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n);
+}
+
+C_EXPORT int cuda_b200_prefetch_next(const void* ptr, unsigned long long bytes)
+{
+    // Larger requests are cut: more than this does not stay in the 126 MB L2 next to the running linear.
+    static long long cap_mb = -1;
+    if (cap_mb < 0)
+    {
+        const char* e = getenv("CCCC_B200_PREFETCH_CAP_MB");
+        cap_mb = e ? atoll(e) : 64;
+    }
+    const unsigned long long cap = (unsigned long long)cap_mb << 20;
+    PrefetchHint& h = prefetch_hint();
+    h.ptr = ptr;
+    h.bytes = ptr ? (bytes < cap ? bytes : cap) : 0;
+    return 0;
 }
 
 C_EXPORT int cuda_check_error(const char* label) { return sync_and_report(label ? label : "cuda"); }

@@ -47,6 +47,11 @@ struct GemvParams
     unsigned int n_row_blocks, n_kstages, total_items;
     unsigned int gran;          // items are dealt to CTAs in groups of `gran`: 1 = stream-K, n_kstages = whole row blocks
     unsigned int n_stages;      // ring depth
+    const uint8_t* next_ptr;    // optional: bytes to bring into L2 while this linear streams (the next
+    unsigned long long next_bytes;    // linear's weights); 0 = none
+#ifdef B200_TRACE
+    unsigned long long* trace;  // debug builds only: 8 timestamps per CTA
+#endif
 };
 
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;    // 2 s
@@ -111,6 +116,25 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
                  "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
+}
+// L2 eviction policies: weights of the running linear are read once (evict first); lines prefetched
+// for the next linear should survive until it runs (evict last).
+__device__ __forceinline__ uint64_t l2_policy_evict_first()
+{
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last()
+{
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+// Bring [ptr, ptr+bytes) into L2 (no shared-memory destination).  16-byte aligned, multiple of 16.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* ptr, uint32_t bytes, uint64_t policy)
+{
+    asm volatile("cp.async.bulk.prefetch.L2.global.L2::cache_hint [%0], %1, %2;" ::"l"(ptr), "r"(bytes), "l"(policy) : "memory");
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -287,6 +311,15 @@ __host__ __device__ inline unsigned int cta_of_item(unsigned int i, unsigned int
 
 // 3-D tiled TMA load, completion counted on an mbarrier.  c0 is always 0 here (the inner extent is
 // one whole 16-byte-aligned run), so the 16-byte rule on the inner coordinate holds by construction.
+__device__ __forceinline__ void tma_load_3d_hint(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar,
+    uint64_t policy)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], "
+        "[%5], %6;" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar)
 {
     asm volatile(
@@ -318,6 +351,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const ItemRange items = cta_items(blockIdx.x, gridDim.x, p.total_items, p.gran);
     const unsigned int n_items = items.end - items.beg;
+#ifdef B200_TRACE
+#define B200_STAMP(slot) do { if (p.trace) { p.trace[(size_t)blockIdx.x * 8 + (slot)] = global_timer_ns(); } } while (0)
+#else
+#define B200_STAMP(slot) do { } while (0)
+#endif
+    if (threadIdx.x == 0) { B200_STAMP(0); }
 
     if (threadIdx.x == 0)
     {
@@ -337,14 +376,18 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
     {
         // =========================== producer: one elected lane ===========================
         if (lane != 0) { return; }
+        const uint64_t pol_stream = l2_policy_evict_first();
         auto issue_weights = [&](unsigned int it) {
             const unsigned int item = items.beg + it;
             const unsigned int rb = item / p.n_kstages, ks = item % p.n_kstages;
             const unsigned int s = it % NS;
             unsigned char* st = stages + (size_t)s * Cfg::STAGE_BYTES;
             mbar_expect_tx(full_bar + s, Cfg::W_BYTES + Cfg::S_BYTES);
-            tma_load_3d(st, &tmW, 0, (int)(rb * R), (int)(ks * Cfg::SKS), full_bar + s);
-            if (WT == DT_FP4) { tma_load_3d(st + Cfg::W_BYTES, &tmS, 0, (int)(rb * R), (int)(ks * (Cfg::SKS / 2)), full_bar + s); }
+            tma_load_3d_hint(st, &tmW, 0, (int)(rb * R), (int)(ks * Cfg::SKS), full_bar + s, pol_stream);
+            if (WT == DT_FP4)
+            {
+                tma_load_3d_hint(st + Cfg::W_BYTES, &tmS, 0, (int)(rb * R), (int)(ks * (Cfg::SKS / 2)), full_bar + s, pol_stream);
+            }
         };
         auto issue_acts = [&](unsigned int it) {
             const unsigned int item = items.beg + it;
@@ -358,8 +401,21 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
         // Weights do not depend on the previous kernel of the stream: prefetch the first ring of
         // stages before waiting for it; activations only after.
         const unsigned int pre = min(NS, n_items);
+        B200_STAMP(1);
         for (unsigned int it = 0; it < pre; it++) { issue_weights(it); }
+        B200_STAMP(2);
+        if (p.next_bytes != 0)
+        {
+            // This CTA's share of the next linear's weights goes to L2 now, behind its own first
+            // stages: HBM then keeps streaming through this kernel's tail and the next one's start.
+            const unsigned long long per = ((p.next_bytes / gridDim.x) + 15ull) & ~15ull;
+            unsigned long long off = (unsigned long long)blockIdx.x * per;
+            const unsigned long long end = min(off + per, p.next_bytes & ~15ull);
+            const uint64_t pol_keep = l2_policy_evict_last();
+            for (; off < end; off += 32768ull) { bulk_prefetch_l2(p.next_ptr + off, (uint32_t)min(32768ull, end - off), pol_keep); }
+        }
         pdl_wait();
+        B200_STAMP(3);
         for (unsigned int it = 0; it < pre; it++) { issue_acts(it); }
         bool ok = true;
         unsigned int issued = pre;
@@ -433,6 +489,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
                 }
             }
             if (!ok) { continue; }
+            if (it == 0 && threadIdx.x == 0) { B200_STAMP(4); }
             const unsigned int ks = ks0 + j;
             const unsigned int kval = min((unsigned int)Cfg::SKE, p.K - ks * Cfg::SKE);
             const unsigned int nsteps = kval / Cfg::KSTEP;    // beyond K the TMA fills zeros; skip them
@@ -550,6 +607,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
         }
 
         // ---- end of the segment: combine the k-split warps, then write or hand over ----
+        if (it >= n_items && threadIdx.x == 0) { B200_STAMP(5); }
         float* myred = red + wk * TILE;
 #pragma unroll
         for (int rt = 0; rt < RT; rt++)
@@ -649,6 +707,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
         }
         consumer_bar_sync<CT>();    // `red` and sh_flags[1] are reused by the next segment
     }
+    if (threadIdx.x == 0) { B200_STAMP(6); }
 }
 
 // ---- plain kernel: any shape, stride or alignment ----------------------------------------------------

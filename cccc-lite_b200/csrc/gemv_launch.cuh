@@ -40,6 +40,25 @@ static bool is_pow2_scale(float s)
     return m == 0.5f && e >= -39 && e <= 41;    // 2^-40 .. 2^40
 }
 
+#ifdef B200_TRACE
+// debug builds only: a caller-provided buffer receives 8 timestamps per CTA per launch
+static unsigned long long* g_trace_base = nullptr;
+static size_t g_trace_off = 0, g_trace_cap = 0;
+extern "C" __attribute__((visibility("default"))) void cuda_b200_trace_set(void* buf, size_t n_u64)
+{
+    g_trace_base = (unsigned long long*)buf;
+    g_trace_off = 0;
+    g_trace_cap = n_u64;
+}
+static unsigned long long* trace_next(unsigned int grid)
+{
+    if (!g_trace_base || g_trace_off + (size_t)grid * 8 > g_trace_cap) { return nullptr; }
+    unsigned long long* p = g_trace_base + g_trace_off;
+    g_trace_off += (size_t)grid * 8;
+    return p;
+}
+#endif
+
 static int tuning_align()
 {
     static int v = -2;
@@ -70,7 +89,7 @@ static int launch_gemv_cfg(GemvParams p, const GemvScratch* ws, cudaStream_t str
     const int budget = (Cfg::OCC == 2) ? (ws->smem_per_sm / 2 - 1024) : ws->max_smem;
     int ns = (budget - Cfg::HEADER_BYTES - Cfg::RED_BYTES) / Cfg::STAGE_BYTES;
     if (ns > Cfg::kMaxStages) { ns = Cfg::kMaxStages; }
-    if (ns < 2) { return -2; }
+    if (ns < 1) { return -2; }
     p.n_row_blocks = (p.N + Cfg::R - 1) / Cfg::R;
     p.n_kstages = (p.K + Cfg::SKE - 1) / Cfg::SKE;
     const unsigned long long total = (unsigned long long)p.n_row_blocks * p.n_kstages;
@@ -119,6 +138,9 @@ static int launch_gemv_cfg(GemvParams p, const GemvScratch* ws, cudaStream_t str
         return -2;
     }
 
+#ifdef B200_TRACE
+    p.trace = trace_next(grid);
+#endif
     const size_t smem = (size_t)Cfg::HEADER_BYTES + (size_t)ns * Cfg::STAGE_BYTES + Cfg::RED_BYTES;
     auto kernel = gemv_wq_kernel<Cfg, SCALED>;
     static bool attr_set[kMaxDevices] = {};    // per instantiation, per device
@@ -163,6 +185,8 @@ static int launch_gemv(const GemvParams& p, const GemvScratch* ws, cudaStream_t 
     if (tuning_variant() == 4 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 8, 16, 2, 1>, SCALED>(p, ws, stream, pdl); }
     if (tuning_variant() == 5 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 8, 32, 2, 1>, SCALED>(p, ws, stream, pdl); }
     if (tuning_variant() == 2 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 1, 8, 16, 2, 2>, SCALED>(p, ws, stream, pdl); }
+    if (tuning_variant() == 12 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 7, 32, 2, 2>, SCALED>(p, ws, stream, pdl); }
+    if (tuning_variant() == 13 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 7, 16, 2, 2>, SCALED>(p, ws, stream, pdl); }
     if (tuning_variant() == 9 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 7, 14, 2, 2>, SCALED>(p, ws, stream, pdl); }
     if (tuning_variant() == 10 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 1, 7, 14, 2, 2>, SCALED>(p, ws, stream, pdl); }
     if (p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 8, 32, 2, 1>, SCALED>(p, ws, stream, pdl); }
@@ -223,6 +247,19 @@ static int plan_for(int w_type, const void* W, const void* blk, const void* X, c
 }
 
 
+// One-shot hint armed by cuda_b200_prefetch_next and consumed by the next decode launch of this
+// host thread.
+struct PrefetchHint
+{
+    const void* ptr = nullptr;
+    unsigned long long bytes = 0;
+};
+inline PrefetchHint& prefetch_hint()
+{
+    static thread_local PrefetchHint h;
+    return h;
+}
+
 // The whole entry: argument checks done by the caller; picks the kernel and launches it on
 // `st`.  Returns the C-ABI code (0 ok, 1 CUDA error, -1 bad argument).
 static int run_linear_wq(const GemvScratch* ws, int w_type, const void* W, const void* blk_scales, float inv_scale, const void* X,
@@ -250,6 +287,15 @@ static int run_linear_wq(const GemvScratch* ws, int w_type, const void* W, const
     p.beta = beta;
     p.post_scale = 1.0f;
     p.out_f32 = (flags & 4u) ? 1u : 0u;
+    {
+        PrefetchHint& h = prefetch_hint();
+        if (h.ptr && (((uintptr_t)h.ptr) & 15u) == 0)
+        {
+            p.next_ptr = (const uint8_t*)h.ptr;
+            p.next_bytes = h.bytes;
+        }
+        h = PrefetchHint();    // one shot, whichever kernel this call takes
+    }
     const bool pdl = (flags & 1u) != 0;
 
     int plan = plan_for(w_type, W, blk_scales, X, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n);

@@ -55,3 +55,57 @@ HOST_EXPORT void cccc_host_gemm(void* g, int ta, int tb, int M, int N, int K, fl
     ((GpuControl*)g)->cublas_->gemm((MatrixTransType)ta, (MatrixTransType)tb, M, N, K, alpha, A, (DataType)typeA, lda, invA, B,
         (DataType)typeB, ldb, invB, beta, C, (DataType)typeC, ldc, 0.0f, (const uint8_t*)blkA, (const uint8_t*)blkB);
 }
+
+// ---- weight container ---------------------------------------------------------------------------------
+#include "bin_file.h"
+
+#include <cstring>
+#include <string>
+
+HOST_EXPORT void* cccc_host_bin_open(const char* path)
+{
+    auto* f = new BinFile();
+    if (!f->open(path))
+    {
+        delete f;
+        return nullptr;
+    }
+    return f;
+}
+HOST_EXPORT void cccc_host_bin_close(void* f) { delete (BinFile*)f; }
+HOST_EXPORT int cccc_host_bin_has(void* f, const char* key) { return ((BinFile*)f)->has(key) ? 1 : 0; }
+HOST_EXPORT unsigned long long cccc_host_bin_bytes_read(void* f) { return ((BinFile*)f)->bytesRead(); }
+// Loads one rank's shard into caller buffers (sizes from the shard shape); returns 0, or -1 with a
+// message in err (at most err_len bytes).  dims[0..2] = dtype, n, k.
+HOST_EXPORT int cccc_host_bin_load_shard(void* f, const char* name, int N, int K, char kind, int world, int rank, void* weights,
+    unsigned long long weights_cap, void* scales, unsigned long long scales_cap, float* quant_scale, int* dims, char* err,
+    int err_len)
+{
+    WeightShard s;
+    std::string e;
+    if (!loadWeightShard(*(BinFile*)f, name, N, K, kind, world, rank, &s, &e) || s.weights.size() > weights_cap
+        || s.block_scales.size() > scales_cap)
+    {
+        if (e.empty()) { e = "destination too small"; }
+        if (err && err_len > 0)
+        {
+            std::strncpy(err, e.c_str(), (size_t)err_len - 1);
+            err[err_len - 1] = '\0';
+        }
+        return -1;
+    }
+    std::memcpy(weights, s.weights.data(), s.weights.size());
+    if (!s.block_scales.empty()) { std::memcpy(scales, s.block_scales.data(), s.block_scales.size()); }
+    *quant_scale = s.quant_scale;
+    dims[0] = (int)s.dtype;
+    dims[1] = s.n;
+    dims[2] = s.k;
+    return 0;
+}
+// Writes a container from parallel arrays of keys / blobs (tests, and saving a quantised cache).
+HOST_EXPORT int cccc_host_bin_write(const char* path, int count, const char** keys, const void** blobs, const unsigned long long* lens)
+{
+    BinWriter w;
+    for (int i = 0; i < count; i++) { w.add(keys[i], blobs[i], (size_t)lens[i]); }
+    return w.save(path) ? 0 : -1;
+}

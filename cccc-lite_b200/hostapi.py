@@ -28,6 +28,13 @@ SYMBOLS = {
     "cccc_host_mul": (None, [_vp, _vp, _vp, _f, _f, _i, _i]),
     "cccc_host_mul_batched": (None, [_vp, _vp, _vp, _i, _i, _f, _f]),
     "cccc_host_gemm": (None, [_vp, _i, _i, _i, _i, _i, _f, _vp, _i, _i, _f, _vp, _i, _i, _f, _f, _vp, _i, _i, _vp, _vp]),
+    "cccc_host_bin_open": (_vp, [C.c_char_p]),
+    "cccc_host_bin_close": (None, [_vp]),
+    "cccc_host_bin_has": (_i, [_vp, C.c_char_p]),
+    "cccc_host_bin_bytes_read": (C.c_ulonglong, [_vp]),
+    "cccc_host_bin_load_shard": (_i, [_vp, C.c_char_p, _i, _i, C.c_char, _i, _i, _vp, C.c_ulonglong, _vp, C.c_ulonglong,
+                                      C.POINTER(C.c_float), C.POINTER(C.c_int), C.c_char_p, _i]),
+    "cccc_host_bin_write": (_i, [C.c_char_p, _i, C.POINTER(C.c_char_p), C.POINTER(C.c_void_p), C.POINTER(C.c_ulonglong)]),
 }
 _lib = None
 

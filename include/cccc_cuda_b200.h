@@ -104,6 +104,14 @@ C_EXPORT int cuda_gemm_wq_bf16_static(int w_type, const void* W, const void* blk
     void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx,
     unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta, void* stream, unsigned int flags);
 
+/* No counterpart in the reference (which launches every linear in isolation).  Arms a one-shot hint
+ * for the calling host thread: the next cuda_gemm_wq_bf16 call that takes the decode kernel also
+ * brings [ptr, ptr + bytes) into L2 (cp.async.bulk.prefetch.L2) while it streams its own weights.
+ * Point it at the weights of the linear that will run next: that linear then starts from L2 and HBM
+ * keeps streaming across the gap between the two kernels.  ptr must be 16-byte aligned device memory
+ * that stays valid until that call has run; at most 64 MB are taken.  ptr = NULL disarms.  Returns 0. */
+C_EXPORT int cuda_b200_prefetch_next(const void* ptr, unsigned long long bytes);
+
 /* Tuning/diagnostic: returns which kernel cuda_gemm_wq_bf16 would pick for a shape
  * (0 = plain kernel, 1 = decode GEMV (M<=32), 2 = prefill tcgen05 GEMM) without launching. */
 C_EXPORT int cuda_gemm_wq_bf16_plan(int w_type, const void* W, const void* blk_scales, const void* X,
