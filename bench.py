@@ -5,9 +5,10 @@
 Workload (N=1): the linears of one decode token of a Qwen3-8B-shaped model with FP8_E5M2 weights
 and BF16 activations: 36 layers x (q 4096<-4096, k 1024<-4096, v 1024<-4096, o 4096<-4096,
 gate 12288<-4096, up 12288<-4096, down 4096<-12288) plus lm_head 151936<-4096, batch M tokens
-(default 1).  A step is one pass over all 253 linears, each through the library's C-ABI
-(cuda_gemm_wq_bf16); 7.57 GB of distinct weights are resident in HBM, so every step streams far
-more than the L2 holds.  The metric is algorithmic bytes per second (weights + scales +
+(default 1).  A step is one pass over all 253 linears through the library's C-ABI: q,k,v and
+gate,up of a layer, which read the same activations, as one cuda_gemm_wq_bf16_group call each
+(--group 0: every linear its own cuda_gemm_wq_bf16 call), the others as cuda_gemm_wq_bf16.
+7.57 GB of distinct weights are resident in HBM, so every step streams far more than the L2 holds.  The metric is algorithmic bytes per second (weights + scales +
 activations in + out, each counted once per linear).
 
 With N>1 (launched under torchrun, one rank per GPU) the same token is computed tensor-parallel:
@@ -172,30 +173,51 @@ def build_model(torch, capi, dims, M, wtype, rank, world, dev):
     return wt, lin, bufs
 
 
-def run_step(torch, dist, capi, wt, lin, bufs, M, world, flags, prefetch=True):
+def plan_step(capi, lin, bufs, M, world, grouped):
+    """The launches of one token: consecutive linears that read the same buffer (q,k,v; gate,up) become
+    one grouped call when `grouped`; row-parallel linears stay alone (their partial sums are reduced)."""
+    import math
+
+    calls, i = [], 0
+    while i < len(lin):
+        L = lin[i]
+        row_parallel = world > 1 and L["kind"] == "row"
+        members = [L]
+        if grouped and not row_parallel:
+            while (i + len(members) < len(lin) and len(members) < 3 and lin[i + len(members)]["src"] == L["src"]
+                   and lin[i + len(members)]["K"] == L["K"] and lin[i + len(members)]["name"] != "lm_head"
+                   and not (world > 1 and lin[i + len(members)]["kind"] == "row") and L["name"] != "lm_head"):
+                members.append(lin[i + len(members)])
+        src = bufs["x"] if L["name"] == "lm_head" else bufs[L["src"]]
+        items = []
+        for Lm in members:
+            dst = bufs["logits"] if Lm["name"] == "lm_head" else bufs[Lm["name"]]
+            out = bufs["partial"] if row_parallel else dst
+            items.append(dict(W=Lm["W"], S=Lm["S"], inv=Lm["inv"], Y=out, N=Lm["N"], alpha=1.0 / (W_STD * math.sqrt(Lm["fullK"]))))
+        calls.append(dict(items=items, group=capi.make_group(items, L["K"]), src=src, K=L["K"], row_parallel=row_parallel,
+                          dst=bufs["logits"] if L["name"] == "lm_head" else bufs[L["name"]], name=L["name"]))
+        i += len(members)
+    return calls
+
+
+def run_step(torch, dist, capi, wt, calls, bufs, M, world, flags):
     """One token's linears.  alpha keeps activation magnitudes steady through the random layers.
     With more than one rank, row-parallel linears (o, down) write FP32 partial sums, which are
     all-reduced and rounded to BF16 once; the logits are all-gathered."""
-    import math
-
     n_launch = 0
-    for idx, L in enumerate(lin):
-        name = L["name"]
-        if prefetch and idx + 1 < len(lin):
-            capi.prefetch_next(lin[idx + 1]["W"])
-        src = bufs[L["src"]] if name != "lm_head" else bufs["x"]
-        dst = bufs["logits"] if name == "lm_head" else bufs[name]
-        alpha = 1.0 / (W_STD * math.sqrt(L["fullK"]))
-        row_parallel = world > 1 and L["kind"] == "row"
-        out = bufs["partial"] if row_parallel else dst
-        rc = capi.gemm_wq_bf16(wt, L["W"], L["S"], L["inv"], src, out, L["N"], M, L["K"], alpha=alpha,
-                               flags=flags | (capi.FLAG_OUT_F32 if row_parallel else 0))
+    for c in calls:
+        if len(c["items"]) == 1:
+            it = c["items"][0]
+            rc = capi.gemm_wq_bf16(wt, it["W"], it["S"], it["inv"], c["src"], it["Y"], it["N"], M, c["K"], alpha=it["alpha"],
+                                   flags=flags | (capi.FLAG_OUT_F32 if c["row_parallel"] else 0))
+        else:
+            rc = capi.gemm_wq_bf16_group(wt, c["group"], c["src"], M, c["K"], flags=flags)
         if rc != 0:
-            raise RuntimeError(f"cuda_gemm_wq_bf16 failed on {name}: {rc}")
+            raise RuntimeError(f"linear {c['name']} failed: {rc}")
         n_launch += 1
-        if row_parallel:
-            dist.all_reduce(out)
-            dst.copy_(out)
+        if c["row_parallel"]:
+            dist.all_reduce(bufs["partial"])
+            c["dst"].copy_(bufs["partial"])
     if world > 1:
         dist.all_gather_into_tensor(bufs["logits_all"], bufs["logits"])
     return n_launch
@@ -244,6 +266,7 @@ def gpu_arm(args):
     wt, lin, bufs = build_model(torch, capi, dims, M, args.wtype, rank, world, dev)
     # the layer chain: "down" of a layer is the next layer's "x"
     bufs["down"] = bufs["x"]
+    calls = plan_step(capi, lin, bufs, M, world, bool(args.group))
     flags = capi.FLAG_PDL if args.pdl else 0
 
     x_host = torch.randn(M, dims[0]).to(torch.bfloat16).pin_memory()
@@ -265,7 +288,7 @@ def gpu_arm(args):
 
     with torch.cuda.stream(stream):
         bufs["x"].copy_(x_host, non_blocking=True)
-        launches_per_step = run_step(torch, dist, capi, wt, lin, bufs, M, world, flags, not args.no_l2_prefetch)  # first call: workspace
+        launches_per_step = run_step(torch, dist, capi, wt, calls, bufs, M, world, flags)  # first call: workspace
         stream.synchronize()
         assert capi.check_error("bench warmup") == 0
         graph = None
@@ -273,13 +296,13 @@ def gpu_arm(args):
             graph = torch.cuda.CUDAGraph()
             bufs["x"].copy_(x_host, non_blocking=True)
             with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
-                run_step(torch, dist, capi, wt, lin, bufs, M, world, flags, not args.no_l2_prefetch)
+                run_step(torch, dist, capi, wt, calls, bufs, M, world, flags)
 
         def one_step():
             if graph is not None:
                 graph.replay()
             else:
-                run_step(torch, dist, capi, wt, lin, bufs, M, world, flags, not args.no_l2_prefetch)
+                run_step(torch, dist, capi, wt, calls, bufs, M, world, flags)
 
         # ---- device-resident arm ----
         for _ in range(args.warmup):
@@ -338,7 +361,7 @@ def gpu_arm(args):
             "workload": f"{'llama-3.1-8b w4a16' if args.wtype == 'fp4' else 'qwen3-8b w8a16'} decode linears: "
                         f"{dims[5]} layers x (q,k,v,o,gate,up,down) + lm_head, M={M}",
             "tokens": M, "bytes_per_step": bytes_per_step, "l2": "7.5 GB of distinct weights per step (> L2)",
-            "cuda_graph": graph is not None, "pdl": bool(args.pdl), "l2_prefetch_next": not args.no_l2_prefetch, "parallelism": f"tp{world}",
+            "cuda_graph": graph is not None, "pdl": bool(args.pdl), "grouped_qkv_gateup": bool(args.group), "parallelism": f"tp{world}",
             "tok_per_s": round(M / (ms_per_step * 1e-3), 1),
         },
         "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": x_host.numel() * 2,
@@ -491,7 +514,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--no-l2-prefetch", action="store_true", help="do not hint the next linear's weights into L2")
+    ap.add_argument("--group", type=int, default=1, help="1: q,k,v and gate,up of a layer go through cuda_gemm_wq_bf16_group")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (small cases for profiling)")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--watchdog", type=float, default=420.0, help="seconds after which a stuck run exits by itself")

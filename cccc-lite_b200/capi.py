@@ -31,10 +31,20 @@ SYMBOLS = {
     "cuda_gemm_wq_bf16": (_i, [_i, _vp, _vp, _f, _vp, _vp, _u, _u, _u, _u, _u, _u, _u, _f, _f, _vp, _u]),
     "cuda_gemm_wq_bf16_static": (_i, [_i, _vp, _vp, _f, _vp, _vp, _u, _u, _u, _u, _u, _u, _u, _f, _f, _vp, _u]),
     "cuda_gemm_wq_bf16_plan": (_i, [_i, _vp, _vp, _vp, _vp, _u, _u, _u, _u, _u, _u, _u]),
-    "cuda_b200_prefetch_next": (_i, [_vp, C.c_ulonglong]),
     "cuda_b200_launch_count": (C.c_ulonglong, []),
     "cuda_b200_version": (C.c_char_p, []),
 }
+
+
+
+class WqLinear(C.Structure):
+    """cuda_wq_linear of include/cccc_cuda_b200.h."""
+    _fields_ = [("W", C.c_void_p), ("blk_scales", C.c_void_p), ("Y", C.c_void_p), ("inv_scale", C.c_float),
+                ("alpha", C.c_float), ("beta", C.c_float), ("N_out", C.c_uint), ("ldw", C.c_uint), ("ldy_m", C.c_uint),
+                ("ldy_n", C.c_uint)]
+
+
+SYMBOLS["cuda_gemm_wq_bf16_group"] = (_i, [_i, _u, C.POINTER(WqLinear), _vp, _u, _u, _u, _vp, _u])
 
 _lib = None
 
@@ -104,20 +114,39 @@ def gemm_wq_bf16_static(w_type: int, W, blk, inv_scale: float, X, Y, N: int, M: 
                                           N if ldy_m is None else ldy_m, ldy_n, alpha, beta, stream, flags)
 
 
+def make_group(linears, K: int):
+    """A ctypes array of cuda_wq_linear from dicts with W, S (block scales or None), Y, N, and optional
+    inv, alpha, beta, ldw, ldy_m, ldy_n.  Build it once and reuse it: it only holds pointers."""
+    arr = (WqLinear * len(linears))()
+    for a, L in zip(arr, linears):
+        a.W = _ptr(L["W"])
+        a.blk_scales = _ptr(L.get("S"))
+        a.Y = _ptr(L["Y"])
+        a.inv_scale = L.get("inv", 1.0)
+        a.alpha = L.get("alpha", 1.0)
+        a.beta = L.get("beta", 0.0)
+        a.N_out = L["N"]
+        a.ldw = L.get("ldw", K)
+        a.ldy_m = L.get("ldy_m", L["N"])
+        a.ldy_n = L.get("ldy_n", 1)
+    return arr
+
+
+def gemm_wq_bf16_group(w_type: int, group, X, M: int, K: int, *, ldx: int | None = None, stream: int | None = None,
+                       flags: int = 0) -> int:
+    """Several linears sharing the activations X in one call (`group` from make_group)."""
+    if stream is None:
+        import torch
+
+        stream = torch.cuda.current_stream().cuda_stream
+    return lib().cuda_gemm_wq_bf16_group(w_type, len(group), group, _ptr(X), M, K, K if ldx is None else ldx, stream, flags)
+
+
 def gemm_wq_bf16_plan(w_type: int, W, blk, X, Y, N: int, M: int, K: int, *, ldw=None, ldx=None, ldy_m=None,
                       ldy_n: int = 1) -> int:
     return lib().cuda_gemm_wq_bf16_plan(w_type, _ptr(W), _ptr(blk), _ptr(X), _ptr(Y), N, M, K,
                                         K if ldw is None else ldw, K if ldx is None else ldx,
                                         N if ldy_m is None else ldy_m, ldy_n)
-
-
-def prefetch_next(t, nbytes: int | None = None) -> int:
-    """Arm the one-shot L2 prefetch hint with a tensor (or raw pointer + byte count)."""
-    if t is None:
-        return lib().cuda_b200_prefetch_next(None, 0)
-    if nbytes is None:
-        nbytes = t.numel() * t.element_size()
-    return lib().cuda_b200_prefetch_next(_ptr(t), nbytes)
 
 
 def launch_count() -> int:

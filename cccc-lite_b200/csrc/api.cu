@@ -4,7 +4,6 @@
 #include "../../include/cccc_cuda_b200.h"
 
 #include <atomic>
-#include <cstdlib>
 #include <mutex>
 
 namespace b200
@@ -120,28 +119,33 @@ C_EXPORT int cuda_gemm_wq_bf16(int w_type, const void* W, const void* blk_scales
         beta, (cudaStream_t)stream, flags);
 }
 
+C_EXPORT int cuda_gemm_wq_bf16_group(int w_type, unsigned int count, const cuda_wq_linear* linears, const void* X,
+    unsigned int M_tokens, unsigned int K, unsigned int ldx, void* stream, unsigned int flags)
+{
+    if (w_type != DT_E4M3 && w_type != DT_E5M2 && w_type != DT_FP4) { return -1; }
+    if (count == 0 || M_tokens == 0) { return 0; }
+    if (!linears || !X) { return -1; }
+    for (unsigned int j = 0; j < count; j++)
+    {
+        if (linears[j].N_out != 0 && (!linears[j].W || !linears[j].Y)) { return -1; }
+    }
+    Workspace* ws = workspace();
+    if (!ws)
+    {
+        fprintf(stderr, "gemm_wq_bf16 kernel launch failed: no workspace on this device\n");
+        return 1;
+    }
+    static_assert(sizeof(GroupItem) == sizeof(cuda_wq_linear), "GroupItem mirrors cuda_wq_linear");
+    return run_linear_wq_group(&ws->scratch, w_type, count, reinterpret_cast<const GroupItem*>(linears), X, M_tokens, K, ldx,
+        (cudaStream_t)stream, flags);
+}
+
 C_EXPORT int cuda_gemm_wq_bf16_plan(int w_type, const void* W, const void* blk_scales, const void* X, const void* Y,
     unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m,
     unsigned int ldy_n)
 {
     if (w_type != DT_E4M3 && w_type != DT_E5M2 && w_type != DT_FP4) { return -1; }
     return plan_for(w_type, W, blk_scales, X, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n);
-}
-
-C_EXPORT int cuda_b200_prefetch_next(const void* ptr, unsigned long long bytes)
-{
-    // Larger requests are cut: more than this does not stay in the 126 MB L2 next to the running linear.
-    static long long cap_mb = -1;
-    if (cap_mb < 0)
-    {
-        const char* e = getenv("CCCC_B200_PREFETCH_CAP_MB");
-        cap_mb = e ? atoll(e) : 64;
-    }
-    const unsigned long long cap = (unsigned long long)cap_mb << 20;
-    PrefetchHint& h = prefetch_hint();
-    h.ptr = ptr;
-    h.bytes = ptr ? (bytes < cap ? bytes : cap) : 0;
-    return 0;
 }
 
 C_EXPORT int cuda_check_error(const char* label) { return sync_and_report(label ? label : "cuda"); }

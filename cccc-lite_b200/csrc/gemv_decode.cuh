@@ -8,8 +8,8 @@
 // accumulators: the weight tile is the A operand (16 output features x 16 k), the tokens are
 // the 8 columns of B.  The k order inside a fragment is permuted so that every lane converts
 // the 16 bytes it loaded itself; the activation fragment is loaded in the same order.
-// A CTA takes at most half of an SM, so that under programmatic dependent launch the next
-// linear of the stream is already resident and prefetching its weights while this one ends.
+// Under programmatic dependent launch the weight prefetch of a linear is issued before it waits
+// for the previous kernel of the stream; activations, outputs and scratch are touched only after.
 //
 // Work is cut stream-K style: the (row block, k stage) items of the whole matrix are dealt to
 // the CTAs in equal contiguous runs, so every SM streams the same number of bytes whatever the
@@ -27,6 +27,20 @@
 
 namespace b200
 {
+
+constexpr int kMaxGroup = 3;    // linears that may share one launch (same activations, same K)
+
+// One linear of a grouped launch.  Its row blocks are [rb_begin, next segment's rb_begin).
+struct GemvSeg
+{
+    const uint8_t* W;
+    const uint8_t* blk;
+    uint16_t* Y;
+    unsigned int N, ldw;
+    unsigned int rb_begin;
+    long long ldy_m, ldy_n;
+    float w_scale, alpha, beta, post_scale;
+};
 
 struct GemvParams
 {
@@ -47,8 +61,8 @@ struct GemvParams
     unsigned int n_row_blocks, n_kstages, total_items;
     unsigned int gran;          // items are dealt to CTAs in groups of `gran`: 1 = stream-K, n_kstages = whole row blocks
     unsigned int n_stages;      // ring depth
-    const uint8_t* next_ptr;    // optional: bytes to bring into L2 while this linear streams (the next
-    unsigned long long next_bytes;    // linear's weights); 0 = none
+    unsigned int n_seg;         // linears in this launch (1 unless grouped); the fields above describe the
+    GemvSeg seg[kMaxGroup];     // first one, seg[] all of them (unused entries have rb_begin = 0xFFFFFFFF)
 #ifdef B200_TRACE
     unsigned long long* trace;  // debug builds only: 8 timestamps per CTA
 #endif
@@ -117,24 +131,12 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                  "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
-// L2 eviction policies: weights of the running linear are read once (evict first); lines prefetched
-// for the next linear should survive until it runs (evict last).
+// L2 eviction policy of the streamed weights: each byte is read once, so it should be the first to go.
 __device__ __forceinline__ uint64_t l2_policy_evict_first()
 {
     uint64_t pol;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
     return pol;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_last()
-{
-    uint64_t pol;
-    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
-    return pol;
-}
-// Bring [ptr, ptr+bytes) into L2 (no shared-memory destination).  16-byte aligned, multiple of 16.
-__device__ __forceinline__ void bulk_prefetch_l2(const void* ptr, uint32_t bytes, uint64_t policy)
-{
-    asm volatile("cp.async.bulk.prefetch.L2.global.L2::cache_hint [%0], %1, %2;" ::"l"(ptr), "r"(bytes), "l"(policy) : "memory");
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -333,6 +335,8 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
 template <class Cfg, bool SCALED>
 __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
     gemv_wq_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
+        const __grid_constant__ CUtensorMap tmW1, const __grid_constant__ CUtensorMap tmS1,
+        const __grid_constant__ CUtensorMap tmW2, const __grid_constant__ CUtensorMap tmS2,
         const __grid_constant__ CUtensorMap tmX, const GemvParams p)
 {
     constexpr int WT = Cfg::WT, MT = Cfg::MT, RT = Cfg::RT, WK = Cfg::WK, R = Cfg::R;
@@ -382,12 +386,14 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
             const unsigned int rb = item / p.n_kstages, ks = item % p.n_kstages;
             const unsigned int s = it % NS;
             unsigned char* st = stages + (size_t)s * Cfg::STAGE_BYTES;
+            // which linear of the group this row block belongs to, and its row block there
+            const unsigned int j = (rb >= p.seg[1].rb_begin ? 1u : 0u) + (rb >= p.seg[2].rb_begin ? 1u : 0u);
+            const int row0 = (int)((rb - p.seg[j].rb_begin) * R);
+            const CUtensorMap* mw = j == 0 ? &tmW : (j == 1 ? &tmW1 : &tmW2);
+            const CUtensorMap* ms = j == 0 ? &tmS : (j == 1 ? &tmS1 : &tmS2);
             mbar_expect_tx(full_bar + s, Cfg::W_BYTES + Cfg::S_BYTES);
-            tma_load_3d_hint(st, &tmW, 0, (int)(rb * R), (int)(ks * Cfg::SKS), full_bar + s, pol_stream);
-            if (WT == DT_FP4)
-            {
-                tma_load_3d_hint(st + Cfg::W_BYTES, &tmS, 0, (int)(rb * R), (int)(ks * (Cfg::SKS / 2)), full_bar + s, pol_stream);
-            }
+            tma_load_3d_hint(st, mw, 0, row0, (int)(ks * Cfg::SKS), full_bar + s, pol_stream);
+            if (WT == DT_FP4) { tma_load_3d_hint(st + Cfg::W_BYTES, ms, 0, row0, (int)(ks * (Cfg::SKS / 2)), full_bar + s, pol_stream); }
         };
         auto issue_acts = [&](unsigned int it) {
             const unsigned int item = items.beg + it;
@@ -404,16 +410,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
         B200_STAMP(1);
         for (unsigned int it = 0; it < pre; it++) { issue_weights(it); }
         B200_STAMP(2);
-        if (p.next_bytes != 0)
-        {
-            // This CTA's share of the next linear's weights goes to L2 now, behind its own first
-            // stages: HBM then keeps streaming through this kernel's tail and the next one's start.
-            const unsigned long long per = ((p.next_bytes / gridDim.x) + 15ull) & ~15ull;
-            unsigned long long off = (unsigned long long)blockIdx.x * per;
-            const unsigned long long end = min(off + per, p.next_bytes & ~15ull);
-            const uint64_t pol_keep = l2_policy_evict_last();
-            for (; off < end; off += 32768ull) { bulk_prefetch_l2(p.next_ptr + off, (uint32_t)min(32768ull, end - off), pol_keep); }
-        }
         pdl_wait();
         B200_STAMP(3);
         for (unsigned int it = 0; it < pre; it++) { issue_acts(it); }
@@ -465,6 +461,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
         const unsigned int ks0 = item0 % p.n_kstages;
         const unsigned int seg = min(p.n_kstages - ks0, n_items - it);    // items of this row block in my run
         const bool first_segment = (it == 0);
+        const unsigned int lj = (rb >= p.seg[1].rb_begin ? 1u : 0u) + (rb >= p.seg[2].rb_begin ? 1u : 0u);
+        const GemvSeg& L = p.seg[lj];    // the linear this row block belongs to
+        const float w_scale = L.w_scale;
 
         float acc[RT][MT][2][4];
 #pragma unroll
@@ -526,7 +525,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
 #pragma unroll
                             for (int i = 0; i < 4; i++)
                             {
-                                dequant_fp8x4<WT, SCALED>(w[i], p.w_scale, A[rt][h][(2 * i) % AREGS], A[rt][h][(2 * i + 1) % AREGS]);
+                                dequant_fp8x4<WT, SCALED>(w[i], w_scale, A[rt][h][(2 * i) % AREGS], A[rt][h][(2 * i + 1) % AREGS]);
                             }
                         }
                     }
@@ -626,24 +625,24 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
         consumer_bar_sync<CT>();
         const unsigned int n_out = p.M * R;    // live [token][row] entries
         const bool full = (ks0 == 0 && seg == p.n_kstages);
-        const unsigned int n0 = rb * R;
+        const unsigned int n0 = (rb - L.rb_begin) * R;
         auto store_out = [&](unsigned int e, float v) {
             const unsigned int m = e / R, r = e - m * R;
             const unsigned int n = n0 + r;
-            if (n < p.N)
+            if (n < L.N)
             {
-                const long long yi = (long long)m * p.ldy_m + (long long)n * p.ldy_n;
-                float o = p.alpha * (v * p.post_scale);
+                const long long yi = (long long)m * L.ldy_m + (long long)n * L.ldy_n;
+                float o = L.alpha * (v * L.post_scale);
                 if (p.out_f32)
                 {
-                    float* y = reinterpret_cast<float*>(p.Y) + yi;
-                    if (p.beta != 0.f) { o += p.beta * *y; }
+                    float* y = reinterpret_cast<float*>(L.Y) + yi;
+                    if (L.beta != 0.f) { o += L.beta * *y; }
                     *y = o;
                 }
                 else
                 {
-                    uint16_t* y = p.Y + yi;
-                    if (p.beta != 0.f) { o += p.beta * bf16_bits_to_float(*y); }
+                    uint16_t* y = L.Y + yi;
+                    if (L.beta != 0.f) { o += L.beta * bf16_bits_to_float(*y); }
                     *y = __bfloat16_as_ushort(__float2bfloat16_rn(o));
                 }
             }

@@ -90,7 +90,32 @@ static int launch_gemv_cfg(GemvParams p, const GemvScratch* ws, cudaStream_t str
     int ns = (budget - Cfg::HEADER_BYTES - Cfg::RED_BYTES) / Cfg::STAGE_BYTES;
     if (ns > Cfg::kMaxStages) { ns = Cfg::kMaxStages; }
     if (ns < 1) { return -2; }
-    p.n_row_blocks = (p.N + Cfg::R - 1) / Cfg::R;
+    if (p.n_seg == 0)
+    {
+        // a single linear: describe it as a group of one
+        p.n_seg = 1;
+        p.seg[0].W = p.W;
+        p.seg[0].blk = p.blk;
+        p.seg[0].Y = p.Y;
+        p.seg[0].N = p.N;
+        p.seg[0].ldw = p.ldw;
+        p.seg[0].ldy_m = p.ldy_m;
+        p.seg[0].ldy_n = p.ldy_n;
+        p.seg[0].w_scale = p.w_scale;
+        p.seg[0].alpha = p.alpha;
+        p.seg[0].beta = p.beta;
+        p.seg[0].post_scale = p.post_scale;
+    }
+    p.n_row_blocks = 0;
+    for (int j = 0; j < kMaxGroup; j++)
+    {
+        if ((unsigned)j < p.n_seg)
+        {
+            p.seg[j].rb_begin = p.n_row_blocks;
+            p.n_row_blocks += (p.seg[j].N + Cfg::R - 1) / Cfg::R;
+        }
+        else { p.seg[j].rb_begin = 0xFFFFFFFFu; }
+    }
     p.n_kstages = (p.K + Cfg::SKE - 1) / Cfg::SKE;
     const unsigned long long total = (unsigned long long)p.n_row_blocks * p.n_kstages;
     if (total == 0 || total > 0x7FFFFFFFull) { return -2; }
@@ -116,15 +141,26 @@ static int launch_gemv_cfg(GemvParams p, const GemvScratch* ws, cudaStream_t str
     const unsigned int grid = (unsigned int)(groups < (unsigned long long)ws->sm_count ? groups : ws->sm_count);
     if ((size_t)grid * 2 * Cfg::R * 8 * Cfg::MT * sizeof(float) > ws->partial_bytes || grid > ws->n_counters) { return -2; }
 
-    CUtensorMap tmW, tmS, tmX;
+    CUtensorMap tmW[kMaxGroup], tmS[kMaxGroup], tmX;
     const unsigned long long kbytes = (WT == DT_FP4) ? p.K / 2 : p.K;
-    const unsigned long long ldw_bytes = (WT == DT_FP4) ? p.ldw / 2 : p.ldw;
-    bool ok = make_map(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.W, 64, p.N, kbytes / 64, ldw_bytes, Cfg::R, Cfg::SKS, false);
-    if (ok && WT == DT_FP4)
+    bool ok = true;
+    for (int j = 0; j < kMaxGroup; j++)
     {
-        ok = make_map(&tmS, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.blk, 16, p.N, p.K / 256, p.ldw / 16, Cfg::R, Cfg::SKS / 2, false);
+        if ((unsigned)j >= p.n_seg)
+        {
+            tmW[j] = tmW[0];
+            tmS[j] = tmS[0];
+            continue;
+        }
+        const GemvSeg& g = p.seg[j];
+        const unsigned long long ldw_bytes = (WT == DT_FP4) ? g.ldw / 2 : g.ldw;
+        ok = ok && make_map(&tmW[j], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.W, 64, g.N, kbytes / 64, ldw_bytes, Cfg::R, Cfg::SKS, false);
+        if (ok && WT == DT_FP4)
+        {
+            ok = make_map(&tmS[j], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.blk, 16, g.N, p.K / 256, g.ldw / 16, Cfg::R, Cfg::SKS / 2, false);
+        }
+        else { tmS[j] = tmW[j]; }
     }
-    else { tmS = tmW; }
     ok = ok && make_map(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.X, 64, p.M, p.K / 64, (unsigned long long)p.ldx * 2, Cfg::XB,
                    Cfg::XSLABS, Cfg::XSWZ);
     if (!ok)
@@ -165,7 +201,7 @@ static int launch_gemv_cfg(GemvParams p, const GemvScratch* ws, cudaStream_t str
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     count_launch();
-    if (cudaLaunchKernelEx(&cfg, kernel, tmW, tmS, tmX, p) != cudaSuccess)
+    if (cudaLaunchKernelEx(&cfg, kernel, tmW[0], tmS[0], tmW[1], tmS[1], tmW[2], tmS[2], tmX, p) != cudaSuccess)
     {
         report_launch("gemm_wq_bf16");
         return 1;
@@ -185,6 +221,8 @@ static int launch_gemv(const GemvParams& p, const GemvScratch* ws, cudaStream_t 
     if (tuning_variant() == 4 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 8, 16, 2, 1>, SCALED>(p, ws, stream, pdl); }
     if (tuning_variant() == 5 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 8, 32, 2, 1>, SCALED>(p, ws, stream, pdl); }
     if (tuning_variant() == 2 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 1, 8, 16, 2, 2>, SCALED>(p, ws, stream, pdl); }
+    if (tuning_variant() == 14 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 16, 32, 2, 1>, SCALED>(p, ws, stream, pdl); }
+    if (tuning_variant() == 15 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 2, 8, 32, 2, 1>, SCALED>(p, ws, stream, pdl); }
     if (tuning_variant() == 12 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 7, 32, 2, 2>, SCALED>(p, ws, stream, pdl); }
     if (tuning_variant() == 13 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 7, 16, 2, 2>, SCALED>(p, ws, stream, pdl); }
     if (tuning_variant() == 9 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 7, 14, 2, 2>, SCALED>(p, ws, stream, pdl); }
@@ -247,19 +285,6 @@ static int plan_for(int w_type, const void* W, const void* blk, const void* X, c
 }
 
 
-// One-shot hint armed by cuda_b200_prefetch_next and consumed by the next decode launch of this
-// host thread.
-struct PrefetchHint
-{
-    const void* ptr = nullptr;
-    unsigned long long bytes = 0;
-};
-inline PrefetchHint& prefetch_hint()
-{
-    static thread_local PrefetchHint h;
-    return h;
-}
-
 // The whole entry: argument checks done by the caller; picks the kernel and launches it on
 // `st`.  Returns the C-ABI code (0 ok, 1 CUDA error, -1 bad argument).
 static int run_linear_wq(const GemvScratch* ws, int w_type, const void* W, const void* blk_scales, float inv_scale, const void* X,
@@ -287,15 +312,6 @@ static int run_linear_wq(const GemvScratch* ws, int w_type, const void* W, const
     p.beta = beta;
     p.post_scale = 1.0f;
     p.out_f32 = (flags & 4u) ? 1u : 0u;
-    {
-        PrefetchHint& h = prefetch_hint();
-        if (h.ptr && (((uintptr_t)h.ptr) & 15u) == 0)
-        {
-            p.next_ptr = (const uint8_t*)h.ptr;
-            p.next_bytes = h.bytes;
-        }
-        h = PrefetchHint();    // one shot, whichever kernel this call takes
-    }
     const bool pdl = (flags & 1u) != 0;
 
     int plan = plan_for(w_type, W, blk_scales, X, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n);
@@ -334,6 +350,84 @@ static int run_linear_wq(const GemvScratch* ws, int w_type, const void* W, const
     case DT_E5M2: return launch_plain<DT_E5M2>(p, st);
     default: return launch_plain<DT_FP4>(p, st);
     }
+}
+
+
+// One linear of a group, as the C-ABI passes it (mirrors cuda_wq_linear of the public header).
+struct GroupItem
+{
+    const void* W;
+    const void* blk_scales;
+    void* Y;
+    float inv_scale, alpha, beta;
+    unsigned int N_out, ldw, ldy_m, ldy_n;
+};
+
+// Several linears that read the same activations (q/k/v, gate/up) as ONE launch of the decode
+// kernel: their row blocks are dealt out together.  Anything the decode kernel does not take
+// (more than 32 tokens, unaligned operands, more than kMaxGroup linears) runs one linear at a time.
+static int run_linear_wq_group(const GemvScratch* ws, int w_type, unsigned int count, const GroupItem* items, const void* X,
+    unsigned int M_tokens, unsigned int K, unsigned int ldx, cudaStream_t st, unsigned int flags)
+{
+    bool one_launch = count >= 1 && count <= (unsigned)kMaxGroup && M_tokens <= 32;
+    for (unsigned int j = 0; j < count && one_launch; j++)
+    {
+        one_launch = items[j].N_out != 0
+            && plan_for(w_type, items[j].W, items[j].blk_scales, X, items[j].Y, items[j].N_out, M_tokens, K, items[j].ldw, ldx,
+                   items[j].ldy_m, items[j].ldy_n)
+                == PLAN_DECODE;
+    }
+    if (one_launch)
+    {
+        GemvParams p;
+        memset(&p, 0, sizeof(p));
+        p.X = (const uint16_t*)X;
+        p.partials = ws->partials;
+        p.counters = ws->counters;
+        p.status = ws->status;
+        p.M = M_tokens;
+        p.K = K;
+        p.ldx = ldx;
+        p.out_f32 = (flags & 4u) ? 1u : 0u;
+        p.n_seg = count;
+        bool all_pow2 = true;
+        for (unsigned int j = 0; j < count; j++) { all_pow2 = all_pow2 && is_pow2_scale(items[j].inv_scale); }
+        const bool scaled = w_type != DT_FP4 && !all_pow2;
+        for (unsigned int j = 0; j < count; j++)
+        {
+            GemvSeg& g = p.seg[j];
+            g.W = (const uint8_t*)items[j].W;
+            g.blk = (w_type == DT_FP4) ? (const uint8_t*)items[j].blk_scales : nullptr;
+            g.Y = (uint16_t*)items[j].Y;
+            g.N = items[j].N_out;
+            g.ldw = items[j].ldw;
+            g.ldy_m = items[j].ldy_m;
+            g.ldy_n = items[j].ldy_n;
+            g.alpha = items[j].alpha;
+            g.beta = items[j].beta;
+            g.w_scale = scaled ? items[j].inv_scale : 1.0f;
+            g.post_scale = (w_type == DT_FP4) ? 65536.0f : (scaled ? 1.0f : items[j].inv_scale);
+        }
+        p.W = p.seg[0].W;
+        p.blk = p.seg[0].blk;
+        p.Y = p.seg[0].Y;
+        p.N = p.seg[0].N;
+        p.ldw = p.seg[0].ldw;
+        const bool pdl = (flags & 1u) != 0;
+        int r;
+        if (w_type == DT_FP4) { r = launch_gemv<DT_FP4, false>(p, ws, st, pdl); }
+        else if (scaled) { r = (w_type == DT_E5M2) ? launch_gemv<DT_E5M2, true>(p, ws, st, pdl) : launch_gemv<DT_E4M3, true>(p, ws, st, pdl); }
+        else { r = (w_type == DT_E5M2) ? launch_gemv<DT_E5M2, false>(p, ws, st, pdl) : launch_gemv<DT_E4M3, false>(p, ws, st, pdl); }
+        if (r != -2) { return r; }
+    }
+    for (unsigned int j = 0; j < count; j++)
+    {
+        if (items[j].N_out == 0) { continue; }
+        const int r = run_linear_wq(ws, w_type, items[j].W, items[j].blk_scales, items[j].inv_scale, X, items[j].Y, items[j].N_out,
+            M_tokens, K, items[j].ldw, ldx, items[j].ldy_m, items[j].ldy_n, items[j].alpha, items[j].beta, st, flags);
+        if (r != 0) { return r; }
+    }
+    return 0;
 }
 
 }    // namespace b200

@@ -82,6 +82,27 @@ C_EXPORT int cuda_gemm_wq_bf16(int w_type, const void* W, const void* blk_scales
     void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx,
     unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta, void* stream, unsigned int flags);
 
+/* One linear of a group (see cuda_gemm_wq_bf16_group); fields as the arguments of cuda_gemm_wq_bf16. */
+typedef struct cuda_wq_linear
+{
+    const void* W;
+    const void* blk_scales;
+    void* Y;
+    float inv_scale, alpha, beta;
+    unsigned int N_out, ldw, ldy_m, ldy_n;
+} cuda_wq_linear;
+
+/* Several quantised linears that read the SAME activations X (and so share M_tokens, K, ldx and the
+ * weight type) in one call: the q/k/v projections of a layer, or gate and up.  The reference issues
+ * them as separate ops (scripts/convert_weights.py:488-524 generates one batchedMul per projection,
+ * each reaching cccc/cublas_real.h:943-964); here up to 3 of them that the decode kernel takes
+ * (M_tokens <= 32, TMA-eligible operands) run as ONE launch whose row blocks are dealt to the SMs
+ * together, which saves the per-launch latency that dominates small linears.  Anything else (more
+ * linears, more tokens, unaligned operands) is run one linear at a time, so the result is always
+ * that of `count` separate cuda_gemm_wq_bf16 calls.  stream and flags as there. */
+C_EXPORT int cuda_gemm_wq_bf16_group(int w_type, unsigned int count, const cuda_wq_linear* linears, const void* X,
+    unsigned int M_tokens, unsigned int K, unsigned int ldx, void* stream, unsigned int flags);
+
 /* No counterpart in the reference.  The same linear as cuda_gemm_wq_bf16 for callers that cannot
  * allocate when they issue it: hosts that plan every byte of device memory up front (or have already
  * committed all of it) and hand the library no allocator, and latency-critical loops that may not take
@@ -103,14 +124,6 @@ C_EXPORT int cuda_gemm_wq_bf16(int w_type, const void* W, const void* blk_scales
 C_EXPORT int cuda_gemm_wq_bf16_static(int w_type, const void* W, const void* blk_scales, float inv_scale, const void* X,
     void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx,
     unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta, void* stream, unsigned int flags);
-
-/* No counterpart in the reference (which launches every linear in isolation).  Arms a one-shot hint
- * for the calling host thread: the next cuda_gemm_wq_bf16 call that takes the decode kernel also
- * brings [ptr, ptr + bytes) into L2 (cp.async.bulk.prefetch.L2) while it streams its own weights.
- * Point it at the weights of the linear that will run next: that linear then starts from L2 and HBM
- * keeps streaming across the gap between the two kernels.  ptr must be 16-byte aligned device memory
- * that stays valid until that call has run; at most 64 MB are taken.  ptr = NULL disarms.  Returns 0. */
-C_EXPORT int cuda_b200_prefetch_next(const void* ptr, unsigned long long bytes);
 
 /* Tuning/diagnostic: returns which kernel cuda_gemm_wq_bf16 would pick for a shape
  * (0 = plain kernel, 1 = decode GEMV (M<=32), 2 = prefill tcgen05 GEMM) without launching. */
