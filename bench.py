@@ -216,8 +216,14 @@ def run_step(torch, dist, capi, wt, calls, bufs, M, world, flags):
             raise RuntimeError(f"linear {c['name']} failed: {rc}")
         n_launch += 1
         if c["row_parallel"]:
-            dist.all_reduce(bufs["partial"])
-            c["dst"].copy_(bufs["partial"])
+            ar = bufs.get("push_allreduce")
+            if ar is not None:
+                if ar(bufs["partial"], c["dst"], bufs["partial"].numel(), flags=flags & 1) != 0:
+                    raise RuntimeError("cuda_b200_allreduce_f32_to_bf16 failed")
+                n_launch += 1
+            else:
+                dist.all_reduce(bufs["partial"])
+                c["dst"].copy_(bufs["partial"])
     if world > 1:
         dist.all_gather_into_tensor(bufs["logits_all"], bufs["logits"])
     return n_launch
@@ -267,6 +273,21 @@ def gpu_arm(args):
     # the layer chain: "down" of a layer is the next layer's "x"
     bufs["down"] = bufs["x"]
     calls = plan_step(capi, lin, bufs, M, world, bool(args.group))
+    allreduce = "none"
+    if world > 1:
+        allreduce = "nccl"
+        if args.ar == "push":
+            try:
+                bufs["push_allreduce"] = capi.PushAllReduce(dist, dist.group.WORLD, rank, world, M * dims[0], dev)
+                allreduce = "push"
+            except Exception as e:  # symmetric memory not available on this box: NCCL does the exchange
+                if rank == 0:
+                    print(f"push all-reduce unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr, flush=True)
+        ok = torch.tensor([1 if allreduce == "push" else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            bufs.pop("push_allreduce", None)
+            allreduce = "nccl"
     flags = capi.FLAG_PDL if args.pdl else 0
 
     x_host = torch.randn(M, dims[0]).to(torch.bfloat16).pin_memory()
@@ -361,7 +382,7 @@ def gpu_arm(args):
             "workload": f"{'llama-3.1-8b w4a16' if args.wtype == 'fp4' else 'qwen3-8b w8a16'} decode linears: "
                         f"{dims[5]} layers x (q,k,v,o,gate,up,down) + lm_head, M={M}",
             "tokens": M, "bytes_per_step": bytes_per_step, "l2": "7.5 GB of distinct weights per step (> L2)",
-            "cuda_graph": graph is not None, "pdl": bool(args.pdl), "grouped_qkv_gateup": bool(args.group), "parallelism": f"tp{world}",
+            "cuda_graph": graph is not None, "pdl": bool(args.pdl), "grouped_qkv_gateup": bool(args.group), "allreduce": allreduce, "parallelism": f"tp{world}",
             "tok_per_s": round(M / (ms_per_step * 1e-3), 1),
         },
         "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": x_host.numel() * 2,
@@ -514,6 +535,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--ar", default="push", choices=["push", "nccl"], help="exchange of row-parallel partial sums (N>1)")
     ap.add_argument("--group", type=int, default=1, help="1: q,k,v and gate,up of a layer go through cuda_gemm_wq_bf16_group")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (small cases for profiling)")
     ap.add_argument("--no-prefill", action="store_true")

@@ -60,6 +60,12 @@ static Workspace* workspace()
     return &w;
 }
 
+unsigned int* cuda_b200_status_word()
+{
+    Workspace* ws = workspace();
+    return ws ? ws->scratch.status : nullptr;
+}
+
 int report_launch(const char* label)
 {
     const cudaError_t e = cudaGetLastError();

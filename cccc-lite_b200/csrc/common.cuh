@@ -29,6 +29,8 @@ void count_launch();
 int sync_and_report(const char* label);
 // Launch-only check (no sync) for the asynchronous entry points.
 int report_launch(const char* label);
+// The current device's status word (allocating the workspace if need be); nullptr on failure.
+unsigned int* cuda_b200_status_word();
 
 // ---- scalar codecs ----------------------------------------------------------------------------
 

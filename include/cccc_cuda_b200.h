@@ -125,6 +125,26 @@ C_EXPORT int cuda_gemm_wq_bf16_static(int w_type, const void* W, const void* blk
     void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx,
     unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta, void* stream, unsigned int flags);
 
+/* ---- additions: tensor-parallel exchange ----------------------------------------------------- */
+
+/* No counterpart in the reference (it has no tensor parallelism; its only multi-GPU mode copies
+ * gradients with cudaMemcpyPeer, cccc/Matrix.cpp:498-517).  One-shot all-reduce of the FP32 partial
+ * sums of a row-parallel linear over peer-mapped memory, rounded to BF16 once:
+ *     out_bf16[i] = bf16( sum over ranks of partial[i] ),  i < n,  the same bits on every rank.
+ * peer_recv_ptrs / peer_flag_ptrs are HOST arrays of `world` device pointers: entry r is rank r's
+ * receive area / flag area as mapped into THIS process (symmetric memory or IPC mappings; sizes from
+ * the three helpers below, flag area and counters zeroed once before the first call).  seq_counters
+ * is a small local device buffer.  Every rank must issue the same sequence of calls with the same n
+ * and n_max; n and n_max are multiples of 4, n <= n_max.  Asynchronous on `stream`; flags bit 0 =
+ * programmatic dependent launch.  A peer that does not arrive within one second raises the
+ * library's status word (reported by cuda_check_error) instead of hanging. */
+C_EXPORT int cuda_b200_allreduce_f32_to_bf16(const unsigned long long* peer_recv_ptrs,
+    const unsigned long long* peer_flag_ptrs, void* seq_counters, const void* partial, void* out_bf16, unsigned int n,
+    unsigned int n_max, int rank, int world, void* stream, unsigned int flags);
+C_EXPORT unsigned long long cuda_b200_allreduce_recv_bytes(int world, unsigned int n_max);
+C_EXPORT unsigned long long cuda_b200_allreduce_flag_bytes(int world);
+C_EXPORT unsigned long long cuda_b200_allreduce_counter_bytes(void);
+
 /* Tuning/diagnostic: returns which kernel cuda_gemm_wq_bf16 would pick for a shape
  * (0 = plain kernel, 1 = decode GEMV (M<=32), 2 = prefill tcgen05 GEMM) without launching. */
 C_EXPORT int cuda_gemm_wq_bf16_plan(int w_type, const void* W, const void* blk_scales, const void* X,

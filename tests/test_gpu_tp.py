@@ -51,6 +51,17 @@ def _worker(rank, world, port, q):
                     _, ref = O.linear_wq_bf16(wt, W, blk, inv, X, N, M, K)
                     rel, cos = rel_cos(full.float().cpu().numpy(), ref)
                     results.append((wt, kind, N, K, M, rel <= 1e-2 and cos >= 0.9999 and tuple(full.shape) == (M, N), rel, cos))
+        # the one-shot push all-reduce against NCCL's sum, several calls in a row (both buffer sets)
+        n_max = 8 * 4096
+        ar = capi.PushAllReduce(dist, dist.group.WORLD, rank, world, n_max, torch.device("cuda", rank))
+        g = torch.Generator(device="cuda").manual_seed(100 + rank)
+        for call, n in enumerate((4096, 8 * 4096, 4096, 1024, 4096)):
+            part = torch.randn(n, device="cuda", generator=g, dtype=torch.float32)
+            want = part.clone()
+            dist.all_reduce(want)
+            out = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+            assert ar(part, out, n) == 0 and capi.check_error("push") == 0
+            results.append(("push", call, n, 0, 0, bool(torch.equal(out, want.to(torch.bfloat16))), 0.0, 1.0))
         q.put((rank, results))
     finally:
         dist.destroy_process_group()
