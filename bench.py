@@ -477,7 +477,7 @@ def cpu_baseline(args, budget_s: float):
     xs = {K: rng.standard_normal((M, K)).astype(np.float32) for _, K in shapes}
     done_bytes, t_deq, t_gemm, layers = 0, 0.0, 0.0, 0
     t0 = time.perf_counter()
-    while time.perf_counter() - t0 < budget_s and layers < dims[5]:
+    while layers == 0 or (time.perf_counter() - t0 < budget_s and layers < dims[5]):
         for N, K in shapes:
             W, S = mats[(N, K)]
             _, td, tg = O.cpu_path_dequant_sgemm(wt, W, S, 1.0, xs[K], N, M, K, wf=wf[:N * K])

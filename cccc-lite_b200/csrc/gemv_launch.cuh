@@ -59,28 +59,6 @@ static unsigned long long* trace_next(unsigned int grid)
 }
 #endif
 
-static int tuning_align()
-{
-    static int v = -2;
-    if (v == -2)
-    {
-        const char* e = getenv("CCCC_B200_GEMV_ALIGN");
-        v = e ? atoi(e) : -1;
-    }
-    return v;
-}
-
-static int tuning_variant()
-{
-    static int v = -1;
-    if (v < 0)
-    {
-        const char* e = getenv("CCCC_B200_GEMV_VARIANT");
-        v = e ? atoi(e) : 0;
-    }
-    return v;
-}
-
 template <class Cfg, bool SCALED>
 static int launch_gemv_cfg(GemvParams p, const GemvScratch* ws, cudaStream_t stream, bool pdl)
 {
@@ -89,7 +67,7 @@ static int launch_gemv_cfg(GemvParams p, const GemvScratch* ws, cudaStream_t str
     const int budget = (Cfg::OCC == 2) ? (ws->smem_per_sm / 2 - 1024) : ws->max_smem;
     int ns = (budget - Cfg::HEADER_BYTES - Cfg::RED_BYTES) / Cfg::STAGE_BYTES;
     if (ns > Cfg::kMaxStages) { ns = Cfg::kMaxStages; }
-    if (ns < 1) { return -2; }
+    if (ns < 2) { return -2; }
     if (p.n_seg == 0)
     {
         // a single linear: describe it as a group of one
@@ -125,7 +103,6 @@ static int launch_gemv_cfg(GemvParams p, const GemvScratch* ws, cudaStream_t str
     // so nothing is exchanged between CTAs.  With fewer, the k range is split as well (stream-K).
     // Measured on B200: the exchange costs about 5 us of serial latency, one SM alone streams about
     // 45 GB/s; so the k range is only split when whole row blocks would leave most SMs idle for long.
-    const int align_mode = tuning_align();
     bool whole_blocks = true;
     {
         const double block_bytes = (double)Cfg::R * (double)((WT == DT_FP4) ? p.K / 2 + p.K / 16 : p.K);
@@ -135,7 +112,6 @@ static int launch_gemv_cfg(GemvParams p, const GemvScratch* ws, cudaStream_t str
         const double t_split = 5e-6 + (double)p.n_row_blocks * block_bytes / (sms * 40e9);
         whole_blocks = t_whole <= t_split || Cfg::MT > 1;    // large partial tiles make the exchange far dearer
     }
-    if (align_mode >= 0) { whole_blocks = align_mode == 1; }
     p.gran = whole_blocks ? p.n_kstages : 1u;
     const unsigned long long groups = total / p.gran;
     const unsigned int grid = (unsigned int)(groups < (unsigned long long)ws->sm_count ? groups : ws->sm_count);
@@ -212,32 +188,15 @@ static int launch_gemv_cfg(GemvParams p, const GemvScratch* ws, cudaStream_t str
 template <int WT, bool SCALED>
 static int launch_gemv(const GemvParams& p, const GemvScratch* ws, cudaStream_t stream, bool pdl)
 {
-    //                                                        WT MT RT WR WK SKS XB OCC
-    if (tuning_variant() == 1 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 1, 8, 32, 2, 1>, SCALED>(p, ws, stream, pdl); }
-    if (tuning_variant() == 3 && p.M <= 1) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 1, 8, 64, 1, 1>, SCALED>(p, ws, stream, pdl); }
-    if (tuning_variant() == 6 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 8, 8, 2, 1>, SCALED>(p, ws, stream, pdl); }
-    if (tuning_variant() == 7 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 1, 8, 16, 2, 1>, SCALED>(p, ws, stream, pdl); }
-    if (tuning_variant() == 8 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 1, 8, 32, 2, 1>, SCALED>(p, ws, stream, pdl); }
-    if (tuning_variant() == 4 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 8, 16, 2, 1>, SCALED>(p, ws, stream, pdl); }
-    if (tuning_variant() == 5 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 8, 32, 2, 1>, SCALED>(p, ws, stream, pdl); }
-    if (tuning_variant() == 2 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 1, 8, 16, 2, 2>, SCALED>(p, ws, stream, pdl); }
-    if (tuning_variant() == 14 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 16, 32, 2, 1>, SCALED>(p, ws, stream, pdl); }
-    if (tuning_variant() == 15 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 2, 8, 32, 2, 1>, SCALED>(p, ws, stream, pdl); }
-    if (tuning_variant() == 12 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 7, 32, 2, 2>, SCALED>(p, ws, stream, pdl); }
-    if (tuning_variant() == 13 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 7, 16, 2, 2>, SCALED>(p, ws, stream, pdl); }
-    if (tuning_variant() == 9 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 7, 14, 2, 2>, SCALED>(p, ws, stream, pdl); }
-    if (tuning_variant() == 10 && p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 1, 1, 7, 14, 2, 2>, SCALED>(p, ws, stream, pdl); }
+    // More tokens: more rows per CTA, so that the activation slice (re-read from L2 by every CTA) stays
+    // at or below the weight bytes it is multiplied with.
+    //                                              WT MT RT WR WK SKS XB OCC
     if (p.M <= 2) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 8, 32, 2, 1>, SCALED>(p, ws, stream, pdl); }
     if (p.M <= 8) { return launch_gemv_cfg<GemvCfg<WT, 1, 2, 1, 8, 16, 8, 1>, SCALED>(p, ws, stream, pdl); }
-    if (tuning_variant() == 11)
-    {
-        if (p.M <= 16) { return launch_gemv_cfg<GemvCfg<WT, 2, 2, 2, 4, 4, 16, 1>, SCALED>(p, ws, stream, pdl); }
-        return launch_gemv_cfg<GemvCfg<WT, 4, 2, 4, 2, 2, 32, 1>, SCALED>(p, ws, stream, pdl);
-    }
-    // more tokens: more rows per CTA, so that the activation slice (re-read from L2 by every CTA) stays
-    // at or below the weight bytes it is multiplied with
-    if (p.M <= 16) { return launch_gemv_cfg<GemvCfg<WT, 2, 4, 1, 8, 16, 16, 1>, SCALED>(p, ws, stream, pdl); }
-    return launch_gemv_cfg<GemvCfg<WT, 4, 2, 2, 4, 8, 32, 1>, SCALED>(p, ws, stream, pdl);
+    // (FP4 stages hold twice the elements per weight byte, so twice the activations: half the k steps)
+    constexpr int S16 = (WT == DT_FP4) ? 8 : 16, S32 = (WT == DT_FP4) ? 4 : 8;
+    if (p.M <= 16) { return launch_gemv_cfg<GemvCfg<WT, 2, 4, 1, 8, S16, 16, 1>, SCALED>(p, ws, stream, pdl); }
+    return launch_gemv_cfg<GemvCfg<WT, 4, 2, 2, 4, S32, 32, 1>, SCALED>(p, ws, stream, pdl);
 }
 
 template <int WT>
