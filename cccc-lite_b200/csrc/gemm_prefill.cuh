@@ -4,7 +4,7 @@
 // One CTA computes a tile of 128 output features x up to 256 tokens over the whole K range; two
 // CTAs share an SM (each owns 256 of the 512 TMEM columns), so one CTA's epilogue overlaps the
 // other's main loop.  Per 64-wide k block:
-//   * a TMA lane copies the BF16 activation tile [256 tokens][64 k] into shared memory with the
+//   * a TMA lane copies the BF16 activation tile [256 (or 128) tokens][64 k] into shared memory with the
 //     128-byte swizzle (token rows past M are zero-filled by the TMA),
 //   * eight warps load the quantised weight tile [128 features][64 k] from global memory (16 bytes
 //     per thread, prefetched one k block ahead), dequantise it to BF16 exactly as the reference's
@@ -29,17 +29,16 @@ namespace b200
 {
 
 constexpr int PF_BM = 128;          // output features per tile (UMMA M)
-constexpr int PF_BN = 256;          // tokens per tile (UMMA N, at most)
+constexpr int PF_BN_MAX = 256;      // tokens per tile (UMMA N): 256, or 128 when that fills the GPU better
 constexpr int PF_BK = 64;           // k per block: one 128-byte swizzle row of BF16
 constexpr int PF_STAGES = 2;
 constexpr int PF_DQ_WARPS = 8;      // dequantise, then epilogue
 constexpr int PF_THREADS = 32 * (PF_DQ_WARPS + 2);    // + TMA warp + MMA warp
 constexpr int PF_A_BYTES = PF_BM * PF_BK * 2;         // 16 KB
-constexpr int PF_X_BYTES = PF_BN * PF_BK * 2;         // 32 KB
-constexpr int PF_STAGE_BYTES = PF_A_BYTES + PF_X_BYTES;
 constexpr int PF_HEADER_BYTES = 1024;
-constexpr int PF_SMEM_BYTES = PF_HEADER_BYTES + PF_STAGES * PF_STAGE_BYTES + 1024;    // + slack for 1 KB alignment
-constexpr int PF_TMEM_COLS = 256;
+__host__ __device__ constexpr int pf_x_bytes(int bn) { return bn * PF_BK * 2; }                       // 32 KB at 256 tokens
+__host__ __device__ constexpr int pf_stage_bytes(int bn) { return PF_A_BYTES + pf_x_bytes(bn); }
+__host__ __device__ constexpr int pf_smem_bytes(int bn) { return PF_HEADER_BYTES + PF_STAGES * pf_stage_bytes(bn) + 1024; }    // + slack for 1 KB alignment
 
 struct PrefillParams
 {
@@ -154,7 +153,7 @@ __device__ __forceinline__ void dequant_fp4x16_natural(uint2 nib, uint32_t scale
 }
 
 // ---- the kernel ------------------------------------------------------------------------------------
-template <int WT, bool SCALED>
+template <int WT, bool SCALED, int BN>
 __global__ void __launch_bounds__(PF_THREADS, 2) gemm_wq_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const PrefillParams p)
 {
     extern __shared__ unsigned char pf_smem_raw[];
@@ -171,9 +170,10 @@ __global__ void __launch_bounds__(PF_THREADS, 2) gemm_wq_prefill_kernel(const __
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // token tiles vary fastest, so the CTAs that share a weight tile run together
     const unsigned int n0 = blockIdx.y * PF_BM;      // first output feature of the tile
-    const unsigned int m0 = blockIdx.x * PF_BN;      // first token of the tile
+    constexpr int PF_X_BYTES = pf_x_bytes(BN), PF_STAGE_BYTES = pf_stage_bytes(BN), PF_TMEM_COLS = BN;
+    const unsigned int m0 = blockIdx.x * BN;         // first token of the tile
     const unsigned int n_kblocks = p.K / PF_BK;
-    const unsigned int tile_tokens = min((unsigned int)PF_BN, p.M - m0);
+    const unsigned int tile_tokens = min((unsigned int)BN, p.M - m0);
     const unsigned int umma_n = (tile_tokens + 15u) & ~15u;
 
     if (threadIdx.x == 0)
@@ -354,9 +354,9 @@ __global__ void __launch_bounds__(PF_THREADS, 2) gemm_wq_prefill_kernel(const __
         if (ok && n_kblocks > 0)
         {
             const unsigned int quarter = warp & 3u;
-            const unsigned int half = warp >> 2;    // 0: columns [0,128), 1: [128,256)
+            const unsigned int half = warp >> 2;    // the two warps of a TMEM lane quarter split the token columns
             const unsigned int n = n0 + quarter * 32 + lane;
-            for (unsigned int c0 = half * 128; c0 < half * 128 + 128 && c0 < tile_tokens; c0 += 32)
+            for (unsigned int c0 = half * (BN / 2); c0 < half * (BN / 2) + BN / 2 && c0 < tile_tokens; c0 += 32)
             {
                 uint32_t r[32];
                 tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + c0, r);
@@ -404,35 +404,50 @@ inline bool prefill_supported(int w_type, unsigned int N, unsigned int M, unsign
     return (N + PF_BM - 1) / PF_BM <= 65535u;
 }
 
-template <int WT, bool SCALED>
-static int launch_prefill_t(const CUtensorMap& tmX, const PrefillParams& pp, int device, cudaStream_t stream)
+template <int WT, bool SCALED, int BN>
+static int launch_prefill_bn(const CUtensorMap& tmX, const PrefillParams& pp, int device, cudaStream_t stream)
 {
-    auto kernel = gemm_wq_prefill_kernel<WT, SCALED>;
+    auto kernel = gemm_wq_prefill_kernel<WT, SCALED, BN>;
     static bool attr_set[64] = {};
     if (!attr_set[device])
     {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM_BYTES) != cudaSuccess)
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_smem_bytes(BN)) != cudaSuccess)
         {
             report_launch("gemm_wq_bf16");
             return 1;
         }
         attr_set[device] = true;
     }
-    const dim3 grid((pp.M + PF_BN - 1) / PF_BN, (pp.N + PF_BM - 1) / PF_BM);
+    const dim3 grid((pp.M + BN - 1) / BN, (pp.N + PF_BM - 1) / PF_BM);
     count_launch();
-    kernel<<<grid, PF_THREADS, PF_SMEM_BYTES, stream>>>(tmX, pp);
+    kernel<<<grid, PF_THREADS, pf_smem_bytes(BN), stream>>>(tmX, pp);
     return report_launch("gemm_wq_bf16");
 }
 
-// Returns -2 when the shape has to go elsewhere.
-static int launch_prefill(int w_type, const GemvParams& p, int device, cudaStream_t stream)
+// 256-token tiles halve the weight conversions per flop; 128-token tiles are taken when the larger
+// tile would leave more than half of the 2-per-SM CTA slots empty (few output features, few tokens).
+static int pf_pick_bn(unsigned int N, unsigned int M, int sm_count)
 {
-    if (w_type == DT_FP4 && p.blk == nullptr) { return -2; }
+    const unsigned long long tiles256 = (unsigned long long)((M + 255) / 256) * ((N + PF_BM - 1) / PF_BM);
+    return (M <= 128 || tiles256 * 2 <= (unsigned long long)sm_count) ? 128 : 256;
+}
+
+template <int WT, bool SCALED>
+static int launch_prefill_t(const void* X, unsigned int ldx, const PrefillParams& pp, int device, int sm_count, cudaStream_t stream)
+{
+    const int bn = pf_pick_bn(pp.N, pp.M, sm_count);
     CUtensorMap tmX;
-    if (!make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.X, p.K, p.M, (unsigned long long)p.ldx * 2, PF_BK, PF_BN, true))
+    if (!make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, pp.K, pp.M, (unsigned long long)ldx * 2, PF_BK, (unsigned)bn, true))
     {
         return -2;
     }
+    return bn == 128 ? launch_prefill_bn<WT, SCALED, 128>(tmX, pp, device, stream) : launch_prefill_bn<WT, SCALED, 256>(tmX, pp, device, stream);
+}
+
+// Returns -2 when the shape has to go elsewhere.
+static int launch_prefill(int w_type, const GemvParams& p, int device, int sm_count, cudaStream_t stream)
+{
+    if (w_type == DT_FP4 && p.blk == nullptr) { return -2; }
     PrefillParams pp;
     memset(&pp, 0, sizeof(pp));
     pp.W = p.W;
@@ -450,18 +465,18 @@ static int launch_prefill(int w_type, const GemvParams& p, int device, cudaStrea
     pp.beta = p.beta;
     pp.post_scale = 1.0f;
     pp.out_f32 = p.out_f32;
-    if (w_type == DT_FP4) { return launch_prefill_t<DT_FP4, false>(tmX, pp, device, stream); }
+    if (w_type == DT_FP4) { return launch_prefill_t<DT_FP4, false>(p.X, p.ldx, pp, device, sm_count, stream); }
     int e = 0;
     const bool pow2 = p.w_scale > 0.f && !std::isinf(p.w_scale) && std::frexp(p.w_scale, &e) == 0.5f && e >= -39 && e <= 41;
     if (pow2)
     {
         pp.post_scale = p.w_scale;
         pp.w_scale = 1.0f;
-        return w_type == DT_E5M2 ? launch_prefill_t<DT_E5M2, false>(tmX, pp, device, stream)
-                                 : launch_prefill_t<DT_E4M3, false>(tmX, pp, device, stream);
+        return w_type == DT_E5M2 ? launch_prefill_t<DT_E5M2, false>(p.X, p.ldx, pp, device, sm_count, stream)
+                                 : launch_prefill_t<DT_E4M3, false>(p.X, p.ldx, pp, device, sm_count, stream);
     }
-    return w_type == DT_E5M2 ? launch_prefill_t<DT_E5M2, true>(tmX, pp, device, stream)
-                             : launch_prefill_t<DT_E4M3, true>(tmX, pp, device, stream);
+    return w_type == DT_E5M2 ? launch_prefill_t<DT_E5M2, true>(p.X, p.ldx, pp, device, sm_count, stream)
+                             : launch_prefill_t<DT_E4M3, true>(p.X, p.ldx, pp, device, sm_count, stream);
 }
 
 }    // namespace b200

@@ -299,7 +299,7 @@ static int run_linear_wq(const GemvScratch* ws, int w_type, const void* W, const
     }
     if (plan == PLAN_PREFILL)
     {
-        const int r = launch_prefill(w_type, p, ws->device, st);
+        const int r = launch_prefill(w_type, p, ws->device, ws->sm_count, st);
         if (r != -2) { return r; }
         plan = PLAN_PLAIN;
     }
