@@ -36,6 +36,7 @@ SYMBOLS = {
     "cuda_b200_allreduce_recv_bytes": (C.c_ulonglong, [_i, _u]),
     "cuda_b200_allreduce_flag_bytes": (C.c_ulonglong, [_i]),
     "cuda_b200_allreduce_counter_bytes": (C.c_ulonglong, []),
+    "cuda_argmax_bf16": (_i, [_vp, _u, _u, C.c_ulonglong, _vp, _vp, _vp]),
     "cuda_b200_launch_count": (C.c_ulonglong, []),
     "cuda_b200_version": (C.c_char_p, []),
 }
@@ -185,6 +186,14 @@ class PushAllReduce:
             stream = torch.cuda.current_stream().cuda_stream
         return lib().cuda_b200_allreduce_f32_to_bf16(self.recv_ptrs, self.flag_ptrs, _ptr(self.counters), _ptr(partial), _ptr(out),
                                                      n, self.n_max, self.rank, self.world, stream, flags)
+
+
+def argmax_bf16(logits, rows: int, cols: int, idx_out, val_out=None, ld: int | None = None, stream: int | None = None) -> int:
+    if stream is None:
+        import torch
+
+        stream = torch.cuda.current_stream().cuda_stream
+    return lib().cuda_argmax_bf16(_ptr(logits), rows, cols, cols if ld is None else ld, _ptr(idx_out), _ptr(val_out), stream)
 
 
 def launch_count() -> int:

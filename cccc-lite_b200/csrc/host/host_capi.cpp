@@ -109,3 +109,40 @@ HOST_EXPORT int cccc_host_bin_write(const char* path, int count, const char** ke
     for (int i = 0; i < count; i++) { w.add(keys[i], blobs[i], (size_t)lens[i]); }
     return w.save(path) ? 0 : -1;
 }
+
+// ---- decode-step linears ------------------------------------------------------------------------------
+#include "decode_linears.h"
+
+HOST_EXPORT void* cccc_host_decode_create(void* g, void* binfile, int hidden, int q_dim, int kv_dim, int ffn, int vocab, int layers,
+    int max_tokens, float a_attn, float a_mlp_in, float a_mlp_out, float a_head, char* err, int err_len)
+{
+    auto* d = new DecodeLinears();
+    ModelDims dims;
+    dims.hidden = hidden;
+    dims.q_dim = q_dim;
+    dims.kv_dim = kv_dim;
+    dims.ffn = ffn;
+    dims.vocab = vocab;
+    dims.layers = layers;
+    std::string e;
+    if (!d->load((GpuControl*)g, *(BinFile*)binfile, dims, max_tokens, 1, 0, &e))
+    {
+        if (err && err_len > 0)
+        {
+            std::strncpy(err, e.c_str(), (size_t)err_len - 1);
+            err[err_len - 1] = '\0';
+        }
+        delete d;
+        return nullptr;
+    }
+    d->setAlpha(a_attn, a_mlp_in, a_mlp_out, a_head);
+    return d;
+}
+HOST_EXPORT void cccc_host_decode_destroy(void* d) { delete (DecodeLinears*)d; }
+HOST_EXPORT int cccc_host_decode_step(void* d, const void* x_host, int M, int* ids, float* vals)
+{
+    return ((DecodeLinears*)d)->step((const uint16_t*)x_host, M, ids, vals);
+}
+HOST_EXPORT int cccc_host_decode_launches(void* d) { return ((DecodeLinears*)d)->launchesPerStep(); }
+HOST_EXPORT unsigned long long cccc_host_decode_weight_bytes(void* d) { return ((DecodeLinears*)d)->weightBytes(); }
+HOST_EXPORT void* cccc_host_decode_buffer(void* d, const char* name) { return ((DecodeLinears*)d)->buffer(name); }

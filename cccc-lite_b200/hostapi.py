@@ -35,6 +35,12 @@ SYMBOLS = {
     "cccc_host_bin_load_shard": (_i, [_vp, C.c_char_p, _i, _i, C.c_char, _i, _i, _vp, C.c_ulonglong, _vp, C.c_ulonglong,
                                       C.POINTER(C.c_float), C.POINTER(C.c_int), C.c_char_p, _i]),
     "cccc_host_bin_write": (_i, [C.c_char_p, _i, C.POINTER(C.c_char_p), C.POINTER(C.c_void_p), C.POINTER(C.c_ulonglong)]),
+    "cccc_host_decode_create": (_vp, [_vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _f, _f, C.c_char_p, _i]),
+    "cccc_host_decode_destroy": (None, [_vp]),
+    "cccc_host_decode_step": (_i, [_vp, _vp, _i, C.POINTER(C.c_int), C.POINTER(C.c_float)]),
+    "cccc_host_decode_launches": (_i, [_vp]),
+    "cccc_host_decode_weight_bytes": (C.c_ulonglong, [_vp]),
+    "cccc_host_decode_buffer": (_vp, [_vp, C.c_char_p]),
 }
 _lib = None
 

@@ -145,6 +145,17 @@ C_EXPORT unsigned long long cuda_b200_allreduce_recv_bytes(int world, unsigned i
 C_EXPORT unsigned long long cuda_b200_allreduce_flag_bytes(int world);
 C_EXPORT unsigned long long cuda_b200_allreduce_counter_bytes(void);
 
+/* ---- additions: the caller side of the path ---------------------------------------------------- */
+
+/* Greedy choice on the device: for each of `rows` rows of BF16 logits (row stride ld elements),
+ * idx_out[row] (int32) = index of the first maximum, val_out[row] (float32, may be NULL) = its value;
+ * NaN entries never win, a row of only NaN gives -1.  Replaces the per-token device-to-host copy of
+ * all V float logits that the reference's host sampler needs (cccc/Net.cpp:1783,
+ * cccc-llm/cccc-llm.cpp:181-343, which with temperature 0 returns the first maximum).
+ * Asynchronous on `stream`. */
+C_EXPORT int cuda_argmax_bf16(const void* logits, unsigned int rows, unsigned int cols, unsigned long long ld,
+    void* idx_out, void* val_out, void* stream);
+
 /* Tuning/diagnostic: returns which kernel cuda_gemm_wq_bf16 would pick for a shape
  * (0 = plain kernel, 1 = decode GEMV (M<=32), 2 = prefill tcgen05 GEMM) without launching. */
 C_EXPORT int cuda_gemm_wq_bf16_plan(int w_type, const void* W, const void* blk_scales, const void* X,
