@@ -1,9 +1,13 @@
 // Prefill-side quantized-weight linear (M > 32 tokens): a dense contraction on the 5th-generation
 // tensor cores (tcgen05.mma, accumulators in TMEM).
 //
-// One CTA computes a tile of 128 output features x up to 256 tokens over the whole K range; two
-// CTAs share an SM (each owns 256 of the 512 TMEM columns), so one CTA's epilogue overlaps the
-// other's main loop.  Per 64-wide k block:
+// One CTA computes a tile of 128 or 256 output features x up to 256 tokens over the whole K range.
+// With 128 features two CTAs share an SM (each owns part of the 512 TMEM columns), so one CTA's
+// epilogue overlaps the other's main loop.  The kernel is bound by shared-memory bandwidth: a 1-CTA
+// UMMA (M=128, N=256, K=16) reads 12 KB of operands per 128 cycles (96 B/clk) and the stage fills add
+// as much at full rate (activations 64 B/clk, converted weights 32 B/clk) against 128 B/clk per SM.
+// The 256-feature tile (one CTA per SM, all 512 TMEM columns, three stages) lets two weight tiles
+// share each activation tile, which cuts the fills to 64 B/clk.  Per 64-wide k block:
 //   * a TMA lane copies the BF16 activation tile [256 (or 128) tokens][64 k] into shared memory with the
 //     128-byte swizzle (token rows past M are zero-filled by the TMA),
 //   * eight warps load the quantised weight tile [128 features][64 k] from global memory (16 bytes
@@ -29,16 +33,20 @@ namespace b200
 {
 
 constexpr int PF_BM = 128;          // output features per tile (UMMA M)
-constexpr int PF_BN_MAX = 256;      // tokens per tile (UMMA N): 256, or 128 when that fills the GPU better
+constexpr int PF_BN_MAX = 512;      // tokens per tile: 512 (two N=256 UMMAs per A tile), 256, or 128
 constexpr int PF_BK = 64;           // k per block: one 128-byte swizzle row of BF16
-constexpr int PF_STAGES = 2;
+constexpr int PF_MAX_STAGES = 3;
 constexpr int PF_DQ_WARPS = 8;      // dequantise, then epilogue
 constexpr int PF_THREADS = 32 * (PF_DQ_WARPS + 2);    // + TMA warp + MMA warp
-constexpr int PF_A_BYTES = PF_BM * PF_BK * 2;         // 16 KB
+__host__ __device__ constexpr int pf_a_bytes(int fh) { return fh * PF_BM * PF_BK * 2; }    // 16 KB per 128 features
+__host__ __device__ constexpr int pf_stages(int fh) { return fh == 2 ? 3 : 2; }
 constexpr int PF_HEADER_BYTES = 1024;
 __host__ __device__ constexpr int pf_x_bytes(int bn) { return bn * PF_BK * 2; }                       // 32 KB at 256 tokens
-__host__ __device__ constexpr int pf_stage_bytes(int bn) { return PF_A_BYTES + pf_x_bytes(bn); }
-__host__ __device__ constexpr int pf_smem_bytes(int bn) { return PF_HEADER_BYTES + PF_STAGES * pf_stage_bytes(bn) + 1024; }    // + slack for 1 KB alignment
+__host__ __device__ constexpr int pf_stage_bytes(int bn, int fh) { return pf_a_bytes(fh) + pf_x_bytes(bn); }
+__host__ __device__ constexpr int pf_smem_bytes(int bn, int fh)
+{
+    return PF_HEADER_BYTES + pf_stages(fh) * pf_stage_bytes(bn, fh) + 1024;    // + slack for 1 KB alignment
+}
 
 struct PrefillParams
 {
@@ -153,28 +161,32 @@ __device__ __forceinline__ void dequant_fp4x16_natural(uint2 nib, uint32_t scale
 }
 
 // ---- the kernel ------------------------------------------------------------------------------------
-template <int WT, bool SCALED, int BN>
-__global__ void __launch_bounds__(PF_THREADS, 2) gemm_wq_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const PrefillParams p)
+template <int WT, bool SCALED, int BN, int FH>
+__global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm_wq_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const PrefillParams p)
 {
     extern __shared__ unsigned char pf_smem_raw[];
     // 1 KB alignment for the swizzled tiles
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* full_x = reinterpret_cast<uint64_t*>(smem);          // [PF_STAGES]
-    uint64_t* full_a = full_x + PF_STAGES;                         // [PF_STAGES]
-    uint64_t* empty = full_a + PF_STAGES;                          // [PF_STAGES]
-    uint64_t* acc_full = empty + PF_STAGES;                        // [1]
+    constexpr int PF_STAGES = pf_stages(FH);
+    constexpr int PF_A_BYTES = pf_a_bytes(FH);
+    uint64_t* full_x = reinterpret_cast<uint64_t*>(smem);          // [PF_MAX_STAGES]
+    uint64_t* full_a = full_x + PF_MAX_STAGES;                     // [PF_MAX_STAGES]
+    uint64_t* empty = full_a + PF_MAX_STAGES;                      // [PF_MAX_STAGES]
+    uint64_t* acc_full = empty + PF_MAX_STAGES;                    // [1]
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
     volatile unsigned int* abort_flag = reinterpret_cast<volatile unsigned int*>(tmem_base_slot + 1);
     unsigned char* stages = smem + PF_HEADER_BYTES;
 
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // token tiles vary fastest, so the CTAs that share a weight tile run together
-    const unsigned int n0 = blockIdx.y * PF_BM;      // first output feature of the tile
-    constexpr int PF_X_BYTES = pf_x_bytes(BN), PF_STAGE_BYTES = pf_stage_bytes(BN), PF_TMEM_COLS = BN;
+    const unsigned int n0 = blockIdx.y * (PF_BM * FH);    // first output feature of the tile
+    constexpr int PF_X_BYTES = pf_x_bytes(BN), PF_STAGE_BYTES = pf_stage_bytes(BN, FH), PF_TMEM_COLS = BN * FH;
+    static_assert(BN * FH <= 512, "TMEM has 512 columns");
     const unsigned int m0 = blockIdx.x * BN;         // first token of the tile
     const unsigned int n_kblocks = p.K / PF_BK;
     const unsigned int tile_tokens = min((unsigned int)BN, p.M - m0);
-    const unsigned int umma_n = (tile_tokens + 15u) & ~15u;
+    constexpr int NB = BN > 256 ? BN / 256 : 1;      // UMMAs (of up to 256 tokens) that share one A tile
+    constexpr int BNU = BN / NB;                     // tokens per UMMA
 
     if (threadIdx.x == 0)
     {
@@ -212,7 +224,12 @@ __global__ void __launch_bounds__(PF_THREADS, 2) gemm_wq_prefill_kernel(const __
                     break;
                 }
                 mbar_expect_tx(full_x + s, PF_X_BYTES);
-                tma_load_2d(stages + s * PF_STAGE_BYTES + PF_A_BYTES, &tmX, (int)(kb * PF_BK), (int)m0, full_x + s);
+#pragma unroll
+                for (int nb = 0; nb < NB; nb++)
+                {
+                    tma_load_2d(stages + s * PF_STAGE_BYTES + PF_A_BYTES + nb * (BNU * PF_BK * 2), &tmX, (int)(kb * PF_BK),
+                        (int)(m0 + nb * BNU), full_x + s);
+                }
                 mbar_arrive(full_x + s);
                 issued = kb + 1;
             }
@@ -229,7 +246,6 @@ __global__ void __launch_bounds__(PF_THREADS, 2) gemm_wq_prefill_kernel(const __
         // =========================== MMA lane ===========================
         if (lane == 0)
         {
-            const uint32_t idesc = umma_idesc_bf16(PF_BM, umma_n);
             bool ok = true;
             for (unsigned int kb = 0; kb < n_kblocks && ok; kb++)
             {
@@ -246,11 +262,24 @@ __global__ void __launch_bounds__(PF_THREADS, 2) gemm_wq_prefill_kernel(const __
                 const uint32_t a_addr = smem_u32(stages + s * PF_STAGE_BYTES);
                 const uint32_t b_addr = a_addr + PF_A_BYTES;
 #pragma unroll
-                for (int k = 0; k < PF_BK / 16; k++)
+                for (int nb = 0; nb < NB; nb++)
                 {
-                    // 16 k = 32 bytes further along the 128-byte swizzle row
-                    umma_bf16(tmem_base, umma_desc_kmajor_sw128(a_addr + k * 32), umma_desc_kmajor_sw128(b_addr + k * 32), idesc,
-                        (kb | (unsigned int)k) != 0 ? 1u : 0u);
+                    if (tile_tokens <= (unsigned int)(nb * BNU)) { break; }    // no live token in this part
+                    const unsigned int live = min((unsigned int)BNU, tile_tokens - nb * BNU);
+                    const uint32_t idesc = umma_idesc_bf16(PF_BM, (live + 15u) & ~15u);
+#pragma unroll
+                    for (int k = 0; k < PF_BK / 16; k++)
+                    {
+#pragma unroll
+                        for (int fh = 0; fh < FH; fh++)
+                        {
+                            // 16 k = 32 bytes further along the 128-byte swizzle row; the second 128-feature
+                            // tile sits 16 KB further in the A stage and accumulates BN columns further in TMEM
+                            umma_bf16(tmem_base + fh * BN + nb * BNU, umma_desc_kmajor_sw128(a_addr + fh * (PF_BM * PF_BK * 2) + k * 32),
+                                umma_desc_kmajor_sw128(b_addr + nb * (BNU * PF_BK * 2) + k * 32), idesc,
+                                (kb | (unsigned int)k) != 0 ? 1u : 0u);
+                        }
+                    }
                 }
                 umma_commit(empty + s);
             }
@@ -265,56 +294,64 @@ __global__ void __launch_bounds__(PF_THREADS, 2) gemm_wq_prefill_kernel(const __
     {
         // =========================== dequantise, then epilogue (warps 0..7) ===========================
         const unsigned int tid = threadIdx.x;    // 0..255
-        // two (row, 16-element group) pieces per thread per k block
-        unsigned int prow[2], pq[2];
+        // 2*FH (row, 16-element group) pieces per thread per k block
+        constexpr int NP = 2 * FH;
+        unsigned int prow[NP], pq[NP];
 #pragma unroll
-        for (int i = 0; i < 2; i++)
+        for (int i = 0; i < NP; i++)
         {
             const unsigned int piece = tid + 256u * i;
             prow[i] = piece >> 2;
             pq[i] = piece & 3u;
         }
-        uint4 raw8[2];          // FP8: 16 bytes per piece
-        uint2 raw4[2];          // FP4: 8 bytes per piece
-        uint32_t rawsc[2];      // FP4: the piece's block scale
-        auto load_raw = [&](unsigned int kb) {
+        // raw weight bytes of two k blocks in flight (kb and kb+1): one L2 latency is about one k block
+        uint4 raw8[2][NP];      // [slot][piece] FP8: 16 bytes per piece
+        uint2 raw4[2][NP];      // FP4: 8 bytes per piece
+        uint32_t rawsc[2][NP];  // FP4: the piece's block scale
+        auto load_raw = [&](unsigned int kb, int slot) {
 #pragma unroll
-            for (int i = 0; i < 2; i++)
+            for (int i = 0; i < NP; i++)
             {
                 const unsigned int n = n0 + prow[i];
-                raw8[i] = make_uint4(0, 0, 0, 0);
-                raw4[i] = make_uint2(0, 0);
-                rawsc[i] = 0;
+                raw8[slot][i] = make_uint4(0, 0, 0, 0);
+                raw4[slot][i] = make_uint2(0, 0);
+                rawsc[slot][i] = 0;
                 if (n < p.N)
                 {
                     const size_t e = (size_t)n * p.ldw + (size_t)kb * PF_BK + pq[i] * 16;
                     if (WT == DT_FP4)
                     {
-                        raw4[i] = __ldg(reinterpret_cast<const uint2*>(p.W + e / 2));
-                        rawsc[i] = __ldg(p.blk + e / 16);
+                        raw4[slot][i] = __ldg(reinterpret_cast<const uint2*>(p.W + e / 2));
+                        rawsc[slot][i] = __ldg(p.blk + e / 16);
                     }
-                    else { raw8[i] = __ldg(reinterpret_cast<const uint4*>(p.W + e)); }
+                    else { raw8[slot][i] = __ldg(reinterpret_cast<const uint4*>(p.W + e)); }
                 }
             }
         };
         bool ok = true;
-        if (n_kblocks > 0) { load_raw(0); }
-        for (unsigned int kb = 0; kb < n_kblocks; kb++)
-        {
-            const unsigned int s = kb % PF_STAGES;
-            uint32_t out[2][8];
+        if (n_kblocks > 0) { load_raw(0, 0); }
+        if (n_kblocks > 1) { load_raw(1, 1); }
+        auto convert_and_refill = [&](unsigned int kb, int slot, uint32_t (&out)[NP][8]) {
 #pragma unroll
-            for (int i = 0; i < 2; i++)
+            for (int i = 0; i < NP; i++)
             {
-                if (WT == DT_FP4) { dequant_fp4x16_natural(raw4[i], rawsc[i], out[i]); }
+                if (WT == DT_FP4) { dequant_fp4x16_natural(raw4[slot][i], rawsc[slot][i], out[i]); }
                 else
                 {
-                    const uint32_t w[4] = { raw8[i].x, raw8[i].y, raw8[i].z, raw8[i].w };
+                    const uint32_t w[4] = { raw8[slot][i].x, raw8[slot][i].y, raw8[slot][i].z, raw8[slot][i].w };
 #pragma unroll
                     for (int j = 0; j < 4; j++) { dequant_fp8x4<WT, SCALED>(w[j], p.w_scale, out[i][2 * j], out[i][2 * j + 1]); }
                 }
             }
-            if (kb + 1 < n_kblocks) { load_raw(kb + 1); }    // in flight while this block is stored and multiplied
+            if (kb + 2 < n_kblocks) { load_raw(kb + 2, slot); }    // in flight for two k blocks
+        };
+        for (unsigned int kb = 0; kb < n_kblocks; kb++)
+        {
+            const unsigned int s = kb % PF_STAGES;
+            uint32_t out[NP][8];
+            // the slot index must be a compile-time constant for the arrays to stay in registers
+            if ((kb & 1u) == 0) { convert_and_refill(kb, 0, out); }
+            else { convert_and_refill(kb, 1, out); }
             if (ok && kb >= PF_STAGES && (*abort_flag != 0 || !mbar_wait_bounded(empty + s, ((kb / PF_STAGES) - 1) & 1u)))
             {
                 ok = false;
@@ -328,7 +365,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) gemm_wq_prefill_kernel(const __
             {
                 const uint32_t a_addr = smem_u32(stages + s * PF_STAGE_BYTES);
 #pragma unroll
-                for (int i = 0; i < 2; i++)
+                for (int i = 0; i < NP; i++)
                 {
                     // row r, 16-byte chunks 2q and 2q+1 of its 128-byte row, XOR-swizzled by (r & 7)
                     const uint32_t rowaddr = a_addr + prow[i] * 128;
@@ -355,33 +392,37 @@ __global__ void __launch_bounds__(PF_THREADS, 2) gemm_wq_prefill_kernel(const __
         {
             const unsigned int quarter = warp & 3u;
             const unsigned int half = warp >> 2;    // the two warps of a TMEM lane quarter split the token columns
-            const unsigned int n = n0 + quarter * 32 + lane;
-            for (unsigned int c0 = half * (BN / 2); c0 < half * (BN / 2) + BN / 2 && c0 < tile_tokens; c0 += 32)
-            {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + c0, r);
-                tmem_ld_wait();
-                if (n < p.N)
-                {
 #pragma unroll
-                    for (int j = 0; j < 32; j++)
+            for (int fh = 0; fh < FH; fh++)
+            {
+                const unsigned int n = n0 + fh * PF_BM + quarter * 32 + lane;
+                for (unsigned int c0 = half * (BN / 2); c0 < half * (BN / 2) + BN / 2 && c0 < tile_tokens; c0 += 32)
+                {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + fh * BN + c0, r);
+                    tmem_ld_wait();
+                    if (n < p.N)
                     {
-                        const unsigned int m = m0 + c0 + j;
-                        if (c0 + j < tile_tokens)
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
                         {
-                            const long long yi = (long long)m * p.ldy_m + (long long)n * p.ldy_n;
-                            float o = p.alpha * (__uint_as_float(r[j]) * p.post_scale);
-                            if (p.out_f32)
+                            const unsigned int m = m0 + c0 + j;
+                            if (c0 + j < tile_tokens)
                             {
-                                float* y = reinterpret_cast<float*>(p.Y) + yi;
-                                if (p.beta != 0.f) { o += p.beta * *y; }
-                                *y = o;
-                            }
-                            else
-                            {
-                                uint16_t* y = p.Y + yi;
-                                if (p.beta != 0.f) { o += p.beta * bf16_bits_to_float(*y); }
-                                *y = __bfloat16_as_ushort(__float2bfloat16_rn(o));
+                                const long long yi = (long long)m * p.ldy_m + (long long)n * p.ldy_n;
+                                float o = p.alpha * (__uint_as_float(r[j]) * p.post_scale);
+                                if (p.out_f32)
+                                {
+                                    float* y = reinterpret_cast<float*>(p.Y) + yi;
+                                    if (p.beta != 0.f) { o += p.beta * *y; }
+                                    *y = o;
+                                }
+                                else
+                                {
+                                    uint16_t* y = p.Y + yi;
+                                    if (p.beta != 0.f) { o += p.beta * bf16_bits_to_float(*y); }
+                                    *y = __bfloat16_as_ushort(__float2bfloat16_rn(o));
+                                }
                             }
                         }
                     }
@@ -401,47 +442,60 @@ inline bool prefill_supported(int w_type, unsigned int N, unsigned int M, unsign
     (void)ldy_n;
     (void)w_type;
     if (M <= 32 || K == 0 || (K % PF_BK) != 0 || (ldx % 8) != 0 || (ldw % 16) != 0) { return false; }
-    return (N + PF_BM - 1) / PF_BM <= 65535u;
+    return (N + PF_BM - 1) / PF_BM <= 65535u;    // grid.y
 }
 
-template <int WT, bool SCALED, int BN>
+template <int WT, bool SCALED, int BN, int FH>
 static int launch_prefill_bn(const CUtensorMap& tmX, const PrefillParams& pp, int device, cudaStream_t stream)
 {
-    auto kernel = gemm_wq_prefill_kernel<WT, SCALED, BN>;
+    auto kernel = gemm_wq_prefill_kernel<WT, SCALED, BN, FH>;
     static bool attr_set[64] = {};
     if (!attr_set[device])
     {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_smem_bytes(BN)) != cudaSuccess)
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_smem_bytes(BN, FH)) != cudaSuccess)
         {
             report_launch("gemm_wq_bf16");
             return 1;
         }
         attr_set[device] = true;
     }
-    const dim3 grid((pp.M + BN - 1) / BN, (pp.N + PF_BM - 1) / PF_BM);
+    const dim3 grid((pp.M + BN - 1) / BN, (pp.N + PF_BM * FH - 1) / (PF_BM * FH));
     count_launch();
-    kernel<<<grid, PF_THREADS, pf_smem_bytes(BN), stream>>>(tmX, pp);
+    kernel<<<grid, PF_THREADS, pf_smem_bytes(BN, FH), stream>>>(tmX, pp);
     return report_launch("gemm_wq_bf16");
 }
 
 // 256-token tiles halve the weight conversions per flop; 128-token tiles are taken when the larger
 // tile would leave more than half of the 2-per-SM CTA slots empty (few output features, few tokens).
-static int pf_pick_bn(unsigned int N, unsigned int M, int sm_count)
+static int pf_pick_bn(unsigned int N, unsigned int M, unsigned int K, int sm_count)
 {
-    const unsigned long long tiles256 = (unsigned long long)((M + 255) / 256) * ((N + PF_BM - 1) / PF_BM);
-    return (M <= 128 || tiles256 * 2 <= (unsigned long long)sm_count) ? 128 : 256;
+    const unsigned long long ftiles = (N + PF_BM - 1) / PF_BM;
+    const unsigned long long tiles256 = (unsigned long long)((M + 255) / 256) * ftiles;
+    const unsigned long long tiles512 = (unsigned long long)((M + 511) / 512) * ftiles;
+    if (M <= 128 || tiles256 * 2 <= (unsigned long long)sm_count) { return 128; }
+    // 256 features x 256 tokens per CTA (one CTA per SM, the activation tile shared by two weight
+    // tiles) when that still fills most of the SMs; -256 encodes it
+    (void)tiles512;
+    const unsigned long long tiles_wide = (unsigned long long)((M + 255) / 256) * ((N + 2 * PF_BM - 1) / (2 * PF_BM));
+    // Measured at M=2048: K=12288 1107 vs 1066 TFLOP/s for it, K=4096 861 vs 964 against it (its
+    // prologue and epilogue are not hidden by a second CTA), so it is taken for long K only.
+    if (K >= 8192 && tiles_wide * 10 >= (unsigned long long)sm_count * 8) { return -256; }
+    return 256;
 }
 
 template <int WT, bool SCALED>
 static int launch_prefill_t(const void* X, unsigned int ldx, const PrefillParams& pp, int device, int sm_count, cudaStream_t stream)
 {
-    const int bn = pf_pick_bn(pp.N, pp.M, sm_count);
+    const int bn = pf_pick_bn(pp.N, pp.M, pp.K, sm_count);
     CUtensorMap tmX;
-    if (!make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, pp.K, pp.M, (unsigned long long)ldx * 2, PF_BK, (unsigned)bn, true))
+    if (!make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, pp.K, pp.M, (unsigned long long)ldx * 2, PF_BK,
+            (unsigned)(bn == 128 ? 128 : 256), true))
     {
         return -2;
     }
-    return bn == 128 ? launch_prefill_bn<WT, SCALED, 128>(tmX, pp, device, stream) : launch_prefill_bn<WT, SCALED, 256>(tmX, pp, device, stream);
+    if (bn == -256) { return launch_prefill_bn<WT, SCALED, 256, 2>(tmX, pp, device, stream); }
+    return bn == 128 ? launch_prefill_bn<WT, SCALED, 128, 1>(tmX, pp, device, stream)
+                     : launch_prefill_bn<WT, SCALED, 256, 1>(tmX, pp, device, stream);
 }
 
 // Returns -2 when the shape has to go elsewhere.

@@ -31,7 +31,7 @@ def run(wt, W, blk, inv, X, N, M, K, **kw):
 
 @pytest.mark.parametrize("wt", WTS)
 @pytest.mark.parametrize("N,K,M", [(128, 64, 33), (128, 256, 64), (256, 512, 256), (384, 1024, 300), (200, 320, 257),
-                                   (1024, 4096, 512)])
+                                   (1024, 4096, 512), (15300, 128, 600), (2500, 8192, 300)])
 def test_prefill_small_shapes_match_oracle(wt, N, K, M):
     c = capi()
     W, blk, inv, X = O.make_inputs(wt, N, K, M, seed=N + M, scaled=True)
