@@ -60,6 +60,12 @@ def lib() -> C.CDLL:
     global _lib
     if _lib is None:
         if not os.path.exists(LIB_PATH):
+            # not a fallback: the CUDA library is the only implementation; build it or fail
+            import subprocess
+            import sys
+
+            subprocess.check_call([sys.executable, os.path.join(HERE, "build.py")])
+        if not os.path.exists(LIB_PATH):
             raise RuntimeError(f"{LIB_PATH} is missing: build it with `python cccc-lite_b200/build.py`")
         L = C.CDLL(LIB_PATH)
         for name, (res, args) in SYMBOLS.items():
