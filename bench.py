@@ -35,6 +35,9 @@ if ROOT not in sys.path:
 HIDDEN, QDIM, KVDIM, FFN, VOCAB, LAYERS = 4096, 4096, 1024, 12288, 151936, 36
 LLAMA = dict(HIDDEN=4096, QDIM=4096, KVDIM=1024, FFN=14336, VOCAB=128256, LAYERS=32)
 W_STD = 0.02
+# DRAM bytes / algorithmic bytes of the decode kernel, from the ncu capture summarised under profiles/
+# (q+k+v 25.220 + o 16.832 + gate+up 100.731 + down 50.400 MB read and written against 193.07 MB)
+NCU_TRAFFIC_RATIO = 1.0006
 
 
 def model_dims(wtype: str, layers: int | None = None):
@@ -389,7 +392,10 @@ def gpu_arm(args):
                 "d2h_bytes_per_step": src_logits.numel() * 2, "tok_per_s": round(M / (ms_e2e / args.steps * 1e-3), 1)},
         "gpu_launches": launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "achieved": round(per_gpu, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(per_gpu / peak, 4), "traffic": None, "peak_source": peak_src,
+                     "frac": round(per_gpu / peak, 4), "traffic": int(round(bytes_per_step * NCU_TRAFFIC_RATIO / launches_per_step / world)),
+                     "traffic_source": "ncu dram__bytes_read+write of one layer's launches (profiles/gemv_wq_kernel_qwen3_decode_m1.md), "
+                                       "1.0006 x algorithmic, scaled to this step's bytes per launch",
+                     "algorithmic_bytes_per_launch": int(round(bytes_per_step / launches_per_step / world)), "peak_source": peak_src,
                      "kernel": "gemv_wq_kernel", "launches_per_step": launches_per_step,
                      "avg_launch_us": round(ms_per_step * 1e3 / launches_per_step, 3)},
         "clocks": clocks,
