@@ -58,6 +58,8 @@ struct PrefillParams
     long long ldy_m, ldy_n;
     float w_scale, alpha, beta, post_scale;
     unsigned int out_f32;
+    unsigned int y_tma;    // 1: the epilogue stages BF16 tiles in shared memory and writes them with TMA stores
+    unsigned int dbg;
 };
 
 // ---- tcgen05 wrappers --------------------------------------------------------------------------------
@@ -134,6 +136,20 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
         : "memory");
 }
+// 2-D tiled TMA store shared -> global; rows and columns past the tensor's extent are clipped.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(c0), "r"(c1),
+                 "r"(smem_u32(src))
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit_and_wait_read()
+{
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void sts16(uint32_t addr, uint16_t v) { asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(v) : "memory"); }
+__device__ __forceinline__ void bar_sync_named(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
 {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
@@ -162,7 +178,7 @@ __device__ __forceinline__ void dequant_fp4x16_natural(uint2 nib, uint32_t scale
 
 // ---- the kernel ------------------------------------------------------------------------------------
 template <int WT, bool SCALED, int BN, int FH>
-__global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm_wq_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const PrefillParams p)
+__global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm_wq_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY, const PrefillParams p)
 {
     extern __shared__ unsigned char pf_smem_raw[];
     // 1 KB alignment for the swizzled tiles
@@ -223,6 +239,7 @@ __global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm
                     *abort_flag = 1;
                     break;
                 }
+                if (p.dbg & 2u) { mbar_arrive(full_x + s); issued = kb + 1; continue; }
                 mbar_expect_tx(full_x + s, PF_X_BYTES);
 #pragma unroll
                 for (int nb = 0; nb < NB; nb++)
@@ -264,6 +281,7 @@ __global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm
 #pragma unroll
                 for (int nb = 0; nb < NB; nb++)
                 {
+                    if (p.dbg & 4u) { break; }
                     if (tile_tokens <= (unsigned int)(nb * BNU)) { break; }    // no live token in this part
                     const unsigned int live = min((unsigned int)BNU, tile_tokens - nb * BNU);
                     const uint32_t idesc = umma_idesc_bf16(PF_BM, (live + 15u) & ~15u);
@@ -343,15 +361,15 @@ __global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm
                     for (int j = 0; j < 4; j++) { dequant_fp8x4<WT, SCALED>(w[j], p.w_scale, out[i][2 * j], out[i][2 * j + 1]); }
                 }
             }
-            if (kb + 2 < n_kblocks) { load_raw(kb + 2, slot); }    // in flight for two k blocks
+            if (kb + 2 < n_kblocks && !(p.dbg & 8u)) { load_raw(kb + 2, slot); }    // in flight for two k blocks
         };
+        // The conversion of block kb+1 is issued between the stores of block kb and their proxy fence,
+        // so the fence finds the stores already performed.
+        uint32_t out[NP][8];
+        if (n_kblocks > 0) { convert_and_refill(0, 0, out); }
         for (unsigned int kb = 0; kb < n_kblocks; kb++)
         {
             const unsigned int s = kb % PF_STAGES;
-            uint32_t out[NP][8];
-            // the slot index must be a compile-time constant for the arrays to stay in registers
-            if ((kb & 1u) == 0) { convert_and_refill(kb, 0, out); }
-            else { convert_and_refill(kb, 1, out); }
             if (ok && kb >= PF_STAGES && (*abort_flag != 0 || !mbar_wait_bounded(empty + s, ((kb / PF_STAGES) - 1) & 1u)))
             {
                 ok = false;
@@ -373,6 +391,15 @@ __global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm
                     sts128(rowaddr + (((2 * pq[i]) ^ sw) << 4), out[i][0], out[i][1], out[i][2], out[i][3]);
                     sts128(rowaddr + (((2 * pq[i] + 1) ^ sw) << 4), out[i][4], out[i][5], out[i][6], out[i][7]);
                 }
+            }
+            if (kb + 1 < n_kblocks)
+            {
+                // the slot index must be a compile-time constant for the arrays to stay in registers
+                if ((kb & 1u) != 0) { convert_and_refill(kb + 1, 0, out); }
+                else { convert_and_refill(kb + 1, 1, out); }
+            }
+            if (ok)
+            {
                 fence_proxy_async();    // make the generic-proxy stores visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) { mbar_arrive(full_a + s); }
@@ -388,7 +415,38 @@ __global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm
         }
         if (*abort_flag != 0) { ok = false; }
         tc_fence_after();
-        if (ok && n_kblocks > 0)
+        if (ok && n_kblocks > 0 && p.y_tma != 0)
+        {
+            // BF16 tile [BN tokens][128 features] per feature half in the (now idle) stage memory,
+            // then one TMA store per half; the store clips rows past M and features past N
+            const unsigned int quarter = warp & 3u;
+            const unsigned int half = warp >> 2;
+#pragma unroll
+            for (int fh = 0; fh < FH; fh++)
+            {
+                const uint32_t ytile = smem_u32(stages) + fh * (BN * PF_BM * 2) + (quarter * 32 + lane) * 2;
+                for (unsigned int c0 = half * (BN / 2); c0 < half * (BN / 2) + BN / 2 && c0 < tile_tokens; c0 += 32)
+                {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + fh * BN + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                    {
+                        sts16(ytile + (c0 + j) * (PF_BM * 2), __bfloat16_as_ushort(__float2bfloat16_rn(p.alpha * (__uint_as_float(r[j]) * p.post_scale))));
+                    }
+                }
+            }
+            fence_proxy_async();
+            bar_sync_named(1, 32 * PF_DQ_WARPS);
+            if (tid == 0)
+            {
+#pragma unroll
+                for (int fh = 0; fh < FH; fh++) { tma_store_2d(&tmY, stages + fh * (BN * PF_BM * 2), (int)(n0 + fh * PF_BM), (int)m0); }
+                tma_store_commit_and_wait_read();
+            }
+        }
+        else if (ok && n_kblocks > 0 && !(p.dbg & 64u))
         {
             const unsigned int quarter = warp & 3u;
             const unsigned int half = warp >> 2;    // the two warps of a TMEM lane quarter split the token columns
@@ -446,7 +504,7 @@ inline bool prefill_supported(int w_type, unsigned int N, unsigned int M, unsign
 }
 
 template <int WT, bool SCALED, int BN, int FH>
-static int launch_prefill_bn(const CUtensorMap& tmX, const PrefillParams& pp, int device, cudaStream_t stream)
+static int launch_prefill_bn(const CUtensorMap& tmX, const CUtensorMap& tmY, const PrefillParams& pp, int device, cudaStream_t stream)
 {
     auto kernel = gemm_wq_prefill_kernel<WT, SCALED, BN, FH>;
     static bool attr_set[64] = {};
@@ -461,76 +519,8 @@ static int launch_prefill_bn(const CUtensorMap& tmX, const PrefillParams& pp, in
     }
     const dim3 grid((pp.M + BN - 1) / BN, (pp.N + PF_BM * FH - 1) / (PF_BM * FH));
     count_launch();
-    kernel<<<grid, PF_THREADS, pf_smem_bytes(BN, FH), stream>>>(tmX, pp);
+    kernel<<<grid, PF_THREADS, pf_smem_bytes(BN, FH), stream>>>(tmX, tmY, pp);
     return report_launch("gemm_wq_bf16");
-}
-
-// 256-token tiles halve the weight conversions per flop; 128-token tiles are taken when the larger
-// tile would leave more than half of the 2-per-SM CTA slots empty (few output features, few tokens).
-static int pf_pick_bn(unsigned int N, unsigned int M, unsigned int K, int sm_count)
-{
-    const unsigned long long ftiles = (N + PF_BM - 1) / PF_BM;
-    const unsigned long long tiles256 = (unsigned long long)((M + 255) / 256) * ftiles;
-    const unsigned long long tiles512 = (unsigned long long)((M + 511) / 512) * ftiles;
-    if (M <= 128 || tiles256 * 2 <= (unsigned long long)sm_count) { return 128; }
-    // 256 features x 256 tokens per CTA (one CTA per SM, the activation tile shared by two weight
-    // tiles) when that still fills most of the SMs; -256 encodes it
-    (void)tiles512;
-    const unsigned long long tiles_wide = (unsigned long long)((M + 255) / 256) * ((N + 2 * PF_BM - 1) / (2 * PF_BM));
-    // Measured at M=2048: K=12288 1107 vs 1066 TFLOP/s for it, K=4096 861 vs 964 against it (its
-    // prologue and epilogue are not hidden by a second CTA), so it is taken for long K only.
-    if (K >= 8192 && tiles_wide * 10 >= (unsigned long long)sm_count * 8) { return -256; }
-    return 256;
-}
-
-template <int WT, bool SCALED>
-static int launch_prefill_t(const void* X, unsigned int ldx, const PrefillParams& pp, int device, int sm_count, cudaStream_t stream)
-{
-    const int bn = pf_pick_bn(pp.N, pp.M, pp.K, sm_count);
-    CUtensorMap tmX;
-    if (!make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, pp.K, pp.M, (unsigned long long)ldx * 2, PF_BK,
-            (unsigned)(bn == 128 ? 128 : 256), true))
-    {
-        return -2;
-    }
-    if (bn == -256) { return launch_prefill_bn<WT, SCALED, 256, 2>(tmX, pp, device, stream); }
-    return bn == 128 ? launch_prefill_bn<WT, SCALED, 128, 1>(tmX, pp, device, stream)
-                     : launch_prefill_bn<WT, SCALED, 256, 1>(tmX, pp, device, stream);
-}
-
-// Returns -2 when the shape has to go elsewhere.
-static int launch_prefill(int w_type, const GemvParams& p, int device, int sm_count, cudaStream_t stream)
-{
-    if (w_type == DT_FP4 && p.blk == nullptr) { return -2; }
-    PrefillParams pp;
-    memset(&pp, 0, sizeof(pp));
-    pp.W = p.W;
-    pp.blk = p.blk;
-    pp.Y = p.Y;
-    pp.status = p.status;
-    pp.N = p.N;
-    pp.M = p.M;
-    pp.K = p.K;
-    pp.ldw = p.ldw;
-    pp.ldy_m = p.ldy_m;
-    pp.ldy_n = p.ldy_n;
-    pp.w_scale = p.w_scale;
-    pp.alpha = p.alpha;
-    pp.beta = p.beta;
-    pp.post_scale = 1.0f;
-    pp.out_f32 = p.out_f32;
-    if (w_type == DT_FP4) { return launch_prefill_t<DT_FP4, false>(p.X, p.ldx, pp, device, sm_count, stream); }
-    int e = 0;
-    const bool pow2 = p.w_scale > 0.f && !std::isinf(p.w_scale) && std::frexp(p.w_scale, &e) == 0.5f && e >= -39 && e <= 41;
-    if (pow2)
-    {
-        pp.post_scale = p.w_scale;
-        pp.w_scale = 1.0f;
-        return w_type == DT_E5M2 ? launch_prefill_t<DT_E5M2, false>(p.X, p.ldx, pp, device, sm_count, stream)
-                                 : launch_prefill_t<DT_E4M3, false>(p.X, p.ldx, pp, device, sm_count, stream);
-    }
-    return w_type == DT_E5M2 ? launch_prefill_t<DT_E5M2, true>(p.X, p.ldx, pp, device, sm_count, stream)
-                             : launch_prefill_t<DT_E4M3, true>(p.X, p.ldx, pp, device, sm_count, stream);
 }
 
 }    // namespace b200

@@ -6,7 +6,7 @@
 #include "common.cuh"
 #include "gemv_decode.cuh"
 #include "tensor_map.cuh"
-#include "gemm_prefill.cuh"
+#include "prefill_launch.cuh"
 
 #include <cmath>
 #include <cstdlib>
