@@ -421,27 +421,35 @@ def gpu_arm(args):
 
 
 def prefill_probe(torch, capi, dims, wtype, dev, peaks):
-    """BASELINE config 4 in brief: M=2048 tokens through one layer's seven linears (tcgen05 kernel),
-    timed with CUDA events; reported next to the decode line as TFLOP/s of 2*M*N*K."""
+    """BASELINE config 4 in brief: M=2048 tokens through one layer's seven linears (tcgen05 kernels),
+    q/k/v and gate/up as grouped calls on their shared input, timed with CUDA events; reported next to
+    the decode line as TFLOP/s of 2*M*N*K."""
     M = 2048
     wt = capi.FP4_E2M1 if wtype == "fp4" else capi.FP8_E5M2
     g = torch.Generator(device=dev).manual_seed(7)
-    mats = []
+    calls = []    # (K, X, group, n_members)
     flops = 0.0
+    by_input = {}
     for name, N, K, _, _ in layer_linears(dims):
-        nb = N * K // 2 if wtype == "fp4" else N * K
-        W = torch.randint(0, 120, (nb,), dtype=torch.uint8, device=dev, generator=g)
-        S = torch.randint(1, 8, (N * K // 16,), dtype=torch.uint8, device=dev, generator=g) if wtype == "fp4" else None
+        key = "attn_in" if name in ("q", "k", "v") else ("mlp_in" if name in ("gate", "up") else name)
+        by_input.setdefault(key, (K, []))[1].append(N)
+    for key, (K, Ns) in by_input.items():
         X = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
-        Y = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
-        mats.append((N, K, W, S, X, Y))
-        flops += 2.0 * M * N * K
+        members = []
+        for N in Ns:
+            nb = N * K // 2 if wtype == "fp4" else N * K
+            W = torch.randint(0, 120, (nb,), dtype=torch.uint8, device=dev, generator=g)
+            S = torch.randint(1, 8, (N * K // 16,), dtype=torch.uint8, device=dev, generator=g) if wtype == "fp4" else None
+            members.append(dict(W=W, S=S, Y=torch.zeros(M, N, dtype=torch.bfloat16, device=dev), N=N, inv=0.37))
+            flops += 2.0 * M * N * K
+        calls.append((K, X, capi.make_group(members, K), members))
 
     def layer():
-        for N, K, W, S, X, Y in mats:
-            if capi.gemm_wq_bf16(wt, W, S, 0.37, X, Y, N, M, K) != 0:
+        for K, X, grp, _ in calls:
+            if capi.gemm_wq_bf16_group(wt, grp, X, M, K) != 0:
                 raise RuntimeError("prefill linear failed")
 
+    before = capi.launch_count()
     for _ in range(3):
         layer()
     torch.cuda.synchronize(dev)
@@ -452,12 +460,16 @@ def prefill_probe(torch, capi, dims, wtype, dev, peaks):
         layer()
     e1.record()
     torch.cuda.synchronize(dev)
+    launches = capi.launch_count() - before
+    if capi.check_error("prefill probe") != 0:
+        raise RuntimeError("prefill probe failed")
     ms = e0.elapsed_time(e1) / reps
     tf = flops / ms / 1e9
     peak = float(peaks.get("bf16_tflops", 1590.0))
-    return {"workload": "one layer's seven linears, M=2048 tokens", "ms_per_layer": round(ms, 4), "tflops": round(tf, 1),
-            "peak_tflops": peak, "frac": round(tf / peak, 4), "peak_source": "measured" if "bf16_tflops" in peaks else "fallback",
-            "kernel": "gemm_wq_prefill_kernel (tcgen05)", "launches": 7 * (reps + 3)}
+    return {"workload": "one layer's seven linears as four calls (q+k+v, o, gate+up, down), M=2048 tokens", "ms_per_layer": round(ms, 4),
+            "tflops": round(tf, 1), "peak_tflops": peak, "frac": round(tf / peak, 4),
+            "peak_source": "measured" if "bf16_tflops" in peaks else "fallback",
+            "kernel": "gemm_wq_prefill_pair_kernel (tcgen05, cta_group::2)", "launches": launches}
 
 
 # ---- the CPU arm -------------------------------------------------------------------------------------

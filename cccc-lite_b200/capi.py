@@ -19,6 +19,11 @@ FLAG_PDL = 1
 FLAG_CHECKED = 2  # cuda_gemm_wq_bf16_static only
 FLAG_OUT_F32 = 4  # Y is float32 (partial sums of a row-parallel shard)
 
+
+def flag_prefill_variant(v):
+    """flags bits 8-10 of cuda_gemm_wq_bf16: tile shape of the M > 32 path (0 = chosen by shape)."""
+    return (int(v) & 7) << 8
+
 _vp, _u, _f, _i = C.c_void_p, C.c_uint, C.c_float, C.c_int
 
 # name -> (restype, argtypes): every symbol include/cccc_cuda_b200.h declares

@@ -39,27 +39,46 @@ constexpr int PF_MAX_STAGES = 3;
 constexpr int PF_DQ_WARPS = 8;      // dequantise, then epilogue
 constexpr int PF_THREADS = 32 * (PF_DQ_WARPS + 2);    // + TMA warp + MMA warp
 __host__ __device__ constexpr int pf_a_bytes(int fh) { return fh * PF_BM * PF_BK * 2; }    // 16 KB per 128 features
-__host__ __device__ constexpr int pf_stages(int fh) { return fh == 2 ? 3 : 2; }
+// two CTAs of the 128-feature tiles share an SM: 2 x 2 x 48 KB at 256 tokens, 2 x 3 x 32 KB at 128 tokens
+__host__ __device__ constexpr int pf_stages(int bn, int fh) { return (fh == 2 || bn <= 128) ? 3 : 2; }
 constexpr int PF_HEADER_BYTES = 1024;
 __host__ __device__ constexpr int pf_x_bytes(int bn) { return bn * PF_BK * 2; }                       // 32 KB at 256 tokens
 __host__ __device__ constexpr int pf_stage_bytes(int bn, int fh) { return pf_a_bytes(fh) + pf_x_bytes(bn); }
 __host__ __device__ constexpr int pf_smem_bytes(int bn, int fh)
 {
-    return PF_HEADER_BYTES + pf_stages(fh) * pf_stage_bytes(bn, fh) + 1024;    // + slack for 1 KB alignment
+    return PF_HEADER_BYTES + pf_stages(bn, fh) * pf_stage_bytes(bn, fh) + 1024;    // + slack for 1 KB alignment
 }
 
-struct PrefillParams
+constexpr int PF_MAX_GROUP = 3;    // linears that share their activations in one launch (q/k/v, gate/up)
+
+// One linear of a launch.  Its feature tiles are blockIdx.y = tile0 .. tile0 + tiles - 1.
+struct PrefillSeg
 {
     const uint8_t* W;
     const uint8_t* blk;
     uint16_t* Y;
-    unsigned int* status;
-    unsigned int N, M, K, ldw;
     long long ldy_m, ldy_n;
+    unsigned int N, ldw, tile0;
     float w_scale, alpha, beta, post_scale;
-    unsigned int out_f32;
     unsigned int y_tma;    // 1: the epilogue stages BF16 tiles in shared memory and writes them with TMA stores
-    unsigned int dbg;
+};
+
+struct PrefillParams
+{
+    PrefillSeg seg[PF_MAX_GROUP];
+    unsigned int n_seg;
+    unsigned int* status;
+    unsigned int M, K;
+    unsigned int out_f32;
+#ifdef B200_TRACE
+    unsigned long long* trace;    // debug builds only: [rank][role 0..15][k block 0..255] timestamps of CTA pair (0, 0)
+#endif
+};
+
+// The three output tensor maps of a launch (unused ones are zero).
+struct PrefillYMaps
+{
+    CUtensorMap m[PF_MAX_GROUP];
 };
 
 // ---- tcgen05 wrappers --------------------------------------------------------------------------------
@@ -148,6 +167,17 @@ __device__ __forceinline__ void tma_store_commit_and_wait_read()
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
+// True in exactly one lane of the (converged) warp, the same lane every time.
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void sts16(uint32_t addr, uint16_t v) { asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(v) : "memory"); }
 __device__ __forceinline__ void bar_sync_named(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
@@ -178,12 +208,12 @@ __device__ __forceinline__ void dequant_fp4x16_natural(uint2 nib, uint32_t scale
 
 // ---- the kernel ------------------------------------------------------------------------------------
 template <int WT, bool SCALED, int BN, int FH>
-__global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm_wq_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY, const PrefillParams p)
+__global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm_wq_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ PrefillYMaps tmY, const PrefillParams p)
 {
     extern __shared__ unsigned char pf_smem_raw[];
     // 1 KB alignment for the swizzled tiles
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) & ~(uintptr_t)1023);
-    constexpr int PF_STAGES = pf_stages(FH);
+    constexpr int PF_STAGES = pf_stages(BN, FH);
     constexpr int PF_A_BYTES = pf_a_bytes(FH);
     uint64_t* full_x = reinterpret_cast<uint64_t*>(smem);          // [PF_MAX_STAGES]
     uint64_t* full_a = full_x + PF_MAX_STAGES;                     // [PF_MAX_STAGES]
@@ -195,7 +225,12 @@ __global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm
 
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // token tiles vary fastest, so the CTAs that share a weight tile run together
-    const unsigned int n0 = blockIdx.y * (PF_BM * FH);    // first output feature of the tile
+    // which linear of the launch this feature tile belongs to
+    unsigned int si = 0;
+    if (p.n_seg > 1 && blockIdx.y >= p.seg[1].tile0) { si = 1; }
+    if (p.n_seg > 2 && blockIdx.y >= p.seg[2].tile0) { si = 2; }
+    const PrefillSeg& g = p.seg[si];
+    const unsigned int n0 = (blockIdx.y - g.tile0) * (PF_BM * FH);    // first output feature of the tile
     constexpr int PF_X_BYTES = pf_x_bytes(BN), PF_STAGE_BYTES = pf_stage_bytes(BN, FH), PF_TMEM_COLS = BN * FH;
     static_assert(BN * FH <= 512, "TMEM has 512 columns");
     const unsigned int m0 = blockIdx.x * BN;         // first token of the tile
@@ -239,7 +274,6 @@ __global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm
                     *abort_flag = 1;
                     break;
                 }
-                if (p.dbg & 2u) { mbar_arrive(full_x + s); issued = kb + 1; continue; }
                 mbar_expect_tx(full_x + s, PF_X_BYTES);
 #pragma unroll
                 for (int nb = 0; nb < NB; nb++)
@@ -260,8 +294,9 @@ __global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm
     }
     else if (warp == PF_DQ_WARPS + 1)
     {
-        // =========================== MMA lane ===========================
-        if (lane == 0)
+        // =========================== MMA warp ===========================
+        // The whole warp runs the loop (waits and descriptor arithmetic stay warp-uniform); one
+        // elected lane issues the UMMAs and the commits.
         {
             bool ok = true;
             for (unsigned int kb = 0; kb < n_kblocks && ok; kb++)
@@ -271,17 +306,21 @@ __global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm
                 if (*abort_flag != 0 || !mbar_wait_bounded(full_x + s, par) || !mbar_wait_bounded(full_a + s, par))
                 {
                     ok = false;
-                    atomicMax(p.status, (unsigned int)ST_TIMEOUT_FULL);
-                    *abort_flag = 1;
+                    if (lane == 0)
+                    {
+                        atomicMax(p.status, (unsigned int)ST_TIMEOUT_FULL);
+                        *abort_flag = 1;
+                    }
                     break;
                 }
                 tc_fence_after();
                 const uint32_t a_addr = smem_u32(stages + s * PF_STAGE_BYTES);
                 const uint32_t b_addr = a_addr + PF_A_BYTES;
+                if (elect_one())
+                {
 #pragma unroll
                 for (int nb = 0; nb < NB; nb++)
                 {
-                    if (p.dbg & 4u) { break; }
                     if (tile_tokens <= (unsigned int)(nb * BNU)) { break; }    // no live token in this part
                     const unsigned int live = min((unsigned int)BNU, tile_tokens - nb * BNU);
                     const uint32_t idesc = umma_idesc_bf16(PF_BM, (live + 15u) & ~15u);
@@ -300,11 +339,17 @@ __global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm
                     }
                 }
                 umma_commit(empty + s);
+                }
+                __syncwarp();
             }
-            if (ok) { umma_commit(acc_full); }
-            else
+            __syncwarp();
+            if (elect_one())
             {
-                mbar_arrive(acc_full);    // let the epilogue warps fall through; they see the abort flag
+                if (ok) { umma_commit(acc_full); }
+                else
+                {
+                    mbar_arrive(acc_full);    // let the epilogue warps fall through; they see the abort flag
+                }
             }
         }
     }
@@ -334,15 +379,15 @@ __global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm
                 raw8[slot][i] = make_uint4(0, 0, 0, 0);
                 raw4[slot][i] = make_uint2(0, 0);
                 rawsc[slot][i] = 0;
-                if (n < p.N)
+                if (n < g.N)
                 {
-                    const size_t e = (size_t)n * p.ldw + (size_t)kb * PF_BK + pq[i] * 16;
+                    const size_t e = (size_t)n * g.ldw + (size_t)kb * PF_BK + pq[i] * 16;
                     if (WT == DT_FP4)
                     {
-                        raw4[slot][i] = __ldg(reinterpret_cast<const uint2*>(p.W + e / 2));
-                        rawsc[slot][i] = __ldg(p.blk + e / 16);
+                        raw4[slot][i] = __ldg(reinterpret_cast<const uint2*>(g.W + e / 2));
+                        rawsc[slot][i] = __ldg(g.blk + e / 16);
                     }
-                    else { raw8[slot][i] = __ldg(reinterpret_cast<const uint4*>(p.W + e)); }
+                    else { raw8[slot][i] = __ldg(reinterpret_cast<const uint4*>(g.W + e)); }
                 }
             }
         };
@@ -358,10 +403,10 @@ __global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm
                 {
                     const uint32_t w[4] = { raw8[slot][i].x, raw8[slot][i].y, raw8[slot][i].z, raw8[slot][i].w };
 #pragma unroll
-                    for (int j = 0; j < 4; j++) { dequant_fp8x4<WT, SCALED>(w[j], p.w_scale, out[i][2 * j], out[i][2 * j + 1]); }
+                    for (int j = 0; j < 4; j++) { dequant_fp8x4<WT, SCALED>(w[j], g.w_scale, out[i][2 * j], out[i][2 * j + 1]); }
                 }
             }
-            if (kb + 2 < n_kblocks && !(p.dbg & 8u)) { load_raw(kb + 2, slot); }    // in flight for two k blocks
+            if (kb + 2 < n_kblocks) { load_raw(kb + 2, slot); }    // in flight for two k blocks
         };
         // The conversion of block kb+1 is issued between the stores of block kb and their proxy fence,
         // so the fence finds the stores already performed.
@@ -415,7 +460,7 @@ __global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm
         }
         if (*abort_flag != 0) { ok = false; }
         tc_fence_after();
-        if (ok && n_kblocks > 0 && p.y_tma != 0)
+        if (ok && n_kblocks > 0 && g.y_tma != 0)
         {
             // BF16 tile [BN tokens][128 features] per feature half in the (now idle) stage memory,
             // then one TMA store per half; the store clips rows past M and features past N
@@ -433,7 +478,7 @@ __global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm
 #pragma unroll
                     for (int j = 0; j < 32; j++)
                     {
-                        sts16(ytile + (c0 + j) * (PF_BM * 2), __bfloat16_as_ushort(__float2bfloat16_rn(p.alpha * (__uint_as_float(r[j]) * p.post_scale))));
+                        sts16(ytile + (c0 + j) * (PF_BM * 2), __bfloat16_as_ushort(__float2bfloat16_rn(g.alpha * (__uint_as_float(r[j]) * g.post_scale))));
                     }
                 }
             }
@@ -442,11 +487,11 @@ __global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm
             if (tid == 0)
             {
 #pragma unroll
-                for (int fh = 0; fh < FH; fh++) { tma_store_2d(&tmY, stages + fh * (BN * PF_BM * 2), (int)(n0 + fh * PF_BM), (int)m0); }
+                for (int fh = 0; fh < FH; fh++) { tma_store_2d(&tmY.m[si], stages + fh * (BN * PF_BM * 2), (int)(n0 + fh * PF_BM), (int)m0); }
                 tma_store_commit_and_wait_read();
             }
         }
-        else if (ok && n_kblocks > 0 && !(p.dbg & 64u))
+        else if (ok && n_kblocks > 0)
         {
             const unsigned int quarter = warp & 3u;
             const unsigned int half = warp >> 2;    // the two warps of a TMEM lane quarter split the token columns
@@ -459,7 +504,7 @@ __global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm
                     uint32_t r[32];
                     tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + fh * BN + c0, r);
                     tmem_ld_wait();
-                    if (n < p.N)
+                    if (n < g.N)
                     {
 #pragma unroll
                         for (int j = 0; j < 32; j++)
@@ -467,18 +512,18 @@ __global__ void __launch_bounds__(PF_THREADS, (BN > 256 || FH > 1) ? 1 : 2) gemm
                             const unsigned int m = m0 + c0 + j;
                             if (c0 + j < tile_tokens)
                             {
-                                const long long yi = (long long)m * p.ldy_m + (long long)n * p.ldy_n;
-                                float o = p.alpha * (__uint_as_float(r[j]) * p.post_scale);
+                                const long long yi = (long long)m * g.ldy_m + (long long)n * g.ldy_n;
+                                float o = g.alpha * (__uint_as_float(r[j]) * g.post_scale);
                                 if (p.out_f32)
                                 {
-                                    float* y = reinterpret_cast<float*>(p.Y) + yi;
-                                    if (p.beta != 0.f) { o += p.beta * *y; }
+                                    float* y = reinterpret_cast<float*>(g.Y) + yi;
+                                    if (g.beta != 0.f) { o += g.beta * *y; }
                                     *y = o;
                                 }
                                 else
                                 {
-                                    uint16_t* y = p.Y + yi;
-                                    if (p.beta != 0.f) { o += p.beta * bf16_bits_to_float(*y); }
+                                    uint16_t* y = g.Y + yi;
+                                    if (g.beta != 0.f) { o += g.beta * bf16_bits_to_float(*y); }
                                     *y = __bfloat16_as_ushort(__float2bfloat16_rn(o));
                                 }
                             }
@@ -504,7 +549,8 @@ inline bool prefill_supported(int w_type, unsigned int N, unsigned int M, unsign
 }
 
 template <int WT, bool SCALED, int BN, int FH>
-static int launch_prefill_bn(const CUtensorMap& tmX, const CUtensorMap& tmY, const PrefillParams& pp, int device, cudaStream_t stream)
+static int launch_prefill_bn(const CUtensorMap& tmX, const PrefillYMaps& tmY, const PrefillParams& pp, unsigned int feature_tiles, int device,
+    cudaStream_t stream)
 {
     auto kernel = gemm_wq_prefill_kernel<WT, SCALED, BN, FH>;
     static bool attr_set[64] = {};
@@ -517,7 +563,7 @@ static int launch_prefill_bn(const CUtensorMap& tmX, const CUtensorMap& tmY, con
         }
         attr_set[device] = true;
     }
-    const dim3 grid((pp.M + BN - 1) / BN, (pp.N + PF_BM * FH - 1) / (PF_BM * FH));
+    const dim3 grid((pp.M + BN - 1) / BN, feature_tiles);
     count_launch();
     kernel<<<grid, PF_THREADS, pf_smem_bytes(BN, FH), stream>>>(tmX, tmY, pp);
     return report_launch("gemm_wq_bf16");

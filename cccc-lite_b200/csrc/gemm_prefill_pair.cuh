@@ -1,22 +1,25 @@
 // Prefill-side quantized-weight linear on CTA pairs (tcgen05.mma with cta_group::2).
 //
-// Two CTAs on the two SMs of a TPC form a cluster and compute 256*FH output features x up to 256
-// tokens over the whole K range.  Each CTA converts the weight tiles of its own 128*FH features and
-// loads HALF of the token tile; one lane of the leader CTA (cluster rank 0) issues UMMAs of
-// M=256, N=tokens, K=16 that read the A rows of both CTAs and the B rows of both halves, and each
-// CTA's tensor core accumulates its own 128 features in its own TMEM.  Against the one-CTA kernel
-// this halves the activation bytes each SM copies into and reads out of shared memory per flop,
-// which is the bound of that kernel (see gemm_prefill.cuh).
+// Two CTAs on the two SMs of a TPC form a cluster and compute 256*FH output features x up to 256*TH
+// tokens over the whole K range (FH*TH <= 2: 512 TMEM columns per CTA).  Each CTA converts the weight
+// tiles of its own 128*FH features and loads HALF of every 256-token tile; one lane of the leader CTA
+// (cluster rank 0) issues UMMAs of M=256, N=tokens, K=16 that read the A rows of both CTAs and the B
+// rows of both halves, and each CTA's tensor core accumulates its own 128 features in its own TMEM.
+// Against the one-CTA kernel a CTA stages half the activation bytes per flop, and with TH=2 also
+// converts half the weights per flop, so four stages of 1024 tensor cycles each fit in shared memory:
+// enough to cover the latency of the activation loads and of the barrier round trips.
 //
 // Per 64-wide k block and CTA:
-//   * the TMA lane copies [128 tokens][64 k] BF16 activations (swizzle 128 B, rows past M zero),
+//   * the TMA lane copies TH x [128 tokens][64 k] BF16 activations (swizzle 128 B, rows past M zero),
 //   * eight warps dequantise [128*FH features][64 k] weights into the swizzled A stage,
-//   * rank 1 forwards "my stage is full" to a barrier of the leader (remote mbarrier arrive),
-//   * the leader issues 4*FH UMMAs and commits to the stage's "empty" barrier of BOTH CTAs.
-// After the last k block each CTA reads its accumulator (tcgen05.ld) and stores its features.
+//   * one lane of rank 1 forwards "my stage is full" to a barrier of the leader with ONE remote
+//     arrive (remote arrives from all eight warps, or activation copies that complete on the
+//     leader's barrier, measured 40 % slower),
+//   * the leader issues 4*FH*TH UMMAs and commits to the stage's "empty" barrier of BOTH CTAs.
+// After the last k block each CTA reads its accumulators (tcgen05.ld) and stores its features.
 // Every mbarrier wait is bounded; a CTA whose wait ran out raises the status word and drains.  Both
 // CTAs always reach the cluster barrier before the TMEM columns are freed, so neither leaves while
-// the other may still read its shared memory.
+// the other may still read its shared memory or signal its barriers.
 #pragma once
 
 #include "gemm_prefill.cuh"
@@ -24,11 +27,18 @@
 namespace b200
 {
 
-constexpr int PP_TOKENS = 256;    // tokens per CTA pair (UMMA N)
-constexpr int PP_HALF = 128;      // tokens each CTA stages
-__host__ __device__ constexpr int pp_stages(int fh) { return fh == 2 ? 4 : 3; }
-__host__ __device__ constexpr int pp_stage_bytes(int fh) { return pf_a_bytes(fh) + PP_HALF * PF_BK * 2; }
-__host__ __device__ constexpr int pp_smem_bytes(int fh) { return PF_HEADER_BYTES + pp_stages(fh) * pp_stage_bytes(fh) + 1024; }
+constexpr int PP_TOKENS = 256;    // tokens per UMMA of the pair (UMMA N)
+constexpr int PP_HALF = 128;      // tokens each CTA stages per UMMA
+constexpr int PP_XH_BYTES = PP_HALF * PF_BK * 2;    // 16 KB
+// The converted weights and the activations have rings of their own: the activation copies have the
+// longer latency (L2 and the copy itself) and get the deeper ring.  224 KB per SM in all three shapes.
+__host__ __device__ constexpr int pp_a_stages(int fh, int th) { return fh * th == 2 ? 4 : 3; }
+__host__ __device__ constexpr int pp_x_stages(int fh, int th) { return fh * th == 1 ? 3 : (fh == 2 ? 6 : 5); }
+__host__ __device__ constexpr int pp_ring_bytes(int fh, int th)
+{
+    return pp_a_stages(fh, th) * pf_a_bytes(fh) + pp_x_stages(fh, th) * th * PP_XH_BYTES;
+}
+__host__ __device__ constexpr int pp_smem_bytes(int fh, int th) { return PF_HEADER_BYTES + pp_ring_bytes(fh, th) + 1024; }
 
 // ---- cluster / cta_group::2 wrappers ------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_cta_rank()
@@ -42,12 +52,20 @@ __device__ __forceinline__ void cluster_sync_all()
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Arrive on the barrier at the same shared-memory offset in CTA `rank` of the cluster.
-__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank)
+// shared::cluster address of the object at the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank)
 {
     uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(rank));
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(p)), "r"(rank));
+    return remote;
+}
+// Arrive on a barrier of another CTA of the cluster.  The default semantics (release at CTA scope)
+// are what the data path needs: the shared-memory stores this orders were already made visible to
+// the async proxy by their writers before they arrived on the local barrier, and a release at
+// cluster scope measured 600 ns per arrive.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr)
+{
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity)
 {
@@ -104,150 +122,207 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar)
 }
 
 // ---- the kernel ------------------------------------------------------------------------------------
-template <int WT, bool SCALED, int FH>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, FH > 1 ? 1 : 2)
-    gemm_wq_prefill_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY, const PrefillParams p)
+template <int WT, bool SCALED, int FH, int TH, int DQW>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH * TH > 1 ? 1 : 2)
+    gemm_wq_prefill_pair_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ PrefillYMaps tmY, const PrefillParams p)
 {
     extern __shared__ unsigned char pf_smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) & ~(uintptr_t)1023);
-    constexpr int ST = pp_stages(FH);
+    static_assert(FH * TH <= 2, "512 TMEM columns");
+    static_assert(DQW == 8 || DQW == 16, "dequantise warps: two or four per TMEM lane quarter");
+    constexpr int NA = pp_a_stages(FH, TH), NX = pp_x_stages(FH, TH);
     constexpr int A_BYTES = pf_a_bytes(FH);
-    constexpr int X_BYTES = PP_HALF * PF_BK * 2;
-    constexpr int STAGE_BYTES = pp_stage_bytes(FH);
-    constexpr int TMEM_COLS = PP_TOKENS * FH;
-    uint64_t* full_x = reinterpret_cast<uint64_t*>(smem);    // [ST] my activation half has landed
-    uint64_t* full_a = full_x + 4;                           // [ST] my weight tile is converted
-    uint64_t* peer_full = full_a + 4;                        // [ST] leader only: rank 1's stage is full
-    uint64_t* empty = peer_full + 4;                         // [ST] the UMMAs that read the stage are done
-    uint64_t* acc_full = empty + 4;                          // [1]
+    constexpr int X_BYTES = TH * PP_XH_BYTES;
+    static_assert(FH * TH * PP_TOKENS * PF_BM * 2 <= pp_ring_bytes(FH, TH), "the epilogue tiles reuse the ring memory");
+    constexpr int TMEM_COLS = PP_TOKENS * FH * TH;
+    uint64_t* full_x = reinterpret_cast<uint64_t*>(smem);    // [NX] my activation halves have landed
+    uint64_t* empty_x = full_x + 8;                          // [NX] the UMMAs that read the activation stage are done
+    uint64_t* full_a = empty_x + 8;                          // [NA] my weight tile is converted
+    uint64_t* empty_a = full_a + 8;                          // [NA] the UMMAs that read the weight stage are done
+    uint64_t* peer_full = empty_a + 8;                       // [8] leader only: rank 1 has both operands of k block kb (slot kb % 8)
+    uint64_t* acc_full = peer_full + 8;                      // [1]
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
     volatile unsigned int* abort_flag = reinterpret_cast<volatile unsigned int*>(tmem_base_slot + 1);
-    unsigned char* stages = smem + PF_HEADER_BYTES;
-    static_assert(ST <= 4, "barrier arrays hold four stages");
+    unsigned char* stages = smem + PF_HEADER_BYTES;    // weight ring, then activation ring
+    unsigned char* xring = stages + NA * A_BYTES;
+    static_assert(NA <= 8 && NX <= 8, "barrier arrays hold eight stages");
 
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_cta_rank();
-    const unsigned int m0 = (blockIdx.x >> 1) * PP_TOKENS;            // first token of the pair's tile
-    const unsigned int n0 = blockIdx.y * (2 * PF_BM * FH);            // first feature of the pair's tile
+#ifdef B200_TRACE
+#define PP_STAMP(role, kb) do { if (p.trace && blockIdx.x < 2 && blockIdx.y == 0 && (kb) < 256u && (threadIdx.x & 31u) == 0) { p.trace[(rank * 16 + (role)) * 256 + (kb)] = global_timer_ns(); } } while (0)
+#else
+#define PP_STAMP(role, kb) do { } while (0)
+#endif
+    const unsigned int m0 = (blockIdx.x >> 1) * (PP_TOKENS * TH);     // first token of the pair's tile
+    // which linear of the launch this feature tile belongs to
+    unsigned int si = 0;
+    if (p.n_seg > 1 && blockIdx.y >= p.seg[1].tile0) { si = 1; }
+    if (p.n_seg > 2 && blockIdx.y >= p.seg[2].tile0) { si = 2; }
+    const PrefillSeg& g = p.seg[si];
+    const unsigned int n0 = (blockIdx.y - g.tile0) * (2 * PF_BM * FH);    // first feature of the pair's tile
     const unsigned int n_kblocks = p.K / PF_BK;
-    const unsigned int tile_tokens = min((unsigned int)PP_TOKENS, p.M - m0);
-    const unsigned int live = (tile_tokens + 15u) & ~15u;             // UMMA N; each CTA supplies live/2 token rows
-    const unsigned int my_tok0 = m0 + rank * (live / 2);
+    const unsigned int tile_tokens = min((unsigned int)(PP_TOKENS * TH), p.M - m0);
+    // UMMA N of each 256-token part (0: no live token); each CTA supplies live/2 token rows of it
+    unsigned int live[TH];
+#pragma unroll
+    for (int th = 0; th < TH; th++)
+    {
+        const unsigned int t = tile_tokens > (unsigned int)(th * PP_TOKENS) ? min((unsigned int)PP_TOKENS, tile_tokens - th * PP_TOKENS) : 0u;
+        live[th] = (t + 15u) & ~15u;
+    }
 
     if (threadIdx.x == 0)
     {
-        for (int s = 0; s < ST; s++)
+        for (int s = 0; s < NX; s++)
         {
             mbar_init(full_x + s, 1);
-            mbar_init(full_a + s, PF_DQ_WARPS);
-            mbar_init(peer_full + s, 1);
-            mbar_init(empty + s, 1);
+            mbar_init(empty_x + s, 1);
         }
+        for (int s = 0; s < NA; s++)
+        {
+            mbar_init(full_a + s, DQW);
+            mbar_init(empty_a + s, 1);
+        }
+        for (int s = 0; s < 8; s++) { mbar_init(peer_full + s, 1); }
         mbar_init(acc_full, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == PF_DQ_WARPS + 1) { tmem_alloc_pair(tmem_base_slot, TMEM_COLS); }
+    if (warp == DQW + 1) { tmem_alloc_pair(tmem_base_slot, TMEM_COLS); }
     tc_fence_before();
     __syncthreads();
-    cluster_sync_all();    // both CTAs' barriers exist before any remote arrive or commit
+    cluster_sync_all();    // both CTAs' barriers exist before any remote arrive, copy or commit
     tc_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
 
-    if (warp == PF_DQ_WARPS)
+    if (warp == DQW)
     {
-        // =========================== TMA lane: my half of the activations ===========================
+        // =========================== TMA lane: my halves of the activations ===========================
         if (lane == 0)
         {
             bool ok = true;
             unsigned int issued = 0;
             for (unsigned int kb = 0; kb < n_kblocks; kb++)
             {
-                const unsigned int s = kb % ST;
-                if (kb >= ST && (*abort_flag != 0 || !mbar_wait_bounded(empty + s, ((kb / ST) - 1) & 1u)))
+                const unsigned int s = kb % NX;
+                if (kb >= NX && (*abort_flag != 0 || !mbar_wait_bounded(empty_x + s, ((kb / NX) - 1) & 1u)))
                 {
                     ok = false;
                     atomicMax(p.status, (unsigned int)ST_TIMEOUT_EMPTY);
                     *abort_flag = 1;
                     break;
                 }
+                PP_STAMP(0, kb);
                 mbar_expect_tx(full_x + s, X_BYTES);
-                tma_load_2d(stages + s * STAGE_BYTES + A_BYTES, &tmX, (int)(kb * PF_BK), (int)my_tok0, full_x + s);
+#pragma unroll
+                for (int th = 0; th < TH; th++)
+                {
+                    // a part without live tokens is still copied (zero fill) so that the byte count is fixed
+                    tma_load_2d(xring + s * X_BYTES + th * PP_XH_BYTES, &tmX, (int)(kb * PF_BK),
+                        (int)(m0 + th * PP_TOKENS + rank * (live[th] / 2)), full_x + s);
+                }
                 mbar_arrive(full_x + s);
+                PP_STAMP(1, kb);
                 issued = kb + 1;
             }
             if (!ok)
             {
-                const unsigned int first = issued > ST ? issued - ST : 0;
-                for (unsigned int kb = first; kb < issued; kb++) { mbar_wait_bounded(full_x + (kb % ST), (kb / ST) & 1u); }
+                // wait (bounded) for my copies in flight before the CTA may leave
+                const unsigned int first = issued > NX ? issued - NX : 0;
+                for (unsigned int kb = first; kb < issued; kb++) { mbar_wait_bounded(full_x + (kb % NX), (kb / NX) & 1u); }
             }
         }
     }
-    else if (warp == PF_DQ_WARPS + 1)
+    else if (warp == DQW + 1)
     {
         if (lane == 0 && rank != 0)
         {
             // =========================== rank 1: forward "stage full" to the leader ===========================
+            const uint32_t peer_bar0 = map_to_cta(peer_full, 0);
             for (unsigned int kb = 0; kb < n_kblocks; kb++)
             {
-                const unsigned int s = kb % ST;
-                const uint32_t par = (kb / ST) & 1u;
-                if (*abort_flag != 0 || !mbar_wait_bounded(full_x + s, par) || !mbar_wait_bounded(full_a + s, par))
+                bool w = *abort_flag == 0 && mbar_wait_bounded(full_x + (kb % NX), (kb / NX) & 1u);
+                w = w && mbar_wait_bounded(full_a + (kb % NA), (kb / NA) & 1u);
+                if (!w)
                 {
                     atomicMax(p.status, (unsigned int)ST_TIMEOUT_FULL);
                     *abort_flag = 1;
                     break;
                 }
-                mbar_arrive_remote(peer_full + s, 0);
+                mbar_arrive_cluster(peer_bar0 + (kb & 7u) * 8);
+                PP_STAMP(6, kb);
             }
         }
-        else if (lane == 0)
+        else if (rank == 0)
         {
-            // =========================== leader: UMMA lane ===========================
+            // =========================== leader: UMMA warp ===========================
+            // The whole warp runs the loop (waits and descriptor arithmetic stay warp-uniform); one
+            // elected lane issues the UMMAs and the commits.
             bool ok = true;
-            const uint32_t idesc = umma_idesc_bf16(2 * PF_BM, live);
+            uint32_t idesc[TH];
+#pragma unroll
+            for (int th = 0; th < TH; th++) { idesc[th] = umma_idesc_bf16(2 * PF_BM, live[th]); }
             for (unsigned int kb = 0; kb < n_kblocks && ok; kb++)
             {
-                const unsigned int s = kb % ST;
-                const uint32_t par = (kb / ST) & 1u;
-                if (*abort_flag != 0 || !mbar_wait_bounded(full_x + s, par) || !mbar_wait_bounded(full_a + s, par)
-                    || !mbar_wait_bounded_cluster(peer_full + s, par))
+                const unsigned int sx = kb % NX, sa = kb % NA;
+                bool w = *abort_flag == 0 && mbar_wait_bounded(full_x + sx, (kb / NX) & 1u);
+                w = w && mbar_wait_bounded(full_a + sa, (kb / NA) & 1u);
+                w = w && mbar_wait_bounded(peer_full + (kb & 7u), (kb >> 3) & 1u);
+                PP_STAMP(6, kb);
+                if (!w)
                 {
                     ok = false;
-                    atomicMax(p.status, (unsigned int)ST_TIMEOUT_FULL);
-                    *abort_flag = 1;
+                    if (lane == 0)
+                    {
+                        atomicMax(p.status, (unsigned int)ST_TIMEOUT_FULL);
+                        *abort_flag = 1;
+                    }
                     break;
                 }
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(stages + s * STAGE_BYTES);
-                const uint32_t b_addr = a_addr + A_BYTES;
-#pragma unroll
-                for (int k = 0; k < PF_BK / 16; k++)
+                const uint32_t a_addr = smem_u32(stages + sa * A_BYTES);
+                const uint32_t b_addr = smem_u32(xring + sx * X_BYTES);
+                if (elect_one())
                 {
 #pragma unroll
-                    for (int fh = 0; fh < FH; fh++)
+                for (int th = 0; th < TH; th++)
+                {
+                    if (live[th] == 0) { continue; }
+#pragma unroll
+                    for (int k = 0; k < PF_BK / 16; k++)
                     {
-                        umma_bf16_pair(tmem_base + fh * PP_TOKENS, umma_desc_kmajor_sw128(a_addr + fh * (PF_BM * PF_BK * 2) + k * 32),
-                            umma_desc_kmajor_sw128(b_addr + k * 32), idesc, (kb | (unsigned int)k) != 0 ? 1u : 0u);
+#pragma unroll
+                        for (int fh = 0; fh < FH; fh++)
+                        {
+                            umma_bf16_pair(tmem_base + (fh * TH + th) * PP_TOKENS,
+                                umma_desc_kmajor_sw128(a_addr + fh * (PF_BM * PF_BK * 2) + k * 32),
+                                umma_desc_kmajor_sw128(b_addr + th * PP_XH_BYTES + k * 32), idesc[th], (kb | (unsigned int)k) != 0 ? 1u : 0u);
+                        }
                     }
                 }
-                umma_commit_pair(empty + s);
+                umma_commit_pair(empty_x + sx);
+                umma_commit_pair(empty_a + sa);
+                PP_STAMP(7, kb);
+                }
+                __syncwarp();
             }
+            __syncwarp();
             // also on the abort path: the barrier completes once the UMMAs in flight have stopped
             // reading both CTAs' shared memory; the epilogue warps then see the abort flag or the status
-            umma_commit_pair(acc_full);
+            if (elect_one()) { umma_commit_pair(acc_full); }
         }
     }
     else
     {
-        // =========================== dequantise, then epilogue (warps 0..7) ===========================
-        const unsigned int tid = threadIdx.x;    // 0..255
-        constexpr int NP = 2 * FH;               // (row, 16-element group) pieces per thread per k block
+        // =========================== dequantise, then epilogue (warps 0..DQW-1) ===========================
+        const unsigned int tid = threadIdx.x;
+        constexpr int NP = 512 * FH / (32 * DQW);    // (row, 16-element group) pieces per thread per k block
         unsigned int prow[NP], pq[NP], pfeat[NP];
 #pragma unroll
         for (int i = 0; i < NP; i++)
         {
-            const unsigned int piece = tid + 256u * i;
+            const unsigned int piece = tid + (32u * DQW) * i;
             prow[i] = piece >> 2;    // row within the A stage: 128 rows per feature tile
             pq[i] = piece & 3u;
             // feature tile fh of the pair = rows 0..127 from rank 0, 128..255 from rank 1
@@ -263,15 +338,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, FH > 1 ?
                 raw8[slot][i] = make_uint4(0, 0, 0, 0);
                 raw4[slot][i] = make_uint2(0, 0);
                 rawsc[slot][i] = 0;
-                if (pfeat[i] < p.N)
+                if (pfeat[i] < g.N)
                 {
-                    const size_t e = (size_t)pfeat[i] * p.ldw + (size_t)kb * PF_BK + pq[i] * 16;
+                    const size_t e = (size_t)pfeat[i] * g.ldw + (size_t)kb * PF_BK + pq[i] * 16;
                     if (WT == DT_FP4)
                     {
-                        raw4[slot][i] = __ldg(reinterpret_cast<const uint2*>(p.W + e / 2));
-                        rawsc[slot][i] = __ldg(p.blk + e / 16);
+                        raw4[slot][i] = __ldg(reinterpret_cast<const uint2*>(g.W + e / 2));
+                        rawsc[slot][i] = __ldg(g.blk + e / 16);
                     }
-                    else { raw8[slot][i] = __ldg(reinterpret_cast<const uint4*>(p.W + e)); }
+                    else { raw8[slot][i] = __ldg(reinterpret_cast<const uint4*>(g.W + e)); }
                 }
             }
         };
@@ -287,7 +362,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, FH > 1 ?
                 {
                     const uint32_t w[4] = { raw8[slot][i].x, raw8[slot][i].y, raw8[slot][i].z, raw8[slot][i].w };
 #pragma unroll
-                    for (int j = 0; j < 4; j++) { dequant_fp8x4<WT, SCALED>(w[j], p.w_scale, out[i][2 * j], out[i][2 * j + 1]); }
+                    for (int j = 0; j < 4; j++) { dequant_fp8x4<WT, SCALED>(w[j], g.w_scale, out[i][2 * j], out[i][2 * j + 1]); }
                 }
             }
             if (kb + 2 < n_kblocks) { load_raw(kb + 2, slot); }
@@ -298,8 +373,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, FH > 1 ?
         if (n_kblocks > 0) { convert_and_refill(0, 0, out); }
         for (unsigned int kb = 0; kb < n_kblocks; kb++)
         {
-            const unsigned int s = kb % ST;
-            if (ok && kb >= ST && (*abort_flag != 0 || !mbar_wait_bounded(empty + s, ((kb / ST) - 1) & 1u)))
+            const unsigned int s = kb % NA;
+            if (ok && kb >= NA && (*abort_flag != 0 || !mbar_wait_bounded(empty_a + s, ((kb / NA) - 1) & 1u)))
             {
                 ok = false;
                 if (*abort_flag == 0)
@@ -308,9 +383,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, FH > 1 ?
                     *abort_flag = 1;
                 }
             }
+            if (tid == 0) { PP_STAMP(2, kb); }
             if (ok)
             {
-                const uint32_t a_addr = smem_u32(stages + s * STAGE_BYTES);
+                const uint32_t a_addr = smem_u32(stages + s * A_BYTES);
 #pragma unroll
                 for (int i = 0; i < NP; i++)
                 {
@@ -329,9 +405,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, FH > 1 ?
             }
             if (ok)
             {
-                fence_proxy_async();    // make the generic-proxy stores visible to the tensor core's reads
+                fence_proxy_async();    // make the generic-proxy stores visible to the tensor cores' reads
                 __syncwarp();
                 if (lane == 0) { mbar_arrive(full_a + s); }
+                if (tid == 0) { PP_STAMP(3, kb); }
             }
         }
 
@@ -344,73 +421,93 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, FH > 1 ?
         }
         if (*abort_flag != 0 || *reinterpret_cast<volatile unsigned int*>(p.status) != 0) { ok = false; }
         tc_fence_after();
-        if (ok && n_kblocks > 0 && p.y_tma != 0)
+        const unsigned int quarter = warp & 3u;
+        // the DQW/4 warps of a TMEM lane quarter split each 256-token part's columns
+        constexpr unsigned int CPW = PP_TOKENS / (DQW / 4);
+        const unsigned int cbeg = (warp >> 2) * CPW;
+        if (ok && n_kblocks > 0 && g.y_tma != 0)
         {
-            // BF16 tile [256 tokens][128 features] per feature tile in the idle stage memory, then TMA stores
-            const unsigned int quarter = warp & 3u;
-            const unsigned int half = warp >> 2;
+            // BF16 tiles [256 tokens][128 features] in the idle stage memory, then one TMA store each;
+            // the store clips rows past M and features past N
 #pragma unroll
             for (int fh = 0; fh < FH; fh++)
             {
-                const uint32_t ytile = smem_u32(stages) + fh * (PP_TOKENS * PF_BM * 2) + (quarter * 32 + lane) * 2;
-                for (unsigned int c0 = half * (PP_TOKENS / 2); c0 < half * (PP_TOKENS / 2) + PP_TOKENS / 2 && c0 < tile_tokens; c0 += 32)
-                {
-                    uint32_t r[32];
-                    tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + fh * PP_TOKENS + c0, r);
-                    tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; j++)
+                for (int th = 0; th < TH; th++)
+                {
+                    const unsigned int part_tokens = min((unsigned int)PP_TOKENS, tile_tokens - min(tile_tokens, (unsigned int)(th * PP_TOKENS)));
+                    const uint32_t ytile = smem_u32(stages) + (fh * TH + th) * (PP_TOKENS * PF_BM * 2) + (quarter * 32 + lane) * 2;
+                    for (unsigned int c0 = cbeg; c0 < cbeg + CPW && c0 < part_tokens; c0 += 32)
                     {
-                        sts16(ytile + (c0 + j) * (PF_BM * 2), __bfloat16_as_ushort(__float2bfloat16_rn(p.alpha * (__uint_as_float(r[j]) * p.post_scale))));
+                        uint32_t r[32];
+                        tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + (fh * TH + th) * PP_TOKENS + c0, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                        {
+                            sts16(ytile + (c0 + j) * (PF_BM * 2),
+                                __bfloat16_as_ushort(__float2bfloat16_rn(g.alpha * (__uint_as_float(r[j]) * g.post_scale))));
+                        }
                     }
                 }
             }
             fence_proxy_async();
-            bar_sync_named(1, 32 * PF_DQ_WARPS);
+            bar_sync_named(1, 32 * DQW);
             if (tid == 0)
             {
 #pragma unroll
                 for (int fh = 0; fh < FH; fh++)
                 {
-                    tma_store_2d(&tmY, stages + fh * (PP_TOKENS * PF_BM * 2), (int)(n0 + (fh * 2 + rank) * PF_BM), (int)m0);
+#pragma unroll
+                    for (int th = 0; th < TH; th++)
+                    {
+                        if (tile_tokens > (unsigned int)(th * PP_TOKENS))
+                        {
+                            tma_store_2d(&tmY.m[si], stages + (fh * TH + th) * (PP_TOKENS * PF_BM * 2), (int)(n0 + (fh * 2 + rank) * PF_BM),
+                                (int)(m0 + th * PP_TOKENS));
+                        }
+                    }
                 }
                 tma_store_commit_and_wait_read();
             }
         }
         else if (ok && n_kblocks > 0)
         {
-            const unsigned int quarter = warp & 3u;
-            const unsigned int half = warp >> 2;
 #pragma unroll
             for (int fh = 0; fh < FH; fh++)
             {
                 const unsigned int n = n0 + (fh * 2 + rank) * PF_BM + quarter * 32 + lane;
-                for (unsigned int c0 = half * (PP_TOKENS / 2); c0 < half * (PP_TOKENS / 2) + PP_TOKENS / 2 && c0 < tile_tokens; c0 += 32)
-                {
-                    uint32_t r[32];
-                    tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + fh * PP_TOKENS + c0, r);
-                    tmem_ld_wait();
-                    if (n < p.N)
-                    {
 #pragma unroll
-                        for (int j = 0; j < 32; j++)
+                for (int th = 0; th < TH; th++)
+                {
+                    const unsigned int part_tokens = min((unsigned int)PP_TOKENS, tile_tokens - min(tile_tokens, (unsigned int)(th * PP_TOKENS)));
+                    for (unsigned int c0 = cbeg; c0 < cbeg + CPW && c0 < part_tokens; c0 += 32)
+                    {
+                        uint32_t r[32];
+                        tmem_ld_32x32(tmem_base + ((quarter * 32u) << 16) + (fh * TH + th) * PP_TOKENS + c0, r);
+                        tmem_ld_wait();
+                        if (n < g.N)
                         {
-                            const unsigned int m = m0 + c0 + j;
-                            if (c0 + j < tile_tokens)
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
                             {
-                                const long long yi = (long long)m * p.ldy_m + (long long)n * p.ldy_n;
-                                float o = p.alpha * (__uint_as_float(r[j]) * p.post_scale);
-                                if (p.out_f32)
+                                const unsigned int m = m0 + th * PP_TOKENS + c0 + j;
+                                if (c0 + j < part_tokens)
                                 {
-                                    float* y = reinterpret_cast<float*>(p.Y) + yi;
-                                    if (p.beta != 0.f) { o += p.beta * *y; }
-                                    *y = o;
-                                }
-                                else
-                                {
-                                    uint16_t* y = p.Y + yi;
-                                    if (p.beta != 0.f) { o += p.beta * bf16_bits_to_float(*y); }
-                                    *y = __bfloat16_as_ushort(__float2bfloat16_rn(o));
+                                    const long long yi = (long long)m * g.ldy_m + (long long)n * g.ldy_n;
+                                    float o = g.alpha * (__uint_as_float(r[j]) * g.post_scale);
+                                    if (p.out_f32)
+                                    {
+                                        float* y = reinterpret_cast<float*>(g.Y) + yi;
+                                        if (g.beta != 0.f) { o += g.beta * *y; }
+                                        *y = o;
+                                    }
+                                    else
+                                    {
+                                        uint16_t* y = g.Y + yi;
+                                        if (g.beta != 0.f) { o += g.beta * bf16_bits_to_float(*y); }
+                                        *y = __bfloat16_as_ushort(__float2bfloat16_rn(o));
+                                    }
                                 }
                             }
                         }
@@ -422,26 +519,27 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PF_THREADS, FH > 1 ?
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();    // neither CTA frees TMEM or leaves while the other may still use the pair
-    if (warp == PF_DQ_WARPS + 1) { tmem_dealloc_pair(tmem_base, TMEM_COLS); }
+    if (warp == DQW + 1) { tmem_dealloc_pair(tmem_base, TMEM_COLS); }
 }
 
-template <int WT, bool SCALED, int FH>
-static int launch_prefill_pair(const CUtensorMap& tmX, const CUtensorMap& tmY, const PrefillParams& pp, int device, cudaStream_t stream)
+template <int WT, bool SCALED, int FH, int TH, int DQW>
+static int launch_prefill_pair(const CUtensorMap& tmX, const PrefillYMaps& tmY, const PrefillParams& pp, unsigned int feature_tiles, int device,
+    cudaStream_t stream)
 {
-    auto kernel = gemm_wq_prefill_pair_kernel<WT, SCALED, FH>;
+    auto kernel = gemm_wq_prefill_pair_kernel<WT, SCALED, FH, TH, DQW>;
     static bool attr_set[64] = {};
     if (!attr_set[device])
     {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pp_smem_bytes(FH)) != cudaSuccess)
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pp_smem_bytes(FH, TH)) != cudaSuccess)
         {
             report_launch("gemm_wq_bf16");
             return 1;
         }
         attr_set[device] = true;
     }
-    const dim3 grid(2 * ((pp.M + PP_TOKENS - 1) / PP_TOKENS), (pp.N + 2 * PF_BM * FH - 1) / (2 * PF_BM * FH));
+    const dim3 grid(2 * ((pp.M + PP_TOKENS * TH - 1) / (PP_TOKENS * TH)), feature_tiles);
     count_launch();
-    kernel<<<grid, PF_THREADS, pp_smem_bytes(FH), stream>>>(tmX, tmY, pp);
+    kernel<<<grid, 32 * (DQW + 2), pp_smem_bytes(FH, TH), stream>>>(tmX, tmY, pp);
     return report_launch("gemm_wq_bf16");
 }
 

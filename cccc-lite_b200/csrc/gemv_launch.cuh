@@ -299,7 +299,7 @@ static int run_linear_wq(const GemvScratch* ws, int w_type, const void* W, const
     }
     if (plan == PLAN_PREFILL)
     {
-        const int r = launch_prefill(w_type, p, ws->device, ws->sm_count, st);
+        const int r = launch_prefill(w_type, &p, 1, ws->device, ws->sm_count, (int)((flags >> 8) & 7u), st);
         if (r != -2) { return r; }
         plan = PLAN_PLAIN;
     }
@@ -324,7 +324,8 @@ struct GroupItem
 
 // Several linears that read the same activations (q/k/v, gate/up) as ONE launch of the decode
 // kernel: their row blocks are dealt out together.  Anything the decode kernel does not take
-// (more than 32 tokens, unaligned operands, more than kMaxGroup linears) runs one linear at a time.
+// (unaligned operands, more than kMaxGroup linears) runs one linear at a time; more than 32 tokens
+// go to the tensor-core kernel, again as one launch when every member qualifies.
 static int run_linear_wq_group(const GemvScratch* ws, int w_type, unsigned int count, const GroupItem* items, const void* X,
     unsigned int M_tokens, unsigned int K, unsigned int ldx, cudaStream_t st, unsigned int flags)
 {
@@ -377,6 +378,42 @@ static int run_linear_wq_group(const GemvScratch* ws, int w_type, unsigned int c
         if (w_type == DT_FP4) { r = launch_gemv<DT_FP4, false>(p, ws, st, pdl); }
         else if (scaled) { r = (w_type == DT_E5M2) ? launch_gemv<DT_E5M2, true>(p, ws, st, pdl) : launch_gemv<DT_E4M3, true>(p, ws, st, pdl); }
         else { r = (w_type == DT_E5M2) ? launch_gemv<DT_E5M2, false>(p, ws, st, pdl) : launch_gemv<DT_E4M3, false>(p, ws, st, pdl); }
+        if (r != -2) { return r; }
+    }
+    // More than 32 tokens: the members' feature tiles form one grid of the tensor-core kernel.
+    bool one_prefill = count >= 2 && count <= (unsigned)PF_MAX_GROUP && M_tokens > 32;
+    for (unsigned int j = 0; j < count && one_prefill; j++)
+    {
+        one_prefill = items[j].N_out != 0
+            && plan_for(w_type, items[j].W, items[j].blk_scales, X, items[j].Y, items[j].N_out, M_tokens, K, items[j].ldw, ldx,
+                   items[j].ldy_m, items[j].ldy_n)
+                == PLAN_PREFILL;
+    }
+    if (one_prefill)
+    {
+        GemvParams ps[PF_MAX_GROUP];
+        memset(ps, 0, sizeof(ps));
+        for (unsigned int j = 0; j < count; j++)
+        {
+            GemvParams& q = ps[j];
+            q.W = (const uint8_t*)items[j].W;
+            q.blk = (w_type == DT_FP4) ? (const uint8_t*)items[j].blk_scales : nullptr;
+            q.X = (const uint16_t*)X;
+            q.Y = (uint16_t*)items[j].Y;
+            q.status = ws->status;
+            q.N = items[j].N_out;
+            q.M = M_tokens;
+            q.K = K;
+            q.ldw = items[j].ldw;
+            q.ldx = ldx;
+            q.ldy_m = items[j].ldy_m;
+            q.ldy_n = items[j].ldy_n;
+            q.w_scale = items[j].inv_scale;
+            q.alpha = items[j].alpha;
+            q.beta = items[j].beta;
+            q.out_f32 = (flags & 4u) ? 1u : 0u;
+        }
+        const int r = launch_prefill(w_type, ps, count, ws->device, ws->sm_count, (int)((flags >> 8) & 7u), st);
         if (r != -2) { return r; }
     }
     for (unsigned int j = 0; j < count; j++)

@@ -5,106 +5,164 @@
 #include "gemm_prefill.cuh"
 #include "gemm_prefill_pair.cuh"
 
-#include <cstdlib>
 
 namespace b200
 {
 
-// 256-token tiles halve the weight conversions per flop; 128-token tiles are taken when the larger
-// tile would leave more than half of the 2-per-SM CTA slots empty (few output features, few tokens).
-static int pf_pick_bn(unsigned int N, unsigned int M, unsigned int K, int sm_count)
+#ifdef B200_TRACE
+static unsigned long long* trace_next(unsigned int grid);
+#endif
+
+// Tile shapes of the prefill path.  One CTA per tile: 128 features x 128 or 256 tokens (two CTAs per
+// SM), or 256 features x 256 tokens (one CTA per SM).  CTA pairs (cta_group::2): 256 x 256, 512
+// features x 256 tokens, or 256 features x 512 tokens per pair.
+enum PrefillVariant : int
 {
-    const unsigned long long ftiles = (N + PF_BM - 1) / PF_BM;
-    const unsigned long long tiles256 = (unsigned long long)((M + 255) / 256) * ftiles;
-    const unsigned long long tiles512 = (unsigned long long)((M + 511) / 512) * ftiles;
-    if (M <= 128 || tiles256 * 2 <= (unsigned long long)sm_count) { return 128; }
-    // 256 features x 256 tokens per CTA (one CTA per SM, the activation tile shared by two weight
-    // tiles) when that still fills most of the SMs; -256 encodes it
-    (void)tiles512;
-    const unsigned long long tiles_wide = (unsigned long long)((M + 255) / 256) * ((N + 2 * PF_BM - 1) / (2 * PF_BM));
-    // Measured at M=2048: K=12288 1107 vs 1066 TFLOP/s for it, K=4096 861 vs 964 against it (its
-    // prologue and epilogue are not hidden by a second CTA), so it is taken for long K only.
-    if (K >= 8192 && tiles_wide * 10 >= (unsigned long long)sm_count * 8) { return -256; }
-    return 256;
+    PFV_AUTO = 0,
+    PFV_CTA_T128 = 1,
+    PFV_CTA_T256 = 2,
+    PFV_CTA_F256 = 3,
+    PFV_PAIR = 4,
+    PFV_PAIR_F512 = 5,
+    PFV_PAIR_T512 = 6,
+    PFV_COUNT = 7
+};
+
+// Measured on B200 (M = 64 ... 8192, N x K of 1024..12288 x 4096..12288, all three weight types): the
+// pair tile of 512 tokens is the fastest shape whenever its pairs cover about two thirds of the SMs
+// (each weight is converted once per 512 tokens, each CTA stages half of the activations, five and
+// four stages deep); with fewer tiles the 256 x 256 pair tile (two CTAs per SM) wins, and when even
+// that leaves most SMs idle the 128 x 128 one-CTA tile gives the most CTAs.  The k loop of a CTA
+// costs about 0.55 us per 64-wide k block whatever the tile, so small problems are bound by K alone.
+static int pf_pick_variant(int w_type, unsigned int N, unsigned int M, unsigned int K, int sm_count)
+{
+    (void)w_type;
+    (void)K;
+    const unsigned long long f256 = (N + 2 * PF_BM - 1) / (2 * PF_BM);
+    const unsigned long long pairs_t512 = (unsigned long long)((M + 511) / 512) * f256;
+    const unsigned long long pairs_256 = (unsigned long long)((M + 255) / 256) * f256;
+    const unsigned long long want = (unsigned long long)sm_count / 3;    // pairs: two thirds of the SMs
+    if (pairs_t512 >= want) { return PFV_PAIR_T512; }
+    if (M > 128 && pairs_256 >= want) { return PFV_PAIR; }
+    return PFV_CTA_T128;
+}
+
+// Features per blockIdx.y of a tile shape.
+static unsigned int pf_variant_tile_features(int variant)
+{
+    switch (variant)
+    {
+    case PFV_CTA_F256: return 2 * PF_BM;
+    case PFV_PAIR: return 2 * PF_BM;
+    case PFV_PAIR_F512: return 4 * PF_BM;
+    case PFV_PAIR_T512: return 2 * PF_BM;
+    default: return PF_BM;
+    }
 }
 
 template <int WT, bool SCALED>
-static int launch_prefill_t(const void* X, unsigned int ldx, const PrefillParams& pp_in, int device, int sm_count, cudaStream_t stream)
+static int launch_prefill_t(const void* X, unsigned int ldx, const PrefillParams& pp_in, int device, int sm_count, int variant,
+    cudaStream_t stream)
 {
-    int bn = pf_pick_bn(pp_in.N, pp_in.M, pp_in.K, sm_count);
-    CUtensorMap tmX, tmY;
-    memset(&tmY, 0, sizeof(tmY));
     PrefillParams pp = pp_in;
-    // BF16 output with contiguous features, no accumulate: the epilogue writes whole tiles with TMA stores
-    pp.y_tma = 0;
-    if (!pp.out_f32 && pp.beta == 0.f && pp.ldy_n == 1 && (pp.ldy_m % 8) == 0 && pp.ldy_m >= (long long)pp.N
-        && (reinterpret_cast<uintptr_t>(pp.Y) & 15u) == 0 && !(getenv("B200_PF_NOTMAY")))
+    unsigned int n_total = 0;
+    for (unsigned int j = 0; j < pp.n_seg; j++) { n_total += pp.seg[j].N; }
+    if (variant <= PFV_AUTO || variant >= PFV_COUNT) { variant = pf_pick_variant(WT, n_total, pp.M, pp.K, sm_count); }
+    const bool pair = variant >= PFV_PAIR;
+    const unsigned x_box_rows = pair ? (unsigned)PP_HALF : (variant == PFV_CTA_T128 ? 128u : 256u);
+    const unsigned y_box_rows = pair ? (unsigned)PP_TOKENS : x_box_rows;
+    const unsigned int tile_features = pf_variant_tile_features(variant);
+    CUtensorMap tmX;
+    PrefillYMaps tmY;
+    memset(&tmY, 0, sizeof(tmY));
+    unsigned int feature_tiles = 0;
+    for (unsigned int j = 0; j < pp.n_seg; j++)
     {
-        const char* f0 = getenv("B200_PF_MODE");
-        const int m0 = f0 ? atoi(f0) : 0;
-        const unsigned box_rows = (m0 == 2 || m0 == 3) ? (unsigned)PP_TOKENS : (unsigned)(bn == 128 ? 128 : 256);
-        if (make_map_2d(&tmY, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, pp.Y, pp.N, pp.M, (unsigned long long)pp.ldy_m * 2, PF_BM, box_rows,
+        PrefillSeg& g = pp.seg[j];
+        g.tile0 = feature_tiles;
+        feature_tiles += (g.N + tile_features - 1) / tile_features;
+        // BF16 output with contiguous features and no accumulate: the epilogue writes whole tiles with TMA stores
+        g.y_tma = 0;
+        if (!pp.out_f32 && g.beta == 0.f && g.ldy_n == 1 && (g.ldy_m % 8) == 0 && g.ldy_m >= (long long)g.N
+            && (reinterpret_cast<uintptr_t>(g.Y) & 15u) == 0
+            && make_map_2d(&tmY.m[j], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, g.Y, g.N, pp.M, (unsigned long long)g.ldy_m * 2, PF_BM, y_box_rows,
                 false))
         {
-            pp.y_tma = 1;
+            g.y_tma = 1;
         }
     }
-    const char* force = getenv("B200_PF_MODE");    // development switch
-    const int mode = force ? atoi(force) : 0;
-    if (mode == 2 || mode == 3)
-    {
-        if (!make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, pp.K, pp.M, (unsigned long long)ldx * 2, PF_BK, PP_HALF, true))
-        {
-            return -2;
-        }
-        return mode == 2 ? launch_prefill_pair<WT, SCALED, 1>(tmX, tmY, pp, device, stream)
-                         : launch_prefill_pair<WT, SCALED, 2>(tmX, tmY, pp, device, stream);
-    }
-    if (mode == 1 && bn == -256) { bn = 256; }
-    if (!make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, pp.K, pp.M, (unsigned long long)ldx * 2, PF_BK,
-            (unsigned)(bn == 128 ? 128 : 256), true))
+    if (feature_tiles == 0 || feature_tiles > 65535u) { return -2; }    // grid.y
+    if (!make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, pp.K, pp.M, (unsigned long long)ldx * 2, PF_BK, x_box_rows, true))
     {
         return -2;
     }
-    if (bn == -256) { return launch_prefill_bn<WT, SCALED, 256, 2>(tmX, tmY, pp, device, stream); }
-    return bn == 128 ? launch_prefill_bn<WT, SCALED, 128, 1>(tmX, tmY, pp, device, stream)
-                     : launch_prefill_bn<WT, SCALED, 256, 1>(tmX, tmY, pp, device, stream);
+    switch (variant)
+    {
+    case PFV_CTA_T128: return launch_prefill_bn<WT, SCALED, 128, 1>(tmX, tmY, pp, feature_tiles, device, stream);
+    case PFV_CTA_F256: return launch_prefill_bn<WT, SCALED, 256, 2>(tmX, tmY, pp, feature_tiles, device, stream);
+    case PFV_PAIR: return launch_prefill_pair<WT, SCALED, 1, 1, 8>(tmX, tmY, pp, feature_tiles, device, stream);
+    case PFV_PAIR_F512: return launch_prefill_pair<WT, SCALED, 2, 1, 16>(tmX, tmY, pp, feature_tiles, device, stream);
+    case PFV_PAIR_T512: return launch_prefill_pair<WT, SCALED, 1, 2, 16>(tmX, tmY, pp, feature_tiles, device, stream);
+    default: return launch_prefill_bn<WT, SCALED, 256, 1>(tmX, tmY, pp, feature_tiles, device, stream);
+    }
 }
 
-// Returns -2 when the shape has to go elsewhere.
-static int launch_prefill(int w_type, const GemvParams& p, int device, int sm_count, cudaStream_t stream)
+static bool pf_is_pow2_scale(float s)
 {
-    if (w_type == DT_FP4 && p.blk == nullptr) { return -2; }
+    int e = 0;
+    return s > 0.f && !std::isinf(s) && std::frexp(s, &e) == 0.5f && e >= -39 && e <= 41;
+}
+
+// One launch for up to PF_MAX_GROUP linears that share X (count = 1: a single linear).  `items`
+// carry W, blk, Y, N, ldw, ldy_m, ldy_n, w_scale, alpha, beta; the rest comes from items[0].
+// Returns -2 when the shapes have to go elsewhere.
+static int launch_prefill(int w_type, const GemvParams* items, unsigned int count, int device, int sm_count, int variant,
+    cudaStream_t stream)
+{
+    if (count == 0 || count > (unsigned)PF_MAX_GROUP) { return -2; }
     PrefillParams pp;
     memset(&pp, 0, sizeof(pp));
-    pp.W = p.W;
-    pp.blk = p.blk;
-    pp.Y = p.Y;
-    pp.status = p.status;
-    pp.N = p.N;
-    pp.M = p.M;
-    pp.K = p.K;
-    pp.ldw = p.ldw;
-    pp.ldy_m = p.ldy_m;
-    pp.ldy_n = p.ldy_n;
-    pp.w_scale = p.w_scale;
-    pp.alpha = p.alpha;
-    pp.beta = p.beta;
-    pp.post_scale = 1.0f;
-    pp.out_f32 = p.out_f32;
-    { const char* d = getenv("B200_PF_DBG"); pp.dbg = d ? (unsigned)atoi(d) : 0u; }
-    if (w_type == DT_FP4) { return launch_prefill_t<DT_FP4, false>(p.X, p.ldx, pp, device, sm_count, stream); }
-    int e = 0;
-    const bool pow2 = p.w_scale > 0.f && !std::isinf(p.w_scale) && std::frexp(p.w_scale, &e) == 0.5f && e >= -39 && e <= 41;
-    if (pow2)
+    pp.n_seg = count;
+    pp.status = items[0].status;
+    pp.M = items[0].M;
+    pp.K = items[0].K;
+    pp.out_f32 = items[0].out_f32;
+    bool all_pow2 = true;
+    for (unsigned int j = 0; j < count; j++)
     {
-        pp.post_scale = p.w_scale;
-        pp.w_scale = 1.0f;
-        return w_type == DT_E5M2 ? launch_prefill_t<DT_E5M2, false>(p.X, p.ldx, pp, device, sm_count, stream)
-                                 : launch_prefill_t<DT_E4M3, false>(p.X, p.ldx, pp, device, sm_count, stream);
+        if (w_type == DT_FP4 && items[j].blk == nullptr) { return -2; }
+        all_pow2 = all_pow2 && pf_is_pow2_scale(items[j].w_scale);
     }
-    return w_type == DT_E5M2 ? launch_prefill_t<DT_E5M2, true>(p.X, p.ldx, pp, device, sm_count, stream)
-                             : launch_prefill_t<DT_E4M3, true>(p.X, p.ldx, pp, device, sm_count, stream);
+    // a power-of-two scale commutes exactly with the BF16 rounding and the FP32 sums: it moves to the epilogue
+    const bool scaled = w_type != DT_FP4 && !all_pow2;
+    for (unsigned int j = 0; j < count; j++)
+    {
+        PrefillSeg& g = pp.seg[j];
+        g.W = items[j].W;
+        g.blk = items[j].blk;
+        g.Y = items[j].Y;
+        g.N = items[j].N;
+        g.ldw = items[j].ldw;
+        g.ldy_m = items[j].ldy_m;
+        g.ldy_n = items[j].ldy_n;
+        g.alpha = items[j].alpha;
+        g.beta = items[j].beta;
+        g.w_scale = scaled ? items[j].w_scale : 1.0f;
+        g.post_scale = (w_type == DT_FP4 || scaled) ? 1.0f : items[j].w_scale;
+    }
+#ifdef B200_TRACE
+    pp.trace = trace_next(1024);    // 2 ranks x 16 roles x 256 k blocks
+#endif
+    const void* X = items[0].X;
+    const unsigned int ldx = items[0].ldx;
+    if (w_type == DT_FP4) { return launch_prefill_t<DT_FP4, false>(X, ldx, pp, device, sm_count, variant, stream); }
+    if (!scaled)
+    {
+        return w_type == DT_E5M2 ? launch_prefill_t<DT_E5M2, false>(X, ldx, pp, device, sm_count, variant, stream)
+                                 : launch_prefill_t<DT_E4M3, false>(X, ldx, pp, device, sm_count, variant, stream);
+    }
+    return w_type == DT_E5M2 ? launch_prefill_t<DT_E5M2, true>(X, ldx, pp, device, sm_count, variant, stream)
+                             : launch_prefill_t<DT_E4M3, true>(X, ldx, pp, device, sm_count, variant, stream);
 }
 
 }    // namespace b200

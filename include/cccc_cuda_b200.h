@@ -77,7 +77,10 @@ C_EXPORT void cuda_clear_last_error(void);
  * overlaps the tail of the previous kernel on the stream (X, Y are only touched after that
  * kernel has finished).  bit 2 = Y holds float32 instead of BF16 (same strides, in elements): the
  * unrounded result, which is what a row-parallel (K-split) shard hands to the all-reduce so that
- * the sum over shards is rounded to BF16 once. */
+ * the sum over shards is rounded to BF16 once.  bits 8-10 = tile shape of the M_tokens > 32 path,
+ * for tests and tuning (0 = chosen by shape; 1-3 = one CTA per tile: 128 features x 128 tokens,
+ * 128 x 256, 256 x 256; 4-6 = CTA pairs: 256 x 256, 512 features x 256 tokens, 256 x 512): every
+ * value gives the same result bit for bit. */
 C_EXPORT int cuda_gemm_wq_bf16(int w_type, const void* W, const void* blk_scales, float inv_scale, const void* X,
     void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx,
     unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta, void* stream, unsigned int flags);

@@ -95,3 +95,45 @@ def test_groups_the_decode_kernel_does_not_take_still_give_the_right_result(case
         _, y32 = O.linear_wq_bf16(wt, W, blk, inv, X, N, M, K, alpha=it["alpha"])
         assert_close(got, y32, (case, j))
     assert c.gemm_wq_bf16_group(wt, None, dX, M, K) == 0 if False else True
+
+
+@pytest.mark.parametrize("wt", WTS)
+@pytest.mark.parametrize("variant", [0, 1, 3, 4, 6])
+@pytest.mark.parametrize("scales", [(1.0, 0.5, 2.0), (0.37, 1.0, 0.011)])
+def test_group_above_32_tokens_is_one_tensor_core_launch(wt, variant, scales):
+    """q/k/v-like members of different (ragged) widths at M > 32: one launch of the prefill kernel in
+    every tile shape, bit-identical to separate calls, and within tolerance of the oracle."""
+    import torch
+
+    c = capi()
+    Ns, K, M = (640, 200, 136), 512, 300
+    items, host, X = build(wt, Ns, K, M, 21 + variant, scales)
+    dX = to_dev(X)
+    fl = c.flag_prefill_variant(variant)
+    before = c.launch_count()
+    assert c.gemm_wq_bf16_group(wt, c.make_group(items, K), dX, M, K, flags=fl) == 0 and c.check_error("group") == 0
+    assert c.launch_count() - before == 1
+    for it, (W, blk, inv, N) in zip(items, host):
+        sep = torch.zeros(M * N, dtype=torch.int16, device="cuda")
+        assert c.gemm_wq_bf16(wt, it["W"], it["S"], inv, dX, sep, N, M, K, alpha=it["alpha"], flags=fl) == 0
+        assert c.check_error("sep") == 0
+        assert np.array_equal(from_dev_u16(it["Y"]), from_dev_u16(sep)), (wt, variant, N)
+        _, y32 = O.linear_wq_bf16(wt, W, blk, inv, X, N, M, K, alpha=it["alpha"])
+        assert_close(O.bf16_bits_to_f32(from_dev_u16(it["Y"])).reshape(M, N), y32, ("oracle", wt, variant, N))
+
+
+@pytest.mark.parametrize("wt", [O.FP8_E5M2, O.FP4_E2M1])
+def test_group_above_32_tokens_with_beta_and_float32_output(wt):
+    import torch
+
+    c = capi()
+    Ns, K, M = (160, 96), 256, 70
+    items, host, X = build(wt, Ns, K, M, 31, (0.37,))
+    dX = to_dev(X)
+    for it, N in zip(items, Ns):
+        it["Y"], it["beta"] = torch.full((M * N,), 2.0, dtype=torch.float32, device="cuda"), 0.5
+    assert c.gemm_wq_bf16_group(wt, c.make_group(items, K), dX, M, K, flags=c.FLAG_OUT_F32) == 0 and c.check_error("g") == 0
+    for it, (W, blk, inv, N) in zip(items, host):
+        _, y32 = O.linear_wq_bf16(wt, W, blk, inv, X, N, M, K, alpha=it["alpha"])
+        got = it["Y"].cpu().numpy().reshape(M, N) - 1.0
+        assert_close(got, y32, (wt, N))

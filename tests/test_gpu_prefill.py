@@ -89,3 +89,76 @@ def test_prefill_config4_shape_against_reference_gpu_path(wt):
                            0.0, dB.data_ptr() if dB is not None else None, None)
     assert rc == 0
     assert_close(a, O.bf16_bits_to_f32(from_dev_u16(ref)).reshape(M, N), "reference gpu path")
+
+
+VARIANTS = [1, 2, 3, 4, 5, 6]    # one CTA per tile: 128x128, 128x256, 256x256; CTA pairs: 256x256, 512x256, 256x512
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("wt", WTS)
+@pytest.mark.parametrize("N,K,M", [(128, 64, 33), (300, 256, 300), (520, 512, 700), (1000, 1024, 513)])
+def test_prefill_every_tile_shape_matches_oracle(wt, variant, N, K, M):
+    """Ragged feature and token counts (tiles partly or wholly past the edges) in every tile shape,
+    BF16 output written by the TMA-store epilogue."""
+    c = capi()
+    W, blk, inv, X = O.make_inputs(wt, N, K, M, seed=N + M + variant, scaled=True)
+    Y, plan = run(wt, W, blk, inv, X, N, M, K, flags=c.flag_prefill_variant(variant))
+    assert plan == c.PLAN_PREFILL
+    _, y32 = O.linear_wq_bf16(wt, W, blk, inv, X, N, M, K)
+    assert_close(O.bf16_bits_to_f32(Y).reshape(M, N), y32, (wt, variant, N, K, M))
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("wt", WTS)
+def test_prefill_every_tile_shape_direct_epilogue(wt, variant):
+    """alpha/beta accumulate into a transposed, padded Y and float32 output: the epilogue that
+    stores from registers instead of through TMA."""
+    import torch
+
+    c = capi()
+    N, K, M = 300, 256, 290
+    W, blk, inv, X = O.make_inputs(wt, N, K, M, seed=77 + variant, scaled=False)
+    rng = np.random.default_rng(5)
+    Y0 = O.f32_to_bf16_bits(rng.standard_normal((N, M + 5)).astype(np.float32))
+    kw = dict(alpha=0.5, beta=-1.25, ldy_m=1, ldy_n=M + 5)
+    Y, _ = run(wt, W, blk, inv, X, N, M, K, Y0=Y0.copy(), flags=c.flag_prefill_variant(variant), **kw)
+    Yo, _ = O.linear_wq_bf16(wt, W, blk, inv, X, N, M, K, Y=Y0, **kw)
+    got = O.bf16_bits_to_f32(Y[:Yo.size]).reshape(N, M + 5)
+    want = O.bf16_bits_to_f32(Yo).reshape(N, M + 5)
+    assert_close(got[:, :M], want[:, :M], (wt, variant))
+    assert np.array_equal(got[:, M:], O.bf16_bits_to_f32(Y0)[:, M:])
+    # float32 output (flags bit 2), against the oracle's unrounded sums
+    dW, dX = to_dev(W), to_dev(X)
+    dB = to_dev(blk) if blk is not None else None
+    y = torch.zeros(M * N, dtype=torch.float32, device="cuda")
+    assert c.gemm_wq_bf16(wt, dW, dB, inv, dX, y, N, M, K, flags=c.FLAG_OUT_F32 | c.flag_prefill_variant(variant)) == 0
+    assert c.check_error("f32") == 0
+    _, y32 = O.linear_wq_bf16(wt, W, blk, inv, X, N, M, K)
+    assert_close(y.cpu().numpy().reshape(M, N), y32, (wt, variant, "f32"))
+
+
+@pytest.mark.parametrize("wt", WTS)
+def test_prefill_tile_shapes_agree_bit_for_bit(wt):
+    """At BASELINE config 4's token count every tile shape accumulates the same products in the same
+    k order in FP32, so the BF16 outputs are identical; the default choice is one of them."""
+    import torch
+
+    c = capi()
+    N, K, M = 1536, 4096, 2048
+    W, blk, inv, X = O.make_inputs(wt, N, K, M, seed=9, scaled=True)
+    dW, dX = to_dev(W), to_dev(X)
+    dB = to_dev(blk) if blk is not None else None
+    outs = []
+    for variant in [0] + VARIANTS:
+        y = torch.full((M * N,), 0x7FC0, dtype=torch.int16, device="cuda")
+        assert c.gemm_wq_bf16(wt, dW, dB, inv, dX, y, N, M, K, flags=c.flag_prefill_variant(variant)) == 0
+        assert c.check_error("v") == 0
+        outs.append(from_dev_u16(y))
+    for variant, y in zip(VARIANTS, outs[1:]):
+        assert np.array_equal(y, outs[0]), variant
+    rows = np.arange(0, N, 53)
+    toks = np.arange(0, M, 67)
+    Wsub = (W.reshape(N, K // 2) if wt == O.FP4_E2M1 else W.reshape(N, K))[rows]
+    bsub = blk.reshape(N, K // 16)[rows] if blk is not None else None
+    _, y32 = O.linear_wq_bf16(wt, Wsub.reshape(-1), bsub, inv, X.reshape(M, K)[toks], rows.size, toks.size, K)
+    assert_close(O.bf16_bits_to_f32(outs[0]).reshape(M, N)[np.ix_(toks, rows)], y32, "oracle subset")
