@@ -100,7 +100,7 @@ static int launch_prefill_t(const void* X, unsigned int ldx, const PrefillParams
     {
     case PFV_CTA_T128: return launch_prefill_bn<WT, SCALED, 128, 1>(tmX, tmY, pp, feature_tiles, device, stream);
     case PFV_CTA_F256: return launch_prefill_bn<WT, SCALED, 256, 2>(tmX, tmY, pp, feature_tiles, device, stream);
-    case PFV_PAIR: return launch_prefill_pair<WT, SCALED, 1, 1, 8>(tmX, tmY, pp, feature_tiles, device, stream);
+    case PFV_PAIR: return launch_prefill_pair<WT, SCALED, 1, 1, 16>(tmX, tmY, pp, feature_tiles, device, stream);
     case PFV_PAIR_F512: return launch_prefill_pair<WT, SCALED, 2, 1, 16>(tmX, tmY, pp, feature_tiles, device, stream);
     case PFV_PAIR_T512: return launch_prefill_pair<WT, SCALED, 1, 2, 16>(tmX, tmY, pp, feature_tiles, device, stream);
     default: return launch_prefill_bn<WT, SCALED, 256, 1>(tmX, tmY, pp, feature_tiles, device, stream);
