@@ -209,6 +209,15 @@ def run_step(torch, dist, capi, wt, calls, bufs, M, world, flags):
     all-reduced and rounded to BF16 once; the logits are all-gathered."""
     n_launch = 0
     for c in calls:
+        fused = bufs.get("fused_row_linear") if c["row_parallel"] else None
+        if fused is not None:
+            # the row-parallel linear and its all-reduce as one kernel
+            it = c["items"][0]
+            rc = fused(wt, it["W"], it["S"], it["inv"], c["src"], c["dst"], it["N"], M, c["K"], alpha=it["alpha"], flags=flags)
+            if rc != 0:
+                raise RuntimeError(f"fused linear {c['name']} failed: {rc}")
+            n_launch += 1
+            continue
         if len(c["items"]) == 1:
             it = c["items"][0]
             rc = capi.gemm_wq_bf16(wt, it["W"], it["S"], it["inv"], c["src"], it["Y"], it["N"], M, c["K"], alpha=it["alpha"],
@@ -279,17 +288,21 @@ def gpu_arm(args):
     allreduce = "none"
     if world > 1:
         allreduce = "nccl"
-        if args.ar == "push":
+        if args.ar in ("push", "fused"):
             try:
-                bufs["push_allreduce"] = capi.PushAllReduce(dist, dist.group.WORLD, rank, world, M * dims[0], dev)
-                allreduce = "push"
+                if args.ar == "fused":
+                    bufs["fused_row_linear"] = capi.FusedRowLinear(dist, dist.group.WORLD, rank, world, M * dims[0], dev)
+                else:
+                    bufs["push_allreduce"] = capi.PushAllReduce(dist, dist.group.WORLD, rank, world, M * dims[0], dev)
+                allreduce = args.ar
             except Exception as e:  # symmetric memory not available on this box: NCCL does the exchange
                 if rank == 0:
-                    print(f"push all-reduce unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr, flush=True)
-        ok = torch.tensor([1 if allreduce == "push" else 0], device=dev)
+                    print(f"peer-memory all-reduce unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr, flush=True)
+        ok = torch.tensor([1 if allreduce != "nccl" else 0], device=dev)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         if int(ok.item()) == 0:
             bufs.pop("push_allreduce", None)
+            bufs.pop("fused_row_linear", None)
             allreduce = "nccl"
     flags = capi.FLAG_PDL if args.pdl else 0
 
@@ -553,7 +566,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--ar", default="push", choices=["push", "nccl"], help="exchange of row-parallel partial sums (N>1)")
+    ap.add_argument("--ar", default="fused", choices=["fused", "push", "nccl"],
+                    help="exchange of row-parallel partial sums (N>1): inside the linear's kernel, a separate push kernel, or NCCL")
     ap.add_argument("--group", type=int, default=1, help="1: q,k,v and gate,up of a layer go through cuda_gemm_wq_bf16_group")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (small cases for profiling)")
     ap.add_argument("--no-prefill", action="store_true")

@@ -41,6 +41,10 @@ SYMBOLS = {
     "cuda_b200_allreduce_recv_bytes": (C.c_ulonglong, [_i, _u]),
     "cuda_b200_allreduce_flag_bytes": (C.c_ulonglong, [_i]),
     "cuda_b200_allreduce_counter_bytes": (C.c_ulonglong, []),
+    "cuda_gemm_wq_bf16_allreduce": (_i, [_i, _vp, _vp, _f, _vp, _vp, _u, _u, _u, _u, _u, _u, _u, _f, C.POINTER(C.c_ulonglong),
+                                         C.POINTER(C.c_ulonglong), _vp, _u, _i, _i, _vp, _u]),
+    "cuda_b200_fused_flag_bytes": (C.c_ulonglong, [_i]),
+    "cuda_b200_fused_counter_bytes": (C.c_ulonglong, []),
     "cuda_argmax_bf16": (_i, [_vp, _u, _u, C.c_ulonglong, _vp, _vp, _vp]),
     "cuda_b200_launch_count": (C.c_ulonglong, []),
     "cuda_b200_version": (C.c_char_p, []),
@@ -197,6 +201,43 @@ class PushAllReduce:
             stream = torch.cuda.current_stream().cuda_stream
         return lib().cuda_b200_allreduce_f32_to_bf16(self.recv_ptrs, self.flag_ptrs, _ptr(self.counters), _ptr(partial), _ptr(out),
                                                      n, self.n_max, self.rank, self.world, stream, flags)
+
+
+class FusedRowLinear:
+    """The row-parallel linear with its all-reduce inside the kernel (cuda_gemm_wq_bf16_allreduce).
+    Allocates the exchange areas with torch's symmetric memory and keeps the pointer arrays; every
+    rank must construct it and then make the same calls."""
+
+    def __init__(self, dist, group, rank: int, world: int, n_max: int, device):
+        import torch
+        import torch.distributed._symmetric_memory as symm_mem
+
+        L = lib()
+        self.rank, self.world, self.n_max = rank, world, n_max
+        self.recv = symm_mem.empty(L.cuda_b200_allreduce_recv_bytes(world, n_max) // 4, dtype=torch.float32, device=device)
+        self.flag = symm_mem.empty(L.cuda_b200_fused_flag_bytes(world) // 4, dtype=torch.int32, device=device)
+        self.recv.zero_()
+        self.flag.zero_()
+        self.counters = torch.zeros(L.cuda_b200_fused_counter_bytes() // 4, dtype=torch.int32, device=device)
+        hr = symm_mem.rendezvous(self.recv, group)
+        hf = symm_mem.rendezvous(self.flag, group)
+        self._handles = (hr, hf)
+        self.recv_ptrs = (C.c_ulonglong * world)(*[int(p) for p in hr.buffer_ptrs])
+        self.flag_ptrs = (C.c_ulonglong * world)(*[int(p) for p in hf.buffer_ptrs])
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    def __call__(self, w_type: int, W, blk, inv_scale: float, X, Y, N: int, M: int, K: int, *, ldw: int | None = None,
+                 ldx: int | None = None, ldy_m: int | None = None, ldy_n: int = 1, alpha: float = 1.0,
+                 stream: int | None = None, flags: int = 0) -> int:
+        if stream is None:
+            import torch
+
+            stream = torch.cuda.current_stream().cuda_stream
+        return lib().cuda_gemm_wq_bf16_allreduce(w_type, _ptr(W), _ptr(blk), inv_scale, _ptr(X), _ptr(Y), N, M, K,
+                                                 K if ldw is None else ldw, K if ldx is None else ldx,
+                                                 N if ldy_m is None else ldy_m, ldy_n, alpha, self.recv_ptrs, self.flag_ptrs,
+                                                 _ptr(self.counters), self.n_max, self.rank, self.world, stream, flags)
 
 
 def argmax_bf16(logits, rows: int, cols: int, idx_out, val_out=None, ld: int | None = None, stream: int | None = None) -> int:

@@ -146,6 +146,43 @@ C_EXPORT int cuda_gemm_wq_bf16_group(int w_type, unsigned int count, const cuda_
         (cudaStream_t)stream, flags);
 }
 
+C_EXPORT int cuda_gemm_wq_bf16_allreduce(int w_type, const void* W, const void* blk_scales, float inv_scale, const void* X, void* Y,
+    unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m,
+    unsigned int ldy_n, float alpha, const unsigned long long* peer_recv_ptrs, const unsigned long long* peer_flag_ptrs,
+    void* seq_counters, unsigned int n_max, int rank, int world, void* stream, unsigned int flags)
+{
+    if (w_type != DT_E4M3 && w_type != DT_E5M2 && w_type != DT_FP4) { return -1; }
+    if (!W || !X || !Y || N_out == 0 || M_tokens == 0 || K == 0) { return -1; }
+    if (world < 1 || world > kArMaxWorld || rank < 0 || rank >= world) { return -1; }
+    if (world > 1 && (!peer_recv_ptrs || !peer_flag_ptrs || !seq_counters)) { return -1; }
+    Workspace* ws = workspace();
+    if (!ws)
+    {
+        fprintf(stderr, "gemm_wq_bf16 kernel launch failed: no workspace on this device\n");
+        return 1;
+    }
+    GemvAllReduce ar;
+    memset(&ar, 0, sizeof(ar));
+    for (int r = 0; r < world && world > 1; r++)
+    {
+        ar.peer_recv[r] = reinterpret_cast<float*>(peer_recv_ptrs[r]);
+        ar.peer_flag[r] = reinterpret_cast<unsigned int*>(peer_flag_ptrs[r]);
+    }
+    ar.seq = reinterpret_cast<unsigned int*>(seq_counters);
+    ar.n_max = n_max;
+    ar.rank = rank;
+    ar.world = world;
+    return run_linear_wq(&ws->scratch, w_type, W, blk_scales, inv_scale, X, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n, alpha, 0.f,
+        (cudaStream_t)stream, flags, false, &ar);
+}
+
+C_EXPORT unsigned long long cuda_b200_fused_flag_bytes(int world)
+{
+    return world < 1 ? 0ull : 2ull * kArMaxRowBlocks * (unsigned long long)world * sizeof(unsigned int);
+}
+
+C_EXPORT unsigned long long cuda_b200_fused_counter_bytes(void) { return (unsigned long long)kArMaxRowBlocks * sizeof(unsigned int); }
+
 C_EXPORT int cuda_gemm_wq_bf16_plan(int w_type, const void* W, const void* blk_scales, const void* X, const void* Y,
     unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m,
     unsigned int ldy_n)

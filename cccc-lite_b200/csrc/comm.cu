@@ -22,7 +22,6 @@ namespace b200
 
 constexpr int kArCtas = 8;
 constexpr int kArThreads = 256;
-constexpr int kArMaxWorld = 8;
 
 struct ArParams
 {
@@ -35,17 +34,6 @@ struct ArParams
     unsigned int n, n_max;
     int rank, world;
 };
-
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v)
-{
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p)
-{
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 
 __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const ArParams p)
 {
@@ -75,7 +63,8 @@ __global__ void __launch_bounds__(kArThreads) allreduce_push_kernel(const ArPara
         const float4 v = src[i];
         for (int r = 0; r < p.world; r++) { reinterpret_cast<float4*>(p.peer_recv[r] + slot)[i] = v; }
     }
-    __threadfence_system();
+    // The barrier orders every thread's peer stores before the flag stores of threads 0..world-1, whose
+    // release at system scope is cumulative over them; a system fence per storing thread cost 4 us.
     __syncthreads();
     if ((int)threadIdx.x < p.world)
     {

@@ -42,6 +42,20 @@ struct GemvSeg
     float w_scale, alpha, beta, post_scale;
 };
 
+// The exchange of a row-parallel (K-split) shard fused into the kernel's epilogue: every rank's
+// receive area [2 sets][world sources][n_max floats] and flag area [2 sets][kArMaxRowBlocks][world]
+// as mapped into this process (symmetric memory), and this rank's per-row-block sequence counters.
+constexpr int kArMaxWorld = 8;
+constexpr int kArMaxRowBlocks = 2048;
+struct GemvAllReduce
+{
+    float* peer_recv[kArMaxWorld];
+    unsigned int* peer_flag[kArMaxWorld];
+    unsigned int* seq;        // local, [kArMaxRowBlocks]
+    unsigned int n_max;
+    int rank, world;          // world <= 1: no exchange
+};
+
 struct GemvParams
 {
     const uint8_t* W;      // [N, ldw] quantised weight
@@ -63,6 +77,7 @@ struct GemvParams
     unsigned int n_stages;      // ring depth
     unsigned int n_seg;         // linears in this launch (1 unless grouped); the fields above describe the
     GemvSeg seg[kMaxGroup];     // first one, seg[] all of them (unused entries have rb_begin = 0xFFFFFFFF)
+    GemvAllReduce ar;           // fused all-reduce of a row-parallel shard (single linear, beta = 0)
 #ifdef B200_TRACE
     unsigned long long* trace;  // debug builds only: 8 timestamps per CTA
 #endif
@@ -75,7 +90,8 @@ enum : unsigned int
     ST_OK = 0,
     ST_TIMEOUT_FULL = 1,
     ST_TIMEOUT_EMPTY = 2,
-    ST_TIMEOUT_FIXUP = 3
+    ST_TIMEOUT_FIXUP = 3,
+    ST_TIMEOUT_PEER = 4
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
@@ -110,6 +126,16 @@ __device__ __forceinline__ unsigned long long global_timer_ns()
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
+}
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p)
+{
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
 }
 // Bounded wait.  Returns false when the limit ran out (the caller raises the status word).
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity)
@@ -346,7 +372,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty_bar = full_bar + Cfg::kMaxStages;
-    // sh_flags[0] = abort, sh_flags[1] = "this CTA reduces the row block"
+    // sh_flags[0] = abort, [1] = "this CTA reduces the row block", [2] = exchange sequence number, [3] = a peer timed out
     volatile unsigned int* sh_flags = reinterpret_cast<volatile unsigned int*>(smem + 2 * Cfg::kMaxStages * 8);
     unsigned char* stages = smem + Cfg::HEADER_BYTES;
     float* red = reinterpret_cast<float*>(smem + Cfg::HEADER_BYTES + (size_t)p.n_stages * Cfg::STAGE_BYTES);
@@ -647,16 +673,85 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
                 }
             }
         };
+        // Row-parallel shard with the exchange fused in: push this row block's FP32 partial into every
+        // rank's receive area (own rank included), publish the row block's sequence number to every
+        // rank, wait (bounded) for all ranks' numbers, add the slots in rank order and round once.
+        // Every rank computes the same bits, the bits of the separate linear + all-reduce calls.
+        auto exchange_out = [&](auto value_of) {
+            const int W_ = p.ar.world, me = p.ar.rank;
+            if (ctid == 0)
+            {
+                const unsigned int sq = p.ar.seq[rb] + 1;
+                p.ar.seq[rb] = sq;
+                sh_flags[2] = sq;
+                sh_flags[3] = 0;
+            }
+            consumer_bar_sync<CT>();
+            const unsigned int seq = sh_flags[2], set = seq & 1u;
+            const size_t slot = ((size_t)set * W_ + me) * p.ar.n_max;
+            for (unsigned int e = ctid; e < n_out; e += CT)
+            {
+                const unsigned int m = e / R, r = e - m * R, n = n0 + r;
+                if (n < L.N)
+                {
+                    const float o = L.alpha * (value_of(e) * L.post_scale);
+                    const size_t idx = slot + (size_t)m * L.N + n;
+                    for (int rr = 0; rr < W_; rr++) { p.ar.peer_recv[rr][idx] = o; }
+                }
+            }
+            // The barrier orders every thread's peer stores before the flag stores of threads 0..world-1,
+            // whose release at system scope is cumulative over them: no fence per storing thread.
+            consumer_bar_sync<CT>();
+            if ((int)ctid < W_)
+            {
+                st_release_sys(p.ar.peer_flag[ctid] + ((size_t)set * kArMaxRowBlocks + rb) * W_ + me, seq);
+                const unsigned int* f = p.ar.peer_flag[me] + ((size_t)set * kArMaxRowBlocks + rb) * W_ + ctid;
+                const unsigned long long t0 = global_timer_ns();
+                unsigned int spins = 0;
+                while (ld_acquire_sys(f) != seq)
+                {
+                    if ((++spins & 0xFFu) == 0 && global_timer_ns() - t0 > 1000000000ull)
+                    {
+                        atomicMax(p.status, (unsigned int)ST_TIMEOUT_PEER);    // a peer never arrived: report, do not hang
+                        sh_flags[3] = 1;
+                        break;
+                    }
+                }
+            }
+            consumer_bar_sync<CT>();
+            if (sh_flags[3] == 0)
+            {
+                const float* mine = p.ar.peer_recv[me] + (size_t)set * W_ * p.ar.n_max;
+                for (unsigned int e = ctid; e < n_out; e += CT)
+                {
+                    const unsigned int m = e / R, r = e - m * R, n = n0 + r;
+                    if (n < L.N)
+                    {
+                        const size_t idx = (size_t)m * L.N + n;
+                        float acc = __ldcv(mine + idx);    // peers wrote these: never from L1
+                        for (int rr = 1; rr < W_; rr++) { acc += __ldcv(mine + (size_t)rr * p.ar.n_max + idx); }
+                        const long long yi = (long long)m * L.ldy_m + (long long)n * L.ldy_n;
+                        if (p.out_f32) { reinterpret_cast<float*>(L.Y)[yi] = acc; }
+                        else { L.Y[yi] = __bfloat16_as_ushort(__float2bfloat16_rn(acc)); }
+                    }
+                }
+            }
+        };
+        const bool exchange = p.ar.world > 1;
         if (full)
         {
             if (ok)
             {
-                for (unsigned int e = ctid; e < n_out; e += CT)
-                {
+                auto value_of = [&](unsigned int e) {
                     float v = 0.f;
 #pragma unroll
                     for (int w = 0; w < WK; w++) { v += red[w * TILE + e]; }
-                    store_out(e, v);
+                    return v;
+                };
+                if (exchange) { exchange_out(value_of); }
+                else
+                {
+                    for (unsigned int e = ctid; e < n_out; e += CT) { store_out(e, value_of(e)); }
                 }
             }
         }
@@ -691,15 +786,19 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
             if (sh_flags[1] != 0)
             {
                 __threadfence();
-                for (unsigned int e = ctid; e < n_out; e += CT)
-                {
+                auto value_of = [&](unsigned int e) {
                     float v = 0.f;
                     for (unsigned int c = c_first; c <= c_last; c++)
                     {
                         const unsigned int slot = (cta_items(c, gridDim.x, p.total_items, p.gran).beg / p.n_kstages == rb) ? 0u : 1u;
                         v += __ldcg(p.partials + ((size_t)c * 2 + slot) * TILE + e);
                     }
-                    store_out(e, v);
+                    return v;
+                };
+                if (exchange) { exchange_out(value_of); }
+                else
+                {
+                    for (unsigned int e = ctid; e < n_out; e += CT) { store_out(e, value_of(e)); }
                 }
                 if (ctid == 0) { p.counters[c_first] = 0; }
             }

@@ -248,10 +248,18 @@ static int plan_for(int w_type, const void* W, const void* blk, const void* X, c
 // `st`.  Returns the C-ABI code (0 ok, 1 CUDA error, -1 bad argument).
 static int run_linear_wq(const GemvScratch* ws, int w_type, const void* W, const void* blk_scales, float inv_scale, const void* X,
     void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m,
-    unsigned int ldy_n, float alpha, float beta, cudaStream_t st, unsigned int flags, bool decode_only = false)
+    unsigned int ldy_n, float alpha, float beta, cudaStream_t st, unsigned int flags, bool decode_only = false,
+    const GemvAllReduce* ar = nullptr)
 {
     GemvParams p;
     memset(&p, 0, sizeof(p));
+    if (ar != nullptr && ar->world > 1)
+    {
+        // the exchange lives in the decode kernel's epilogue: nothing else takes it
+        if (beta != 0.f || N_out > 16u * (unsigned)kArMaxRowBlocks || (unsigned long long)M_tokens * N_out > ar->n_max) { return -1; }
+        p.ar = *ar;
+        decode_only = true;
+    }
     p.W = (const uint8_t*)W;
     p.blk = (w_type == DT_FP4) ? (const uint8_t*)blk_scales : nullptr;
     p.X = (const uint16_t*)X;

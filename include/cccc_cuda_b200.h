@@ -148,6 +148,29 @@ C_EXPORT unsigned long long cuda_b200_allreduce_recv_bytes(int world, unsigned i
 C_EXPORT unsigned long long cuda_b200_allreduce_flag_bytes(int world);
 C_EXPORT unsigned long long cuda_b200_allreduce_counter_bytes(void);
 
+/* No counterpart in the reference, as above.  The row-parallel (K-split) linear and its all-reduce as
+ * ONE kernel: each CTA of the decode kernel pushes the FP32 partial of its block of output features
+ * into every rank's receive area over NVLink peer stores, publishes that block's sequence number,
+ * waits (bounded, one second) for the other ranks' numbers, adds the `world` partials in rank order
+ * and writes Y once:
+ *     Y[m, n] = bf16( sum over ranks r of alpha * (X_r[m, :] . dq(W_r)[n, :]) ),  the same bits on
+ * every rank, the bits cuda_gemm_wq_bf16 (flags bit 2) followed by cuda_b200_allreduce_f32_to_bf16
+ * produce.  Arguments of the linear as cuda_gemm_wq_bf16 (K, ldw, ldx describe this rank's shard;
+ * beta is 0); flags bit 0 and bit 2 (Y = float32) as there.  The exchange areas are those of
+ * cuda_b200_allreduce_f32_to_bf16 in layout: receive area of cuda_b200_allreduce_recv_bytes(world,
+ * n_max) bytes with n_max >= M_tokens * N_out, flag area of cuda_b200_fused_flag_bytes(world) bytes
+ * and local counters of cuda_b200_fused_counter_bytes() bytes, zeroed once; use areas of their own
+ * for this entry point.  Every rank issues the same sequence of calls.  Returns -1 for a shape the
+ * fused kernel does not take (more than 32 tokens, unaligned operands, more than 32768 features,
+ * M_tokens * N_out > n_max): use the two separate calls then.  world == 1 is the plain linear. */
+C_EXPORT int cuda_gemm_wq_bf16_allreduce(int w_type, const void* W, const void* blk_scales, float inv_scale, const void* X,
+    void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx,
+    unsigned int ldy_m, unsigned int ldy_n, float alpha, const unsigned long long* peer_recv_ptrs,
+    const unsigned long long* peer_flag_ptrs, void* seq_counters, unsigned int n_max, int rank, int world, void* stream,
+    unsigned int flags);
+C_EXPORT unsigned long long cuda_b200_fused_flag_bytes(int world);
+C_EXPORT unsigned long long cuda_b200_fused_counter_bytes(void);
+
 /* ---- additions: the caller side of the path ---------------------------------------------------- */
 
 /* Greedy choice on the device: for each of `rows` rows of BF16 logits (row stride ld elements),

@@ -62,6 +62,30 @@ def _worker(rank, world, port, q):
             out = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
             assert ar(part, out, n) == 0 and capi.check_error("push") == 0
             results.append(("push", call, n, 0, 0, bool(torch.equal(out, want.to(torch.bfloat16))), 0.0, 1.0))
+        # the row-parallel linear with the all-reduce inside the kernel: bit-identical to the two
+        # separate calls, several calls in a row (both buffer sets, whole-row-block and split-k schedules)
+        fused = capi.FusedRowLinear(dist, dist.group.WORLD, rank, world, n_max, torch.device("cuda", rank))
+        for wt in (O.FP8_E5M2, O.FP4_E2M1):
+            for N, K, M in ((4096, 4096, 1), (4096, 12288, 8), (256, 16384, 4), (1000, 2048, 20), (4096, 4096, 1)):
+                W, blk, inv, X = O.make_inputs(wt, N, K, M, seed=3 * N + K + M, scaled=True)
+                s = T.make_shard("row", N, K, world, rank, wt)
+                Ws, bs = T.slice_weight(W, blk, s, N, K, wt)
+                Xs = T.slice_activation(X.reshape(M, K), s)
+                dW = torch.from_numpy(Ws).cuda()
+                dB = torch.from_numpy(bs).cuda() if bs is not None else None
+                dX = torch.from_numpy(Xs.view(np.int16)).cuda()
+                part = torch.zeros(M * N, dtype=torch.float32, device="cuda")
+                two = torch.zeros(M * N, dtype=torch.bfloat16, device="cuda")
+                assert capi.gemm_wq_bf16(wt, dW, dB, inv, dX, part, N, M, s.K, flags=capi.FLAG_OUT_F32) == 0
+                assert ar(part, two, M * N) == 0 and capi.check_error("two") == 0
+                one = torch.full((M * N,), float("nan"), dtype=torch.bfloat16, device="cuda")
+                rc = fused(wt, dW, dB, inv, dX, one, N, M, s.K)
+                ok = rc == 0 and capi.check_error("fused") == 0 and bool(torch.equal(one.view(torch.int16), two.view(torch.int16)))
+                _, ref = O.linear_wq_bf16(wt, W, blk, inv, X, N, M, K)
+                rel, cos = rel_cos(one.float().cpu().numpy().reshape(M, N), ref)
+                results.append(("fused", wt, N, K, M, ok and rel <= 1e-2 and cos >= 0.9999, rel, cos))
+        # a shape the fused kernel does not take is refused, not mangled
+        results.append(("fused-refuses", 0, 0, 0, 0, fused(O.FP8_E5M2, dW, dB, inv, dX, one, 64, 40, 64) == -1, 0.0, 1.0))
         q.put((rank, results))
     finally:
         dist.destroy_process_group()
