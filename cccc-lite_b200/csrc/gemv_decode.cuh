@@ -768,7 +768,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
                     __stcg(mine + e, v);
                 }
             }
-            __threadfence();
+            // The barrier orders every thread's partial stores before thread 0's fence, which is
+            // cumulative over them (one fence per CTA, not one per thread, on either side).
             consumer_bar_sync<CT>();
             const unsigned int c_first = cta_of_item(rb * p.n_kstages, gridDim.x, p.total_items, p.gran);
             const unsigned int c_last = cta_of_item(rb * p.n_kstages + p.n_kstages - 1, gridDim.x, p.total_items, p.gran);
@@ -777,15 +778,16 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
                 unsigned int last = 0;
                 if (ok && sh_flags[0] == 0)
                 {
+                    __threadfence();
                     const unsigned int old = atomicAdd(p.counters + c_first, 1u);
                     last = (old == c_last - c_first) ? 1u : 0u;
+                    __threadfence();
                 }
                 sh_flags[1] = last;
             }
             consumer_bar_sync<CT>();
             if (sh_flags[1] != 0)
             {
-                __threadfence();
                 auto value_of = [&](unsigned int e) {
                     float v = 0.f;
                     for (unsigned int c = c_first; c <= c_last; c++)
