@@ -36,6 +36,15 @@ void DecodeLinears::setAlpha(float attn, float mlp_in, float mlp_out, float head
     alpha_[3] = head;
 }
 
+void DecodeLinears::setPeerExchange(const unsigned long long* recv_ptrs, const unsigned long long* flag_ptrs, void* seq_counters,
+    unsigned int n_max)
+{
+    peer_recv_.assign(recv_ptrs, recv_ptrs + world_);
+    peer_flag_.assign(flag_ptrs, flag_ptrs + world_);
+    peer_seq_ = seq_counters;
+    peer_n_max_ = n_max;
+}
+
 uint16_t* DecodeLinears::buffer(const std::string& name) const
 {
     auto it = buf_.find(name);
@@ -135,6 +144,17 @@ int DecodeLinears::issue(int M, cudaStream_t st)
             launches++;
             return cuda_gemm_wq_bf16((int)l.host.dtype, l.w, l.s, l.host.quant_scale, in, out, (unsigned)l.host.n, (unsigned)M,
                 (unsigned)l.host.k, (unsigned)l.host.k, (unsigned)l.host.k, (unsigned)l.host.n, 1, alpha, 0.f, st, flags);
+        }
+        if (peer_seq_ != nullptr)
+        {
+            const int r = cuda_gemm_wq_bf16_allreduce((int)l.host.dtype, l.w, l.s, l.host.quant_scale, in, out, (unsigned)l.host.n,
+                (unsigned)M, (unsigned)l.host.k, (unsigned)l.host.k, (unsigned)l.host.k, (unsigned)l.host.n, 1, alpha, peer_recv_.data(),
+                peer_flag_.data(), peer_seq_, peer_n_max_, rank_, world_, st, flags);
+            if (r != -1)
+            {
+                launches++;
+                return r;
+            }
         }
         if (!exchange_) { return -1; }
         launches += 2;

@@ -50,6 +50,10 @@ public:
     bool load(GpuControl* gpu, const BinFile& file, const ModelDims& dims, int max_tokens, int world, int rank, std::string* err);
     void setHook(HookFn f) { hook_ = std::move(f); }
     void setExchange(ExchangeFn f) { exchange_ = std::move(f); }
+    // Peer mappings for cuda_gemm_wq_bf16_allreduce (host arrays of `world` device pointers, the local
+    // sequence counters, the receive areas' capacity in floats): row-parallel linears then run with the
+    // all-reduce inside their kernel, and the exchange function only serves shapes that kernel refuses.
+    void setPeerExchange(const unsigned long long* recv_ptrs, const unsigned long long* flag_ptrs, void* seq_counters, unsigned int n_max);
     void setAlpha(float attn, float mlp_in, float mlp_out, float head);    // per-projection output scale (default 1)
 
     // One step for M sequences: x_host holds M rows of `hidden` BF16 values (the embedded tokens).
@@ -86,6 +90,9 @@ private:
     std::map<int, cudaGraphExec_t> graphs_;
     HookFn hook_;
     ExchangeFn exchange_;
+    std::vector<unsigned long long> peer_recv_, peer_flag_;
+    void* peer_seq_ = nullptr;
+    unsigned int peer_n_max_ = 0;
     float alpha_[4] = { 1.f, 1.f, 1.f, 1.f };
     size_t weight_bytes_ = 0;
     int launches_per_step_ = 0;
