@@ -11,11 +11,13 @@
 //
 // Per 64-wide k block and CTA:
 //   * the TMA lane copies TH x [128 tokens][64 k] BF16 activations (swizzle 128 B, rows past M zero),
-//   * eight warps dequantise [128*FH features][64 k] weights into the swizzled A stage,
-//   * one lane of rank 1 forwards "my stage is full" to a barrier of the leader with ONE remote
-//     arrive (remote arrives from all eight warps, or activation copies that complete on the
-//     leader's barrier, measured 40 % slower),
-//   * the leader issues 4*FH*TH UMMAs and commits to the stage's "empty" barrier of BOTH CTAs.
+//   * 8 or 16 warps dequantise [128*FH features][64 k] weights into the swizzled A stage,
+//   * both arrive on ONE "full" barrier of the k block (slot kb % 8); one lane of rank 1 forwards its
+//     completion to the leader's barrier with ONE remote arrive at CTA scope (remote arrives from all
+//     dequantise warps, activation copies completing on the leader's barrier, or a release at
+//     cluster scope each measured 40 % slower),
+//   * the leader issues 4*FH*TH UMMAs and commits to ONE "done" barrier of the k block in BOTH CTAs,
+//     which frees the activation stage and the weight stage (rings of different depth).
 // After the last k block each CTA reads its accumulators (tcgen05.ld) and stores its features.
 // Every mbarrier wait is bounded; a CTA whose wait ran out raises the status word and drains.  Both
 // CTAs always reach the cluster barrier before the TMEM columns are freed, so neither leaves while
@@ -135,12 +137,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
     constexpr int X_BYTES = TH * PP_XH_BYTES;
     static_assert(FH * TH * PP_TOKENS * PF_BM * 2 <= pp_ring_bytes(FH, TH), "the epilogue tiles reuse the ring memory");
     constexpr int TMEM_COLS = PP_TOKENS * FH * TH;
-    uint64_t* full_x = reinterpret_cast<uint64_t*>(smem);    // [NX] my activation halves have landed
-    uint64_t* empty_x = full_x + 8;                          // [NX] the UMMAs that read the activation stage are done
-    uint64_t* full_a = empty_x + 8;                          // [NA] my weight tile is converted
-    uint64_t* empty_a = full_a + 8;                          // [NA] the UMMAs that read the weight stage are done
-    uint64_t* peer_full = empty_a + 8;                       // [8] leader only: rank 1 has both operands of k block kb (slot kb % 8)
-    uint64_t* acc_full = peer_full + 8;                      // [1]
+    // One barrier pair per k block in flight (slot kb % 8), whatever the depth of the two stage rings:
+    // every tcgen05 / mbarrier instruction of the leader's issue loop costs 50-100 cycles of a single
+    // warp's time, so the loop waits on ONE barrier and commits to ONE per k block.
+    //   full[kb % 8]: my activation bytes (TMA) + my dequantise warps (+ on the leader: rank 1's forward)
+    //   done[kb % 8]: the UMMAs of k block kb are complete (multicast commit to both CTAs)
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);      // [8]
+    uint64_t* done = full + 8;                               // [8]
+    uint64_t* acc_full = done + 8;                           // [1]
+    constexpr unsigned int RING = 8;
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
     volatile unsigned int* abort_flag = reinterpret_cast<volatile unsigned int*>(tmem_base_slot + 1);
     unsigned char* stages = smem + PF_HEADER_BYTES;    // weight ring, then activation ring
@@ -174,17 +179,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
 
     if (threadIdx.x == 0)
     {
-        for (int s = 0; s < NX; s++)
+        for (unsigned int s = 0; s < RING; s++)
         {
-            mbar_init(full_x + s, 1);
-            mbar_init(empty_x + s, 1);
+            mbar_init(full + s, 1 + DQW + (rank == 0 ? 1 : 0));
+            mbar_init(done + s, 1);
         }
-        for (int s = 0; s < NA; s++)
-        {
-            mbar_init(full_a + s, DQW);
-            mbar_init(empty_a + s, 1);
-        }
-        for (int s = 0; s < 8; s++) { mbar_init(peer_full + s, 1); }
         mbar_init(acc_full, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -206,7 +205,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
             for (unsigned int kb = 0; kb < n_kblocks; kb++)
             {
                 const unsigned int s = kb % NX;
-                if (kb >= NX && (*abort_flag != 0 || !mbar_wait_bounded(empty_x + s, ((kb / NX) - 1) & 1u)))
+                if (kb >= NX && (*abort_flag != 0 || !mbar_wait_bounded(done + ((kb - NX) % RING), ((kb - NX) / RING) & 1u)))
                 {
                     ok = false;
                     atomicMax(p.status, (unsigned int)ST_TIMEOUT_EMPTY);
@@ -214,15 +213,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
                     break;
                 }
                 PP_STAMP(0, kb);
-                mbar_expect_tx(full_x + s, X_BYTES);
+                mbar_expect_tx(full + (kb % RING), X_BYTES);
 #pragma unroll
                 for (int th = 0; th < TH; th++)
                 {
                     // a part without live tokens is still copied (zero fill) so that the byte count is fixed
                     tma_load_2d(xring + s * X_BYTES + th * PP_XH_BYTES, &tmX, (int)(kb * PF_BK),
-                        (int)(m0 + th * PP_TOKENS + rank * (live[th] / 2)), full_x + s);
+                        (int)(m0 + th * PP_TOKENS + rank * (live[th] / 2)), full + (kb % RING));
                 }
-                mbar_arrive(full_x + s);
+                mbar_arrive(full + (kb % RING));
                 PP_STAMP(1, kb);
                 issued = kb + 1;
             }
@@ -230,7 +229,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
             {
                 // wait (bounded) for my copies in flight before the CTA may leave
                 const unsigned int first = issued > NX ? issued - NX : 0;
-                for (unsigned int kb = first; kb < issued; kb++) { mbar_wait_bounded(full_x + (kb % NX), (kb / NX) & 1u); }
+                // The barrier also counts the dequantise warps, which may have given up too, so it may
+                // never complete: the copies land within microseconds, 100 us per barrier is ample.
+                for (unsigned int kb = first; kb < issued; kb++)
+                {
+                    const unsigned long long t0 = global_timer_ns();
+                    while (!mbar_try_wait(full + (kb % RING), (kb / RING) & 1u) && global_timer_ns() - t0 < 100000ull) {}
+                }
             }
         }
     }
@@ -239,11 +244,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
         if (lane == 0 && rank != 0)
         {
             // =========================== rank 1: forward "stage full" to the leader ===========================
-            const uint32_t peer_bar0 = map_to_cta(peer_full, 0);
+            const uint32_t peer_bar0 = map_to_cta(full, 0);
             for (unsigned int kb = 0; kb < n_kblocks; kb++)
             {
-                bool w = *abort_flag == 0 && mbar_wait_bounded(full_x + (kb % NX), (kb / NX) & 1u);
-                w = w && mbar_wait_bounded(full_a + (kb % NA), (kb / NA) & 1u);
+                const bool w = *abort_flag == 0 && mbar_wait_bounded(full + (kb % RING), (kb / RING) & 1u);
                 if (!w)
                 {
                     atomicMax(p.status, (unsigned int)ST_TIMEOUT_FULL);
@@ -266,9 +270,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
             for (unsigned int kb = 0; kb < n_kblocks && ok; kb++)
             {
                 const unsigned int sx = kb % NX, sa = kb % NA;
-                bool w = *abort_flag == 0 && mbar_wait_bounded(full_x + sx, (kb / NX) & 1u);
-                w = w && mbar_wait_bounded(full_a + sa, (kb / NA) & 1u);
-                w = w && mbar_wait_bounded(peer_full + (kb & 7u), (kb >> 3) & 1u);
+                const bool w = *abort_flag == 0 && mbar_wait_bounded(full + (kb % RING), (kb / RING) & 1u);
                 PP_STAMP(6, kb);
                 if (!w)
                 {
@@ -301,8 +303,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
                         }
                     }
                 }
-                umma_commit_pair(empty_x + sx);
-                umma_commit_pair(empty_a + sa);
+                umma_commit_pair(done + (kb % RING));
                 PP_STAMP(7, kb);
                 }
                 __syncwarp();
@@ -374,7 +375,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
         for (unsigned int kb = 0; kb < n_kblocks; kb++)
         {
             const unsigned int s = kb % NA;
-            if (ok && kb >= NA && (*abort_flag != 0 || !mbar_wait_bounded(empty_a + s, ((kb / NA) - 1) & 1u)))
+            if (ok && kb >= NA && (*abort_flag != 0 || !mbar_wait_bounded(done + ((kb - NA) % RING), ((kb - NA) / RING) & 1u)))
             {
                 ok = false;
                 if (*abort_flag == 0)
@@ -407,7 +408,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
             {
                 fence_proxy_async();    // make the generic-proxy stores visible to the tensor cores' reads
                 __syncwarp();
-                if (lane == 0) { mbar_arrive(full_a + s); }
+                if (lane == 0) { mbar_arrive(full + (kb % RING)); }
                 if (tid == 0) { PP_STAMP(3, kb); }
             }
         }

@@ -42,7 +42,19 @@ static int pf_pick_variant(int w_type, unsigned int N, unsigned int M, unsigned 
     const unsigned long long pairs_t512 = (unsigned long long)((M + 511) / 512) * f256;
     const unsigned long long pairs_256 = (unsigned long long)((M + 255) / 256) * f256;
     const unsigned long long want = (unsigned long long)sm_count / 3;    // pairs: two thirds of the SMs
-    if (pairs_t512 >= want) { return PFV_PAIR_T512; }
+    if (pairs_t512 >= want)
+    {
+        // Both pair tiles are possible: count waves.  One 256 x 512 tile occupies a pair of SMs for two
+        // units of time; 256 x 256 tiles run two per SM pair, so a full wave of them also takes two
+        // units and a last wave that fits one CTA per SM takes one.  The smaller tile converts each
+        // weight twice as often and measured 8-12 % slower at equal occupancy, so it is only taken when
+        // it saves a clear part of a wave (q+k+v at 2048 tokens: 96 large tiles on 74 SM pairs).
+        const unsigned long long slots = (unsigned long long)sm_count / 2;    // SM pairs
+        const double cost_t512 = 2.0 * (double)((pairs_t512 + slots - 1) / slots);
+        const unsigned long long rem = pairs_256 % (2 * slots);
+        const double cost_256 = (2.0 * (double)(pairs_256 / (2 * slots)) + (rem == 0 ? 0.0 : (rem <= slots ? 1.0 : 2.0))) / 0.88;
+        return cost_256 < 0.9 * cost_t512 ? PFV_PAIR : PFV_PAIR_T512;
+    }
     if (M > 128 && pairs_256 >= want) { return PFV_PAIR; }
     return PFV_CTA_T128;
 }
