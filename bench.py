@@ -378,6 +378,28 @@ def gpu_arm(args):
         ms_e2e = max_over_ranks(e2.elapsed_time(e3))
         assert capi.check_error("bench") == 0
 
+        # ---- outside the timed regions: the fused exchange against the two-kernel form, bit for bit ----
+        exchange_check = None
+        if world > 1 and "fused_row_linear" in bufs:
+            try:
+                bufs["x"].copy_(x_host, non_blocking=True)
+                run_step(torch, dist, capi, wt, calls, bufs, M, world, flags)
+                stream.synchronize()
+                fused_logits = src_logits.clone()
+                fused = bufs.pop("fused_row_linear")
+                bufs["push_allreduce"] = capi.PushAllReduce(dist, dist.group.WORLD, rank, world, M * dims[0], dev)
+                bufs["x"].copy_(x_host, non_blocking=True)
+                run_step(torch, dist, capi, wt, calls, bufs, M, world, flags)
+                stream.synchronize()
+                same = torch.tensor([1 if torch.equal(fused_logits, src_logits) else 0], device=dev)
+                dist.all_reduce(same, op=dist.ReduceOp.MIN)
+                bufs.pop("push_allreduce", None)
+                bufs["fused_row_linear"] = fused
+                exchange_check = "logits identical to the two-kernel form on every rank" if int(same.item()) == 1 else "MISMATCH"
+                assert capi.check_error("exchange check") == 0
+            except Exception as e:  # the check must not cost the measurement
+                exchange_check = f"not run ({type(e).__name__}: {e})"
+
     ms_per_step = ms / args.steps
     value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
     e2e_value = bytes_per_step / (ms_e2e / args.steps * 1e-3) / 1e9
@@ -398,7 +420,7 @@ def gpu_arm(args):
             "workload": f"{'llama-3.1-8b w4a16' if args.wtype == 'fp4' else 'qwen3-8b w8a16'} decode linears: "
                         f"{dims[5]} layers x (q,k,v,o,gate,up,down) + lm_head, M={M}",
             "tokens": M, "bytes_per_step": bytes_per_step, "l2": "7.5 GB of distinct weights per step (> L2)",
-            "cuda_graph": graph is not None, "pdl": bool(args.pdl), "grouped_qkv_gateup": bool(args.group), "allreduce": allreduce, "parallelism": f"tp{world}",
+            "cuda_graph": graph is not None, "pdl": bool(args.pdl), "grouped_qkv_gateup": bool(args.group), "allreduce": allreduce, "exchange_check": exchange_check if world > 1 else None, "parallelism": f"tp{world}",
             "tok_per_s": round(M / (ms_per_step * 1e-3), 1),
         },
         "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": x_host.numel() * 2,
