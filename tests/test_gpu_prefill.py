@@ -162,3 +162,27 @@ def test_prefill_tile_shapes_agree_bit_for_bit(wt):
     bsub = blk.reshape(N, K // 16)[rows] if blk is not None else None
     _, y32 = O.linear_wq_bf16(wt, Wsub.reshape(-1), bsub, inv, X.reshape(M, K)[toks], rows.size, toks.size, K)
     assert_close(O.bf16_bits_to_f32(outs[0]).reshape(M, N)[np.ix_(toks, rows)], y32, "oracle subset")
+
+
+@pytest.mark.parametrize("wt", [O.FP8_E5M2, O.FP4_E2M1])
+@pytest.mark.parametrize("pad", [8, 3])
+@pytest.mark.parametrize("variant", [0, 1, 4, 6])
+def test_prefill_padded_output_rows_keep_their_padding(wt, pad, variant):
+    """Y with a row stride larger than N: a multiple of 8 elements keeps the TMA-store epilogue (the
+    store must clip at N, not at the stride), any other stride takes the register epilogue; the padding
+    columns are never written in either."""
+    import torch
+
+    c = capi()
+    N, K, M = 520, 256, 300
+    W, blk, inv, X = O.make_inputs(wt, N, K, M, seed=17 + pad + variant, scaled=True)
+    ld = N + pad
+    dW, dX = to_dev(W), to_dev(X)
+    dB = to_dev(blk) if blk is not None else None
+    y = torch.full((M * ld,), 0x4140, dtype=torch.int16, device="cuda")    # bf16 12.0 everywhere
+    assert c.gemm_wq_bf16(wt, dW, dB, inv, dX, y, N, M, K, ldy_m=ld, flags=c.flag_prefill_variant(variant)) == 0
+    assert c.check_error("padded") == 0
+    got = O.bf16_bits_to_f32(from_dev_u16(y)).reshape(M, ld)
+    _, y32 = O.linear_wq_bf16(wt, W, blk, inv, X, N, M, K)
+    assert_close(got[:, :N], y32, (wt, pad, variant))
+    assert np.all(got[:, N:] == 12.0)
