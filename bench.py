@@ -456,7 +456,7 @@ def gpu_arm(args):
 
 
 def prefill_probe(torch, capi, dims, wtype, dev, peaks):
-    """BASELINE config 4 in brief: M=2048 tokens through one layer's seven linears (tcgen05 kernels),
+    """The prefill configuration (config 4) in brief: M=2048 tokens through one layer's seven linears (tcgen05 kernels),
     q/k/v and gate/up as grouped calls on their shared input, timed with CUDA events; reported next to
     the decode line as TFLOP/s of 2*M*N*K."""
     M = 2048

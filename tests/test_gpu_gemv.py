@@ -53,7 +53,7 @@ def test_ragged_and_config_shapes(wt, N, K, M):
 
 
 def test_config1_unit_scale_w8a16():
-    """BASELINE config 1: x[1,4096] ~ N(0,1) BF16, W[4096,4096] ~ N(0,0.02) E5M2, scale 1.0, seed 0."""
+    """Benchmark configuration 1: x[1,4096] ~ N(0,1) BF16, W[4096,4096] ~ N(0,0.02) E5M2, scale 1.0, seed 0."""
     N = K = 4096
     W, blk, inv, X = O.make_inputs(O.FP8_E5M2, N, K, 1, seed=0, scaled=False)
     assert inv == 1.0
@@ -169,7 +169,7 @@ def test_against_reference_gpu_path(wt):
 
 
 def test_full_size_lm_head_rows_against_oracle():
-    """BASELINE config 2 lm_head [151936, 4096] at M=1: every output checked through a row subset
+    """Benchmark configuration 2, lm_head [151936, 4096] at M=1: every output checked through a row subset
     (the oracle on the full matrix would take minutes) plus a checksum over all rows on device."""
     import torch
 

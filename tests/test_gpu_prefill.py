@@ -62,7 +62,7 @@ def test_prefill_alpha_beta_and_strides(wt):
 
 @pytest.mark.parametrize("wt", WTS)
 def test_prefill_config4_shape_against_reference_gpu_path(wt):
-    """BASELINE config 4 (M=2048 tokens) on the q projection shape, against the reference's own
+    """Benchmark configuration 4 (M=2048 tokens) on the q projection shape, against the reference's own
     dequantise-then-cuBLAS path on the same buffers, plus an oracle check on a row subset."""
     import torch
 
@@ -139,7 +139,7 @@ def test_prefill_every_tile_shape_direct_epilogue(wt, variant):
 
 @pytest.mark.parametrize("wt", WTS)
 def test_prefill_tile_shapes_agree_bit_for_bit(wt):
-    """At BASELINE config 4's token count every tile shape accumulates the same products in the same
+    """At the token count of benchmark configuration 4 every tile shape accumulates the same products in the same
     k order in FP32, so the BF16 outputs are identical; the default choice is one of them."""
     import torch
 
