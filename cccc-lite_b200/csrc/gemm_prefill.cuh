@@ -3,21 +3,23 @@
 //
 // One CTA computes a tile of 128 or 256 output features x up to 256 tokens over the whole K range.
 // With 128 features two CTAs share an SM (each owns part of the 512 TMEM columns), so one CTA's
-// epilogue overlaps the other's main loop.  The kernel is bound by shared-memory bandwidth: a 1-CTA
-// UMMA (M=128, N=256, K=16) reads 12 KB of operands per 128 cycles (96 B/clk) and the stage fills add
-// as much at full rate (activations 64 B/clk, converted weights 32 B/clk) against 128 B/clk per SM.
-// The 256-feature tile (one CTA per SM, all 512 TMEM columns, three stages) lets two weight tiles
-// share each activation tile, which cuts the fills to 64 B/clk.  Per 64-wide k block:
+// epilogue overlaps the other's main loop; the 256-feature tile (one CTA per SM, all 512 TMEM
+// columns, three stages) lets two weight tiles share each activation tile.  Large problems take the
+// CTA-pair kernel (gemm_prefill_pair.cuh); this one serves those with too few tiles for it.
+// Per 64-wide k block:
 //   * a TMA lane copies the BF16 activation tile [256 (or 128) tokens][64 k] into shared memory with the
 //     128-byte swizzle (token rows past M are zero-filled by the TMA),
 //   * eight warps load the quantised weight tile [128 features][64 k] from global memory (16 bytes
-//     per thread, prefetched one k block ahead), dequantise it to BF16 exactly as the reference's
-//     conversion kernels do, and store it into the A-operand stage in the same K-major 128-byte
-//     swizzled layout the UMMA descriptor names,
-//   * one lane issues four tcgen05.mma (M=128, N=tokens rounded up to 16, K=16) and commits to the
-//     barrier that frees the stage.
+//     per thread, prefetched two k blocks ahead), dequantise it to BF16 exactly as the reference's
+//     conversion kernels do, store it into the A-operand stage in the same K-major 128-byte swizzled
+//     layout the UMMA descriptor names, convert the next block while those stores land, then fence,
+//   * the MMA warp (one elected lane issuing) issues four tcgen05.mma (M=128, N=tokens rounded up to
+//     16, K=16) per 128 features and commits to the barrier that frees the stage.
 // After the last k block the eight warps read the accumulator from TMEM (tcgen05.ld, one TMEM lane =
-// one output feature per thread), apply alpha/beta and store BF16.
+// one output feature per thread) and apply alpha; BF16 output with contiguous features goes through
+// a tile in the idle stage memory and one TMA store (which clips ragged edges), anything else (beta,
+// FP32 output, transposed Y) is stored from registers.  A launch may hold up to three linears that
+// share their activations: blockIdx.y walks their feature tiles.
 // Every wait is bounded; on expiry the status word is raised and the CTA drains, waits (bounded)
 // for its copies in flight, frees its TMEM columns and returns.
 #pragma once
