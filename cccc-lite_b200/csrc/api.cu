@@ -18,11 +18,11 @@ void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 // [8 KB, ...)         FP32 partial tiles
 struct Workspace
 {
-    unsigned char* base = nullptr;
+    std::atomic<unsigned char*> base{ nullptr };    // published last (release) once `scratch` is complete
     size_t bytes = 0;
     bool tried = false;
     GemvScratch scratch;
-    unsigned int* status() const { return reinterpret_cast<unsigned int*>(base); }
+    unsigned int* status() const { return reinterpret_cast<unsigned int*>(base.load(std::memory_order_acquire)); }
 };
 constexpr size_t kPartialBytes = 8u << 20;
 static Workspace g_ws[kMaxDevices];
@@ -33,9 +33,9 @@ static Workspace* workspace()
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { return nullptr; }
     Workspace& w = g_ws[dev];
-    if (w.base) { return &w; }
+    if (w.base.load(std::memory_order_acquire)) { return &w; }
     std::lock_guard<std::mutex> lock(g_ws_mutex);
-    if (w.base) { return &w; }
+    if (w.base.load(std::memory_order_relaxed)) { return &w; }
     if (w.tried) { return nullptr; }
     w.tried = true;
     w.scratch.device = dev;
@@ -56,7 +56,7 @@ static Workspace* workspace()
     w.scratch.n_counters = 1024;
     w.scratch.partials = reinterpret_cast<float*>((unsigned char*)p + 8192);
     w.scratch.partial_bytes = kPartialBytes;
-    w.base = (unsigned char*)p;
+    w.base.store((unsigned char*)p, std::memory_order_release);
     return &w;
 }
 
@@ -90,14 +90,14 @@ int sync_and_report(const char* label)
         return 1;
     }
     int dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_ws[dev].base)
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_ws[dev].base.load(std::memory_order_acquire))
     {
         unsigned int st = 0;
         if (cudaMemcpy(&st, g_ws[dev].status(), sizeof(st), cudaMemcpyDeviceToHost) == cudaSuccess && st != 0)
         {
             fprintf(stderr, "%s kernel launch failed: a bounded wait ran out (status %u)\n", label, st);
             // A run that gave up may have left arrival counters behind: start clean again.
-            cudaMemset(g_ws[dev].base, 0, 8192);
+            cudaMemset(g_ws[dev].base.load(std::memory_order_acquire), 0, 8192);
             return 1;
         }
     }

@@ -24,6 +24,8 @@
 // for its copies in flight, frees its TMEM columns and returns.
 #pragma once
 
+#include <atomic>
+
 #include "common.cuh"
 #include "gemv_decode.cuh"
 #include "tensor_map.cuh"
@@ -72,9 +74,6 @@ struct PrefillParams
     unsigned int* status;
     unsigned int M, K;
     unsigned int out_f32;
-#ifdef B200_TRACE
-    unsigned long long* trace;    // debug builds only: [rank][role 0..15][k block 0..255] timestamps of CTA pair (0, 0)
-#endif
 };
 
 // The three output tensor maps of a launch (unused ones are zero).
@@ -555,15 +554,15 @@ static int launch_prefill_bn(const CUtensorMap& tmX, const PrefillYMaps& tmY, co
     cudaStream_t stream)
 {
     auto kernel = gemm_wq_prefill_kernel<WT, SCALED, BN, FH>;
-    static bool attr_set[64] = {};
-    if (!attr_set[device])
+    static std::atomic<bool> attr_set[64];    // zero-initialised; setting the attribute twice is harmless
+    if (!attr_set[device].load(std::memory_order_acquire))
     {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pf_smem_bytes(BN, FH)) != cudaSuccess)
         {
             report_launch("gemm_wq_bf16");
             return 1;
         }
-        attr_set[device] = true;
+        attr_set[device].store(true, std::memory_order_release);
     }
     const dim3 grid((pp.M + BN - 1) / BN, feature_tiles);
     count_launch();

@@ -24,6 +24,8 @@
 // the other may still read its shared memory or signal its barriers.
 #pragma once
 
+#include <atomic>
+
 #include "gemm_prefill.cuh"
 
 namespace b200
@@ -154,11 +156,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
 
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_cta_rank();
-#ifdef B200_TRACE
-#define PP_STAMP(role, kb) do { if (p.trace && blockIdx.x < 2 && blockIdx.y == 0 && (kb) < 256u && (threadIdx.x & 31u) == 0) { p.trace[(rank * 16 + (role)) * 256 + (kb)] = global_timer_ns(); } } while (0)
-#else
-#define PP_STAMP(role, kb) do { } while (0)
-#endif
     const unsigned int m0 = (blockIdx.x >> 1) * (PP_TOKENS * TH);     // first token of the pair's tile
     // which linear of the launch this feature tile belongs to
     unsigned int si = 0;
@@ -212,7 +209,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
                     *abort_flag = 1;
                     break;
                 }
-                PP_STAMP(0, kb);
                 mbar_expect_tx(full + (kb % RING), X_BYTES);
 #pragma unroll
                 for (int th = 0; th < TH; th++)
@@ -222,7 +218,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
                         (int)(m0 + th * PP_TOKENS + rank * (live[th] / 2)), full + (kb % RING));
                 }
                 mbar_arrive(full + (kb % RING));
-                PP_STAMP(1, kb);
                 issued = kb + 1;
             }
             if (!ok)
@@ -255,7 +250,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
                     break;
                 }
                 mbar_arrive_cluster(peer_bar0 + (kb & 7u) * 8);
-                PP_STAMP(6, kb);
             }
         }
         else if (rank == 0)
@@ -271,7 +265,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
             {
                 const unsigned int sx = kb % NX, sa = kb % NA;
                 const bool w = *abort_flag == 0 && mbar_wait_bounded(full + (kb % RING), (kb / RING) & 1u);
-                PP_STAMP(6, kb);
                 if (!w)
                 {
                     ok = false;
@@ -304,7 +297,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
                     }
                 }
                 umma_commit_pair(done + (kb % RING));
-                PP_STAMP(7, kb);
                 }
                 __syncwarp();
             }
@@ -384,7 +376,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
                     *abort_flag = 1;
                 }
             }
-            if (tid == 0) { PP_STAMP(2, kb); }
             if (ok)
             {
                 const uint32_t a_addr = smem_u32(stages + s * A_BYTES);
@@ -409,7 +400,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
                 fence_proxy_async();    // make the generic-proxy stores visible to the tensor cores' reads
                 __syncwarp();
                 if (lane == 0) { mbar_arrive(full + (kb % RING)); }
-                if (tid == 0) { PP_STAMP(3, kb); }
             }
         }
 
@@ -528,15 +518,15 @@ static int launch_prefill_pair(const CUtensorMap& tmX, const PrefillYMaps& tmY, 
     cudaStream_t stream)
 {
     auto kernel = gemm_wq_prefill_pair_kernel<WT, SCALED, FH, TH, DQW>;
-    static bool attr_set[64] = {};
-    if (!attr_set[device])
+    static std::atomic<bool> attr_set[64];    // zero-initialised; setting the attribute twice is harmless
+    if (!attr_set[device].load(std::memory_order_acquire))
     {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pp_smem_bytes(FH, TH)) != cudaSuccess)
         {
             report_launch("gemm_wq_bf16");
             return 1;
         }
-        attr_set[device] = true;
+        attr_set[device].store(true, std::memory_order_release);
     }
     const dim3 grid(2 * ((pp.M + PP_TOKENS * TH - 1) / (PP_TOKENS * TH)), feature_tiles);
     count_launch();

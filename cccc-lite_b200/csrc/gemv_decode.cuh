@@ -44,14 +44,21 @@ struct GemvSeg
 
 // The exchange of a row-parallel (K-split) shard fused into the kernel's epilogue: every rank's
 // receive area [2 sets][world sources][n_max floats] and flag area [2 sets][kArMaxRowBlocks][world]
-// as mapped into this process (symmetric memory), and this rank's per-row-block sequence counters.
+// as mapped into this process (symmetric memory), and this rank's call counters.
+// One counter per exchange area numbers the calls: seq[0] = fused calls completed on this area,
+// seq[1] = CTAs of the running call that have finished (the last one to finish resets it and
+// advances seq[0]).  The call number c = seq[0] + 1 is the value published in the flags and its
+// low bit picks the slot set, so the two sets alternate call by call whatever the calls' shapes
+// are: a rank can only reach call c + 1 after every peer has published flags of call c, that is
+// after every peer has finished reading the slots of call c - 1, which are the ones call c + 1
+// overwrites.
 constexpr int kArMaxWorld = 8;
 constexpr int kArMaxRowBlocks = 2048;
 struct GemvAllReduce
 {
     float* peer_recv[kArMaxWorld];
     unsigned int* peer_flag[kArMaxWorld];
-    unsigned int* seq;        // local, [kArMaxRowBlocks]
+    unsigned int* seq;        // local: [0] completed calls, [1] finished CTAs of the running call
     unsigned int n_max;
     int rank, world;          // world <= 1: no exchange
 };
@@ -78,9 +85,6 @@ struct GemvParams
     unsigned int n_seg;         // linears in this launch (1 unless grouped); the fields above describe the
     GemvSeg seg[kMaxGroup];     // first one, seg[] all of them (unused entries have rb_begin = 0xFFFFFFFF)
     GemvAllReduce ar;           // fused all-reduce of a row-parallel shard (single linear, beta = 0)
-#ifdef B200_TRACE
-    unsigned long long* trace;  // debug builds only: 8 timestamps per CTA
-#endif
 };
 
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;    // 2 s
@@ -381,12 +385,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const ItemRange items = cta_items(blockIdx.x, gridDim.x, p.total_items, p.gran);
     const unsigned int n_items = items.end - items.beg;
-#ifdef B200_TRACE
-#define B200_STAMP(slot) do { if (p.trace) { p.trace[(size_t)blockIdx.x * 8 + (slot)] = global_timer_ns(); } } while (0)
-#else
-#define B200_STAMP(slot) do { } while (0)
-#endif
-    if (threadIdx.x == 0) { B200_STAMP(0); }
 
     if (threadIdx.x == 0)
     {
@@ -433,11 +431,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
         // Weights do not depend on the previous kernel of the stream: prefetch the first ring of
         // stages before waiting for it; activations only after.
         const unsigned int pre = min(NS, n_items);
-        B200_STAMP(1);
         for (unsigned int it = 0; it < pre; it++) { issue_weights(it); }
-        B200_STAMP(2);
         pdl_wait();
-        B200_STAMP(3);
         for (unsigned int it = 0; it < pre; it++) { issue_acts(it); }
         bool ok = true;
         unsigned int issued = pre;
@@ -514,7 +509,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
                 }
             }
             if (!ok) { continue; }
-            if (it == 0 && threadIdx.x == 0) { B200_STAMP(4); }
             const unsigned int ks = ks0 + j;
             const unsigned int kval = min((unsigned int)Cfg::SKE, p.K - ks * Cfg::SKE);
             const unsigned int nsteps = kval / Cfg::KSTEP;    // beyond K the TMA fills zeros; skip them
@@ -632,7 +626,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
         }
 
         // ---- end of the segment: combine the k-split warps, then write or hand over ----
-        if (it >= n_items && threadIdx.x == 0) { B200_STAMP(5); }
         float* myred = red + wk * TILE;
 #pragma unroll
         for (int rt = 0; rt < RT; rt++)
@@ -681,9 +674,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
             const int W_ = p.ar.world, me = p.ar.rank;
             if (ctid == 0)
             {
-                const unsigned int sq = p.ar.seq[rb] + 1;
-                p.ar.seq[rb] = sq;
-                sh_flags[2] = sq;
+                // seq[0] only moves when the last CTA of a call has finished, so every CTA of this
+                // call reads the same number here
+                sh_flags[2] = __ldcg(p.ar.seq) + 1;
                 sh_flags[3] = 0;
             }
             consumer_bar_sync<CT>();
@@ -807,7 +800,17 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
         }
         consumer_bar_sync<CT>();    // `red` and sh_flags[1] are reused by the next segment
     }
-    if (threadIdx.x == 0) { B200_STAMP(6); }
+    if (p.ar.world > 1 && ctid == 0)
+    {
+        // this CTA has finished the call; the last one to do so closes the call on this exchange area
+        const unsigned int c = __ldcg(p.ar.seq) + 1;
+        __threadfence();
+        if (atomicAdd(p.ar.seq + 1, 1u) == gridDim.x - 1)
+        {
+            p.ar.seq[1] = 0;
+            __stcg(p.ar.seq, c);
+        }
+    }
 }
 
 // ---- plain kernel: any shape, stride or alignment ----------------------------------------------------

@@ -8,6 +8,7 @@
 #include "tensor_map.cuh"
 #include "prefill_launch.cuh"
 
+#include <atomic>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -40,24 +41,6 @@ static bool is_pow2_scale(float s)
     return m == 0.5f && e >= -39 && e <= 41;    // 2^-40 .. 2^40
 }
 
-#ifdef B200_TRACE
-// debug builds only: a caller-provided buffer receives 8 timestamps per CTA per launch
-static unsigned long long* g_trace_base = nullptr;
-static size_t g_trace_off = 0, g_trace_cap = 0;
-extern "C" __attribute__((visibility("default"))) void cuda_b200_trace_set(void* buf, size_t n_u64)
-{
-    g_trace_base = (unsigned long long*)buf;
-    g_trace_off = 0;
-    g_trace_cap = n_u64;
-}
-static unsigned long long* trace_next(unsigned int grid)
-{
-    if (!g_trace_base || g_trace_off + (size_t)grid * 8 > g_trace_cap) { return nullptr; }
-    unsigned long long* p = g_trace_base + g_trace_off;
-    g_trace_off += (size_t)grid * 8;
-    return p;
-}
-#endif
 
 template <class Cfg, bool SCALED>
 static int launch_gemv_cfg(GemvParams p, const GemvScratch* ws, cudaStream_t stream, bool pdl)
@@ -141,29 +124,26 @@ static int launch_gemv_cfg(GemvParams p, const GemvScratch* ws, cudaStream_t str
                    Cfg::XSLABS, Cfg::XSWZ);
     if (!ok)
     {
-        static bool told = false;
-        if (!told)
+        static std::atomic<bool> told{ false };
+        if (!told.exchange(true))
         {
-            told = true;
             fprintf(stderr, "gemm_wq_bf16: tensor map encoding failed; using the plain kernel\n");
         }
         return -2;
     }
 
-#ifdef B200_TRACE
-    p.trace = trace_next(grid);
-#endif
     const size_t smem = (size_t)Cfg::HEADER_BYTES + (size_t)ns * Cfg::STAGE_BYTES + Cfg::RED_BYTES;
     auto kernel = gemv_wq_kernel<Cfg, SCALED>;
-    static bool attr_set[kMaxDevices] = {};    // per instantiation, per device
-    if (!attr_set[ws->device])
+    static std::atomic<bool> attr_set[kMaxDevices];    // per instantiation, per device (zero-initialised)
+    if (!attr_set[ws->device].load(std::memory_order_acquire))
     {
+        // setting the same attribute twice from two threads is harmless; the flag only saves the call
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         {
             report_launch("gemm_wq_bf16");
             return 1;
         }
-        attr_set[ws->device] = true;
+        attr_set[ws->device].store(true, std::memory_order_release);
     }
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));

@@ -11,6 +11,7 @@
 #include "gemv_launch.cuh"
 #include "../../include/cccc_cuda_b200.h"
 
+#include <atomic>
 #include <mutex>
 
 namespace
@@ -31,7 +32,7 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 
 struct StaticState
 {
-    bool ready = false;
+    std::atomic<bool> ready{ false };    // set last (release) once base and scratch are complete
     unsigned char* base = nullptr;
     GemvScratch scratch;
 };
@@ -45,9 +46,9 @@ StaticState* static_state()
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { return nullptr; }
     StaticState& st = g_static[dev];
-    if (st.ready) { return &st; }
+    if (st.ready.load(std::memory_order_acquire)) { return &st; }
     std::lock_guard<std::mutex> lock(g_static_mutex);
-    if (st.ready) { return &st; }
+    if (st.ready.load(std::memory_order_relaxed)) { return &st; }
     void* ptr = nullptr;
     const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
     if (e != cudaSuccess || ptr == nullptr)
@@ -69,7 +70,7 @@ StaticState* static_state()
         fprintf(stderr, "gemm_wq_bf16_static kernel launch failed: cannot read the device attributes\n");
         return nullptr;
     }
-    st.ready = true;
+    st.ready.store(true, std::memory_order_release);
     return &st;
 }
 
@@ -97,8 +98,10 @@ C_EXPORT int cuda_gemm_wq_bf16_static(int w_type, const void* W, const void* blk
     }
     cudaStream_t s = (cudaStream_t)stream;
     // The array keeps whatever the last call left in it.  Partial tiles are always written before
-    // they are read; the arrival counters must start at zero, so they are cleared on the stream.
-    if (cudaMemsetAsync(st->scratch.counters, 0, kStaticMaxCtas * sizeof(unsigned int), s) != cudaSuccess)
+    // they are read; the arrival counters must start at zero and the status word must describe this
+    // call only, so both are cleared on the stream (status word at 0, counters at 256).  A failure of
+    // an earlier unchecked call is therefore dropped here, never reported against a later call.
+    if (cudaMemsetAsync(st->base, 0, 256 + kStaticMaxCtas * sizeof(unsigned int), s) != cudaSuccess)
     {
         report_launch("gemm_wq_bf16_static");
         return 1;
@@ -116,14 +119,17 @@ C_EXPORT int cuda_gemm_wq_bf16_static(int w_type, const void* W, const void* blk
     if (flags & 2u)
     {
         // Checked mode: wait for the stream and look at the status word (a stack variable, no allocation).
-        if (cudaStreamSynchronize(s) != cudaSuccess) { return report_launch("gemm_wq_bf16_static") ? 1 : 1; }
+        if (cudaStreamSynchronize(s) != cudaSuccess)
+        {
+            report_launch("gemm_wq_bf16_static");
+            return 1;
+        }
         unsigned int status = 0;
         if (cudaMemcpy(&status, st->scratch.status, sizeof(status), cudaMemcpyDeviceToHost) != cudaSuccess) { return 1; }
         if (status != 0)
         {
             fprintf(stderr, "gemm_wq_bf16_static kernel launch failed: a bounded wait ran out (status %u)\n", status);
-            cudaMemset(st->base, 0, kStaticHeaderBytes);
-            return 1;
+            return 1;    // the next call clears the header again before it runs
         }
     }
     return 0;

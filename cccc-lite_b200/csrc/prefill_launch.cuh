@@ -9,9 +9,6 @@
 namespace b200
 {
 
-#ifdef B200_TRACE
-static unsigned long long* trace_next(unsigned int grid);
-#endif
 
 // Tile shapes of the prefill path.  One CTA per tile: 128 features x 128 or 256 tokens (two CTAs per
 // SM), or 256 features x 256 tokens (one CTA per SM).  CTA pairs (cta_group::2): 256 x 256, 512
@@ -162,9 +159,6 @@ static int launch_prefill(int w_type, const GemvParams* items, unsigned int coun
         g.w_scale = scaled ? items[j].w_scale : 1.0f;
         g.post_scale = (w_type == DT_FP4 || scaled) ? 1.0f : items[j].w_scale;
     }
-#ifdef B200_TRACE
-    pp.trace = trace_next(1024);    // 2 ranks x 16 roles x 256 k blocks
-#endif
     const void* X = items[0].X;
     const unsigned int ldx = items[0].ldx;
     if (w_type == DT_FP4) { return launch_prefill_t<DT_FP4, false>(X, ldx, pp, device, sm_count, variant, stream); }

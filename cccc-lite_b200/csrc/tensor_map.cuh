@@ -15,20 +15,18 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 static EncodeTiledFn encode_tiled_fn()
 {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried)
-    {
-        tried = true;
+    // initialised once, thread-safe (C++11 static initialisation)
+    static const EncodeTiledFn fn = []() -> EncodeTiledFn {
         void* sym = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess
             && q == cudaDriverEntryPointSuccess)
         {
-            fn = (EncodeTiledFn)sym;
+            return (EncodeTiledFn)sym;
         }
-        else { cudaGetLastError(); }
-    }
+        cudaGetLastError();
+        return nullptr;
+    }();
     return fn;
 }
 

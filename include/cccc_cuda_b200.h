@@ -120,10 +120,14 @@ C_EXPORT int cuda_gemm_wq_bf16_group(int w_type, unsigned int count, const cuda_
  * device's attributes; make that first call outside any stream capture.
  * All calls on a device share the one array: order them on one stream.  Two calls that overlap on the
  * GPU (different streams, or the same buffers from two threads) race on it.  The array keeps the
- * previous call's contents; the counters that must start at zero are cleared on the stream by every call.
- * Arguments and result as cuda_gemm_wq_bf16.  flags bit 0: programmatic dependent launch, as there.
- * flags bit 1: checked call - synchronise the stream after the launch and return 1 if one of the
- * kernel's bounded waits ran out (without it such a failure is not reported by this entry point). */
+ * previous call's contents; the counters that must start at zero, and the status word, are cleared on
+ * the stream by every call (a small memset node ahead of the kernel).
+ * Arguments and result as cuda_gemm_wq_bf16.  flags bit 0: programmatic dependent launch, accepted
+ * for symmetry with cuda_gemm_wq_bf16; because the clearing memset sits between this call's kernel
+ * and the previous kernel of the stream, nothing overlaps here and the bit changes no timing.
+ * flags bit 1: checked call - synchronise the stream after the launch and return 1 if one of THIS
+ * call's bounded waits ran out.  Without it such a failure is not reported at all: the next call
+ * clears the status word before it runs, and cuda_check_error() does not look at this array. */
 C_EXPORT int cuda_gemm_wq_bf16_static(int w_type, const void* W, const void* blk_scales, float inv_scale, const void* X,
     void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx,
     unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta, void* stream, unsigned int flags);

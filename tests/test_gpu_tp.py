@@ -1,6 +1,9 @@
-"""Tensor-parallel linears on 2 GPUs (NCCL): each rank runs its shard through the C-ABI, shards
-are combined with all-gather / all-reduce, and the result must equal the 1-GPU result within the
-stated tolerance (max relative error 1e-2, cosine >= 0.9999).  Needs at least two GPUs."""
+"""Tensor-parallel linears on 2, 4 and 8 GPUs (NCCL for the plumbing): each rank runs its shard through
+the C-ABI, shards are combined with all-gather / all-reduce, and the result must equal the unsharded
+(CPU oracle) result within the stated tolerance (max relative error 1e-2, cosine >= 0.9999).  The
+fused linear + all-reduce must give the bits of the two separate calls, also when calls of different
+shapes follow each other on one exchange area with nothing in between.  Each world size needs that
+many GPUs and is skipped otherwise."""
 import os
 import socket
 import sys
@@ -84,6 +87,36 @@ def _worker(rank, world, port, q):
                 _, ref = O.linear_wq_bf16(wt, W, blk, inv, X, N, M, K)
                 rel, cos = rel_cos(one.float().cpu().numpy().reshape(M, N), ref)
                 results.append(("fused", wt, N, K, M, ok and rel <= 1e-2 and cos >= 0.9999, rel, cos))
+        # calls of different shapes back to back on ONE exchange area, no host synchronisation and no
+        # other collective in between: row-block counts and tile heights change from call to call
+        # (4096 features in 32-row blocks, 256 in 32-row blocks, 20 tokens in 64-row blocks), which
+        # is what the per-area call counter exists for.  Expected bits come from the two-kernel form.
+        wt = O.FP8_E5M2
+        mixed = [(4096, 4096, 1), (256, 4096, 4), (4096, 4096, 1), (1000, 2048, 20), (4096, 4096, 1), (256, 4096, 4),
+                 (512, 4096, 32)]
+        prepared = []
+        for N, K, M in mixed:
+            W, blk, inv, X = O.make_inputs(wt, N, K, M, seed=5 * N + K + M, scaled=True)
+            s = T.make_shard("row", N, K, world, rank, wt)
+            Ws, bs = T.slice_weight(W, blk, s, N, K, wt)
+            Xs = T.slice_activation(X.reshape(M, K), s)
+            dW = torch.from_numpy(Ws).cuda()
+            dX = torch.from_numpy(Xs.view(np.int16)).cuda()
+            part = torch.zeros(M * N, dtype=torch.float32, device="cuda")
+            two = torch.zeros(M * N, dtype=torch.bfloat16, device="cuda")
+            assert capi.gemm_wq_bf16(wt, dW, None, inv, dX, part, N, M, s.K, flags=capi.FLAG_OUT_F32) == 0
+            assert ar(part, two, M * N) == 0 and capi.check_error("two") == 0
+            prepared.append((dW, dX, inv, N, M, s.K, two))
+        for rep in range(3):    # an odd number of calls per pass: every pass starts on the other slot set
+            outs = []
+            for dW, dX, inv, N, M, Ks, two in prepared:
+                one = torch.full((M * N,), float("nan"), dtype=torch.bfloat16, device="cuda")
+                assert fused(wt, dW, None, inv, dX, one, N, M, Ks, flags=capi.FLAG_PDL) == 0
+                outs.append(one)
+            ok = capi.check_error("mixed") == 0
+            for (dW, dX, inv, N, M, Ks, two), one in zip(prepared, outs):
+                results.append(("fused-mixed", rep, N, Ks, M, ok and bool(torch.equal(one.view(torch.int16), two.view(torch.int16))),
+                                0.0, 1.0))
         # a shape the fused kernel does not take is refused, not mangled
         results.append(("fused-refuses", 0, 0, 0, 0, fused(O.FP8_E5M2, dW, dB, inv, dX, one, 64, 40, 64) == -1, 0.0, 1.0))
         q.put((rank, results))
@@ -91,21 +124,22 @@ def _worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_two_gpu_shards_match_unsharded():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_shards_match_unsharded(world):
     import torch
     import torch.multiprocessing as mp
 
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     with socket.socket() as sock:
         sock.bind(("127.0.0.1", 0))
         port = sock.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    out = [q.get(timeout=300) for _ in procs]
+    out = [q.get(timeout=600) for _ in procs]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
