@@ -61,6 +61,20 @@ class WqLinear(C.Structure):
 
 SYMBOLS["cuda_gemm_wq_bf16_group"] = (_i, [_i, _u, C.POINTER(WqLinear), _vp, _u, _u, _u, _vp, _u])
 
+
+
+class AttnDecode(C.Structure):
+    """cuda_attn_decode of include/cccc_cuda_b200.h."""
+    _fields_ = [(n, C.c_void_p) for n in ("q", "k", "v", "q_norm", "k_norm", "cos_tab", "sin_tab", "k_cache", "v_cache", "pos", "out")] + [
+        (n, C.c_uint) for n in ("ldq", "ldk", "ldv", "ldo", "B", "H", "Hkv", "head_dim", "T_max")] + [("epsilon", C.c_float), ("dk", C.c_float)]
+
+
+SYMBOLS["cuda_rms_norm_bf16"] = (_i, [_vp, _vp, _vp, _vp, _vp, _u, _u, _f, _vp, _u])
+SYMBOLS["cuda_rope_bf16"] = (_i, [_vp, _vp, _vp, _vp, _u, _u, _u, _u, _vp, _u])
+SYMBOLS["cuda_embed_bf16"] = (_i, [_vp, _vp, _vp, _u, _u, _u, _vp, _u])
+SYMBOLS["cuda_swiglu_bf16"] = (_i, [_vp, _vp, _vp, _u, _u, _u, _u, _u, _vp, _u])
+SYMBOLS["cuda_attn_decode_bf16"] = (_i, [C.POINTER(AttnDecode), _vp, _u])
+
 _lib = None
 
 
@@ -238,6 +252,50 @@ class FusedRowLinear:
                                                  K if ldw is None else ldw, K if ldx is None else ldx,
                                                  N if ldy_m is None else ldy_m, ldy_n, alpha, self.recv_ptrs, self.flag_ptrs,
                                                  _ptr(self.counters), self.n_max, self.rank, self.world, stream, flags)
+
+
+def _stream(stream):
+    if stream is None:
+        import torch
+
+        return torch.cuda.current_stream().cuda_stream
+    return stream
+
+
+def rms_norm_bf16(X, Y, scale, rows: int, inner: int, eps: float = 1e-6, residual=None, sum_out=None, stream=None, flags: int = 0) -> int:
+    return lib().cuda_rms_norm_bf16(_ptr(X), _ptr(residual), _ptr(sum_out), _ptr(Y), _ptr(scale), rows, inner, eps, _stream(stream), flags)
+
+
+def rope_bf16(X, Y, cos_tab, sin_tab, D: int, T: int, B: int, pos_offset: int, stream=None, flags: int = 0) -> int:
+    return lib().cuda_rope_bf16(_ptr(X), _ptr(Y), _ptr(cos_tab), _ptr(sin_tab), D, T, B, pos_offset, _stream(stream), flags)
+
+
+def embed_bf16(ids, W, Y, D: int, n_tokens: int, vocab: int, stream=None, flags: int = 0) -> int:
+    return lib().cuda_embed_bf16(_ptr(ids), _ptr(W), _ptr(Y), D, n_tokens, vocab, _stream(stream), flags)
+
+
+def swiglu_bf16(gate, up, out, rows: int, cols: int, ld_gate=None, ld_up=None, ld_out=None, stream=None, flags: int = 0) -> int:
+    return lib().cuda_swiglu_bf16(_ptr(gate), _ptr(up), _ptr(out), rows, cols, cols if ld_gate is None else ld_gate,
+                                  cols if ld_up is None else ld_up, cols if ld_out is None else ld_out, _stream(stream), flags)
+
+
+def make_attn_decode(*, q, k, v, k_cache, v_cache, pos, out, cos_tab, sin_tab, B: int, H: int, Hkv: int, head_dim: int, T_max: int,
+                     q_norm=None, k_norm=None, ldq=None, ldk=None, ldv=None, ldo=None, eps: float = 1e-6, dk: float = 0.0):
+    """A cuda_attn_decode filled from tensors (it only holds pointers: keep the tensors alive)."""
+    a = AttnDecode()
+    for name, t in (("q", q), ("k", k), ("v", v), ("q_norm", q_norm), ("k_norm", k_norm), ("cos_tab", cos_tab), ("sin_tab", sin_tab),
+                    ("k_cache", k_cache), ("v_cache", v_cache), ("pos", pos), ("out", out)):
+        setattr(a, name, _ptr(t))
+    a.ldq = H * head_dim if ldq is None else ldq
+    a.ldk = Hkv * head_dim if ldk is None else ldk
+    a.ldv = Hkv * head_dim if ldv is None else ldv
+    a.ldo = H * head_dim if ldo is None else ldo
+    a.B, a.H, a.Hkv, a.head_dim, a.T_max, a.epsilon, a.dk = B, H, Hkv, head_dim, T_max, eps, dk
+    return a
+
+
+def attn_decode_bf16(desc, stream=None, flags: int = 0) -> int:
+    return lib().cuda_attn_decode_bf16(C.byref(desc), _stream(stream), flags)
 
 
 def argmax_bf16(logits, rows: int, cols: int, idx_out, val_out=None, ld: int | None = None, stream: int | None = None) -> int:

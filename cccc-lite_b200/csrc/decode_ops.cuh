@@ -1,0 +1,367 @@
+// Device code of the non-GEMM ops of an LLM decode layer, written so that a CTA-sized team of
+// 256 threads can run them either as a kernel of their own (decode_ops.cu) or as one phase of a
+// longer-running kernel: RMSNorm with the reference's summation order, half-rotate RoPE, the
+// KV-cache append, and attention of one new token per sequence over a BF16 cache.
+//
+// Rounding points are the reference's: every tensor the reference materialises in BF16 (the
+// normalised row, the rotated q and k, the scaled scores, the softmax probabilities, the attention
+// output) is rounded to BF16 here at the same place, although nothing but the final output leaves
+// the chip.
+#pragma once
+
+#include "common.cuh"
+#include "gemv_decode.cuh"
+
+#include <cooperative_groups.h>
+
+namespace b200
+{
+
+constexpr int kTeam = 256;    // threads of a team; team barriers are bar.sync 1, 256
+
+__device__ __forceinline__ void team_sync() { consumer_bar_sync<kTeam>(); }
+
+__device__ __forceinline__ float bf16_round(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+__device__ __forceinline__ uint16_t bf16_bits(float f) { return __bfloat16_as_ushort(__float2bfloat16_rn(f)); }
+
+// Sum of squares of `rows` rows of `inner` floats held in shared memory (xs[row * inner + i]), in
+// the order of the reference's kernel (cccc-cuda/cuda_functions.cu:904-933, 256 threads per row):
+// thread t accumulates x[t], x[t+256], ... with one fused multiply-add each, then the 256 partial
+// sums are combined by a halving tree.  part: rows * 256 floats of shared memory.  On return
+// part[row * 256] holds the sum of row `row`; all 256 threads of the team must call.
+__device__ __forceinline__ void team_sum_squares(const float* xs, float* part, unsigned int rows, unsigned int inner, unsigned int tid)
+{
+    for (unsigned int r = 0; r < rows; r++)
+    {
+        float s = 0.f;
+        for (unsigned int i = tid; i < inner; i += kTeam) { s = __fmaf_rn(xs[r * inner + i], xs[r * inner + i], s); }
+        part[r * kTeam + tid] = s;
+    }
+    team_sync();
+    for (unsigned int s = kTeam / 2; s > 0; s >>= 1)
+    {
+        if (tid < s)
+        {
+            for (unsigned int r = 0; r < rows; r++) { part[r * kTeam + tid] += part[r * kTeam + tid + s]; }
+        }
+        team_sync();
+    }
+}
+
+// invstd of the reference: rsqrtf(sum / inner + eps).
+__device__ __forceinline__ float rms_invstd(float sum, unsigned int inner, float eps) { return rsqrtf(sum / (float)inner + eps); }
+
+// y = bf16((x * invstd) * scale), the reference's expression (two roundings-free float products).
+__device__ __forceinline__ float rms_apply(float x, float invstd, float sc) { return bf16_round(__fmul_rn(__fmul_rn(x, invstd), sc)); }
+
+// Half-rotate RoPE of one pair (cccc-cuda/cuda_functions.cu:1324-1344): one product rounded, the
+// other fused into the add, then BF16.
+__device__ __forceinline__ void rope_pair(float xl, float xr, float c, float s, float& yl, float& yr)
+{
+    yl = bf16_round(__fmaf_rn(xl, c, -__fmul_rn(xr, s)));
+    yr = bf16_round(__fmaf_rn(xr, c, __fmul_rn(xl, s)));
+}
+
+// ---- attention of one new token per sequence ------------------------------------------------------
+struct AttnDecodeParams
+{
+    const uint16_t* q;       // [B][ldq]: H heads of HD
+    const uint16_t* k;       // [B][ldk]: Hkv heads of HD (the new token's key, before norm and RoPE)
+    const uint16_t* v;       // [B][ldv]
+    const uint16_t* q_norm;  // [HD] or nullptr
+    const uint16_t* k_norm;  // [HD] or nullptr
+    const uint16_t* cos_tab; // [rows][HD/2]
+    const uint16_t* sin_tab;
+    uint16_t* k_cache;       // [B][Hkv][T_max][HD]
+    uint16_t* v_cache;
+    const int* pos;          // [B]: where the new token goes = index of the newest valid row afterwards
+    uint16_t* out;           // [B][ldo]: H heads of HD
+    unsigned int ldq, ldk, ldv, ldo;
+    unsigned int B, H, Hkv, T_max;
+    float eps, scale;        // RMSNorm epsilon of the q/k norms; 1/sqrt(dk)
+};
+
+// Shared memory of one attention team (floats): see attn_smem_floats().
+template <int G, int HD>
+struct AttnSmem
+{
+    static constexpr int kSlots2 = kTeam / (HD / 8);    // token slots of the P*V pass
+    float* qs;      // [G][HD]   rotated q, BF16-rounded
+    float* kn;      // [HD]      rotated new k (owner split only)
+    float* xin;     // [G+1][HD] raw q heads and the k head (norm input)
+    float* part;    // [G+1][256] partial sums of the norms
+    float* ml;      // [G][2]    this split's max and sum of exponentials
+    float* gl;      // [G][2]    the sequence's max and 1/sum
+    float* opart;   // [G][HD]   this split's partial output
+    float* red;     // [kSlots2][G][HD]
+    float* sc;      // [G][ts_cap] scores, then probabilities
+    __device__ AttnSmem(float* base, unsigned int ts_cap)
+    {
+        qs = base;
+        kn = qs + G * HD;
+        xin = kn + HD;
+        part = xin + (G + 1) * HD;
+        ml = part + (G + 1) * kTeam;
+        gl = ml + 2 * G;
+        opart = gl + 2 * G;
+        red = opart + G * HD;
+        sc = red + kSlots2 * G * HD;
+        (void)ts_cap;
+    }
+};
+template <int G, int HD>
+__host__ __device__ constexpr size_t attn_smem_floats(unsigned int ts_cap)
+{
+    return (size_t)G * HD + HD + (size_t)(G + 1) * HD + (size_t)(G + 1) * kTeam + 4 * G + (size_t)G * HD
+        + (size_t)(kTeam / (HD / 8)) * G * HD + (size_t)G * ts_cap;
+}
+
+// Prologue of a split: the G query heads of kv head `kvh` of sequence b are normalised (optional)
+// and rotated into sm.qs; the split that owns row `pos` also normalises and rotates the new key,
+// appends it and the new value to the caches (MatrixOp.cpp:237-276) and keeps the key in sm.kn.
+template <int G, int HD>
+__device__ __forceinline__ void attn_prologue(const AttnDecodeParams& p, AttnSmem<G, HD>& sm, unsigned int b, unsigned int kvh,
+    unsigned int pos, bool owner, unsigned int tid)
+{
+    constexpr int HALF = HD / 2;
+    const uint16_t* q = p.q + (size_t)b * p.ldq + (size_t)kvh * G * HD;
+    const uint16_t* k = p.k + (size_t)b * p.ldk + (size_t)kvh * HD;
+    for (unsigned int i = tid; i < (G + 1) * HD; i += kTeam)
+    {
+        sm.xin[i] = bf16_bits_to_float(i < G * HD ? q[i] : k[i - G * HD]);
+    }
+    team_sync();
+    if (p.q_norm != nullptr || p.k_norm != nullptr) { team_sum_squares(sm.xin, sm.part, G + 1, HD, tid); }
+    // normalise in place (BF16-rounded, as the reference's rmsNorm output tensor is)
+    for (unsigned int i = tid; i < (G + 1) * HD; i += kTeam)
+    {
+        const unsigned int r = i / HD, d = i - r * HD;
+        const uint16_t* w = r < G ? p.q_norm : p.k_norm;
+        if (w != nullptr) { sm.xin[i] = rms_apply(sm.xin[i], rms_invstd(sm.part[r * kTeam], HD, p.eps), bf16_bits_to_float(w[d])); }
+    }
+    team_sync();
+    for (unsigned int i = tid; i < (G + 1) * HALF; i += kTeam)
+    {
+        const unsigned int r = i / HALF, d = i - r * HALF;
+        const float c = bf16_bits_to_float(p.cos_tab[(size_t)pos * HALF + d]);
+        const float s = bf16_bits_to_float(p.sin_tab[(size_t)pos * HALF + d]);
+        float yl, yr;
+        rope_pair(sm.xin[r * HD + d], sm.xin[r * HD + HALF + d], c, s, yl, yr);
+        float* dst = r < G ? sm.qs + r * HD : sm.kn;
+        dst[d] = yl;
+        dst[HALF + d] = yr;
+    }
+    team_sync();
+    if (owner && pos < p.T_max)
+    {
+        uint16_t* kc = p.k_cache + (((size_t)b * p.Hkv + kvh) * p.T_max + pos) * HD;
+        uint16_t* vc = p.v_cache + (((size_t)b * p.Hkv + kvh) * p.T_max + pos) * HD;
+        const uint16_t* v = p.v + (size_t)b * p.ldv + (size_t)kvh * HD;
+        for (unsigned int i = tid; i < HD; i += kTeam)
+        {
+            kc[i] = bf16_bits(sm.kn[i]);
+            vc[i] = v[i];
+        }
+    }
+}
+
+__device__ __forceinline__ void unpack8(const uint4 v, float (&f)[8])
+{
+    const uint32_t w[4] = { v.x, v.y, v.z, v.w };
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+    {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+}
+
+// Scores of the rows [t0, t1) of one kv head against the G rotated queries:
+// sm.sc[g][t - t0] = bf16(scale * K[t] . q_g) (the reference's BF16 score tensor,
+// MatrixEx.cpp:3056), and this split's maximum and sum of exp(score - maximum) per head in sm.ml.
+// Eight lanes share a row (two 16-byte pieces each for HD = 128), 32 rows per pass.
+template <int G, int HD>
+__device__ __forceinline__ void attn_scores(const AttnDecodeParams& p, AttnSmem<G, HD>& sm, unsigned int b, unsigned int kvh,
+    unsigned int t0, unsigned int t1, unsigned int ts_cap, unsigned int pos, bool owner, unsigned int tid)
+{
+    constexpr int CPL = HD / 64;    // 16-byte pieces per lane
+    const unsigned int sub = tid & 7u, slot = tid >> 3;
+    float qf[G][CPL][8];
+#pragma unroll
+    for (int g = 0; g < G; g++)
+#pragma unroll
+        for (int c = 0; c < CPL; c++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) { qf[g][c][e] = sm.qs[g * HD + (sub + 8 * c) * 8 + e]; }
+    const uint16_t* Kb = p.k_cache + ((size_t)b * p.Hkv + kvh) * p.T_max * HD;
+    float mx[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) { mx[g] = -INFINITY; }
+    constexpr int UNROLL = 4;
+    for (unsigned int tb = t0; tb < t1; tb += 32 * UNROLL)
+    {
+        uint4 kv[UNROLL][CPL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++)
+        {
+            const unsigned int t = tb + u * 32 + slot;
+#pragma unroll
+            for (int c = 0; c < CPL; c++)
+            {
+                kv[u][c] = (t < t1 && !(owner && t == pos)) ? __ldcg(reinterpret_cast<const uint4*>(Kb + (size_t)t * HD) + sub + 8 * c)
+                                                            : make_uint4(0, 0, 0, 0);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++)
+        {
+            const unsigned int t = tb + u * 32 + slot;
+            float acc[G];
+#pragma unroll
+            for (int g = 0; g < G; g++) { acc[g] = 0.f; }
+#pragma unroll
+            for (int c = 0; c < CPL; c++)
+            {
+                float kf[8];
+                if (owner && t == pos)
+                {
+                    // the row this call appends: taken from shared memory, not re-read from the cache
+#pragma unroll
+                    for (int e = 0; e < 8; e++) { kf[e] = sm.kn[(sub + 8 * c) * 8 + e]; }
+                }
+                else { unpack8(kv[u][c], kf); }
+#pragma unroll
+                for (int g = 0; g < G; g++)
+#pragma unroll
+                    for (int e = 0; e < 8; e++) { acc[g] = __fmaf_rn(kf[e], qf[g][c][e], acc[g]); }
+            }
+#pragma unroll
+            for (int g = 0; g < G; g++)
+            {
+                acc[g] += __shfl_xor_sync(0xFFFFFFFFu, acc[g], 1);
+                acc[g] += __shfl_xor_sync(0xFFFFFFFFu, acc[g], 2);
+                acc[g] += __shfl_xor_sync(0xFFFFFFFFu, acc[g], 4);
+                if (t < t1)
+                {
+                    const float s = bf16_round(__fmul_rn(p.scale, acc[g]));
+                    if (sub == 0) { sm.sc[g * ts_cap + (t - t0)] = s; }
+                    mx[g] = fmaxf(mx[g], s);
+                }
+            }
+        }
+    }
+    // maximum over the team (all lanes of a row group hold the same value), then the sum of exponentials
+#pragma unroll
+    for (int g = 0; g < G; g++)
+    {
+#pragma unroll
+        for (int o = 8; o < 32; o <<= 1) { mx[g] = fmaxf(mx[g], __shfl_xor_sync(0xFFFFFFFFu, mx[g], o)); }
+        if ((tid & 31u) == 0) { sm.red[g * 8 + (tid >> 5)] = mx[g]; }
+    }
+    team_sync();
+    if (tid < G)
+    {
+        float m = sm.red[tid * 8];
+        for (int w = 1; w < 8; w++) { m = fmaxf(m, sm.red[tid * 8 + w]); }
+        sm.ml[2 * tid] = m;
+    }
+    team_sync();
+    float ls[G];
+    const unsigned int n_rows = t1 > t0 ? t1 - t0 : 0;
+#pragma unroll
+    for (int g = 0; g < G; g++)
+    {
+        ls[g] = 0.f;
+        const float m = sm.ml[2 * g];
+        for (unsigned int i = tid; i < n_rows; i += kTeam) { ls[g] += __expf(sm.sc[g * ts_cap + i] - m); }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) { ls[g] += __shfl_xor_sync(0xFFFFFFFFu, ls[g], o); }
+    }
+    team_sync();    // sm.red is reused
+#pragma unroll
+    for (int g = 0; g < G; g++)
+    {
+        if ((tid & 31u) == 0) { sm.red[g * 8 + (tid >> 5)] = ls[g]; }
+    }
+    team_sync();
+    if (tid < G)
+    {
+        float l = 0.f;
+        for (int w = 0; w < 8; w++) { l += sm.red[tid * 8 + w]; }
+        sm.ml[2 * tid + 1] = l;
+    }
+    team_sync();
+}
+
+// Probabilities and P*V for the rows [t0, t1): p = bf16(exp(score - max) / sum) with the
+// sequence-wide max and 1/sum in sm.gl (the reference's BF16 softmax tensor, MatrixEx.cpp:3091),
+// then opart[g][d] = sum_t V[t][d] * p[g][t] in FP32.  HD/8 lanes share a row (16 bytes each).
+template <int G, int HD>
+__device__ __forceinline__ void attn_pv(const AttnDecodeParams& p, AttnSmem<G, HD>& sm, unsigned int b, unsigned int kvh,
+    unsigned int t0, unsigned int t1, unsigned int ts_cap, unsigned int pos_row, unsigned int tid)
+{
+    constexpr int LPR = HD / 8;             // lanes per row
+    constexpr int SLOTS = kTeam / LPR;      // rows per pass
+    const unsigned int n = t1 > t0 ? t1 - t0 : 0;
+#pragma unroll
+    for (int g = 0; g < G; g++)
+    {
+        const float m = sm.gl[2 * g], inv = sm.gl[2 * g + 1];
+        for (unsigned int i = tid; i < n; i += kTeam)
+        {
+            sm.sc[g * ts_cap + i] = bf16_round(__fmul_rn(__expf(sm.sc[g * ts_cap + i] - m), inv));
+        }
+    }
+    team_sync();
+    const unsigned int sub = tid % LPR, slot = tid / LPR;
+    const uint16_t* Vb = p.v_cache + ((size_t)b * p.Hkv + kvh) * p.T_max * HD;
+    float acc[G][8];
+#pragma unroll
+    for (int g = 0; g < G; g++)
+#pragma unroll
+        for (int e = 0; e < 8; e++) { acc[g][e] = 0.f; }
+    constexpr int UNROLL = 4;
+    for (unsigned int tb = t0; tb < t1; tb += SLOTS * UNROLL)
+    {
+        uint4 vv[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++)
+        {
+            const unsigned int t = tb + u * SLOTS + slot;
+            // the row this call appended comes from the projection output, not back from the cache
+            const uint16_t* vrow = t == pos_row ? p.v + (size_t)b * p.ldv + (size_t)kvh * HD : Vb + (size_t)t * HD;
+            vv[u] = t < t1 ? __ldcg(reinterpret_cast<const uint4*>(vrow) + sub) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++)
+        {
+            const unsigned int t = tb + u * SLOTS + slot;
+            if (t < t1)
+            {
+                float vf[8];
+                unpack8(vv[u], vf);
+#pragma unroll
+                for (int g = 0; g < G; g++)
+                {
+                    const float pr = sm.sc[g * ts_cap + (t - t0)];
+#pragma unroll
+                    for (int e = 0; e < 8; e++) { acc[g][e] = __fmaf_rn(vf[e], pr, acc[g][e]); }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < G; g++)
+#pragma unroll
+        for (int e = 0; e < 8; e++) { sm.red[(slot * G + g) * HD + sub * 8 + e] = acc[g][e]; }
+    team_sync();
+    for (unsigned int i = tid; i < G * HD; i += kTeam)
+    {
+        float s = 0.f;
+        for (int sl = 0; sl < SLOTS; sl++) { s += sm.red[sl * G * HD + i]; }
+        sm.opart[i] = s;
+    }
+    team_sync();
+}
+
+}    // namespace b200

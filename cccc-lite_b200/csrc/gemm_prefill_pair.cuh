@@ -487,7 +487,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
                                 {
                                     const long long yi = (long long)m * g.ldy_m + (long long)n * g.ldy_n;
                                     float o = g.alpha * (__uint_as_float(r[j]) * g.post_scale);
-                                    if (p.out_f32)
+                                    if (p.out_f32 == 1u)
                                     {
                                         float* y = reinterpret_cast<float*>(g.Y) + yi;
                                         if (g.beta != 0.f) { o += g.beta * *y; }
@@ -496,7 +496,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (DQW + 2), FH *
                                     else
                                     {
                                         uint16_t* y = g.Y + yi;
-                                        if (g.beta != 0.f) { o += g.beta * bf16_bits_to_float(*y); }
+                                        if (g.beta != 0.f) { o = (p.out_f32 == 2u ? __bfloat162float(__float2bfloat16_rn(o)) : o) + g.beta * bf16_bits_to_float(*y); }
                                         *y = __bfloat16_as_ushort(__float2bfloat16_rn(o));
                                     }
                                 }

@@ -78,7 +78,9 @@ struct GemvParams
     float w_scale;              // multiplier applied to each decoded weight before BF16 rounding
     float alpha, beta;
     float post_scale;           // exact power of two folded out of the weights (applied with alpha)
-    unsigned int out_f32;       // 1: Y holds float32 (partial sums of a row-parallel shard), 0: BF16
+    unsigned int out_f32;       // 0: Y is BF16; 1: Y holds float32 (partial sums of a row-parallel shard); 2: Y is BF16 and
+                                // alpha * product is rounded to BF16 before beta * Y is added (the reference's linear
+                                // followed by its residual add, two BF16 tensors)
     unsigned int n_row_blocks, n_kstages, total_items;
     unsigned int gran;          // items are dealt to CTAs in groups of `gran`: 1 = stream-K, n_kstages = whole row blocks
     unsigned int n_stages;      // ring depth
@@ -652,7 +654,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
             {
                 const long long yi = (long long)m * L.ldy_m + (long long)n * L.ldy_n;
                 float o = L.alpha * (v * L.post_scale);
-                if (p.out_f32)
+                if (p.out_f32 == 1u)
                 {
                     float* y = reinterpret_cast<float*>(L.Y) + yi;
                     if (L.beta != 0.f) { o += L.beta * *y; }
@@ -661,7 +663,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
                 else
                 {
                     uint16_t* y = L.Y + yi;
-                    if (L.beta != 0.f) { o += L.beta * bf16_bits_to_float(*y); }
+                    if (L.beta != 0.f) { o = (p.out_f32 == 2u ? __bfloat162float(__float2bfloat16_rn(o)) : o) + L.beta * bf16_bits_to_float(*y); }
                     *y = __bfloat16_as_ushort(__float2bfloat16_rn(o));
                 }
             }
@@ -724,7 +726,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
                         float acc = __ldcv(mine + idx);    // peers wrote these: never from L1
                         for (int rr = 1; rr < W_; rr++) { acc += __ldcv(mine + (size_t)rr * p.ar.n_max + idx); }
                         const long long yi = (long long)m * L.ldy_m + (long long)n * L.ldy_n;
-                        if (p.out_f32) { reinterpret_cast<float*>(L.Y)[yi] = acc; }
+                        if (p.out_f32 == 1u) { reinterpret_cast<float*>(L.Y)[yi] = acc; }
                         else { L.Y[yi] = __bfloat16_as_ushort(__float2bfloat16_rn(acc)); }
                     }
                 }
@@ -850,7 +852,7 @@ __global__ void __launch_bounds__(256) linear_wq_plain_kernel(const GemvParams p
             {
                 const long long yi = (long long)(m0 + mm) * p.ldy_m + (long long)n * p.ldy_n;
                 float o = p.alpha * v;
-                if (p.out_f32)
+                if (p.out_f32 == 1u)
                 {
                     float* y = reinterpret_cast<float*>(p.Y) + yi;
                     if (p.beta != 0.f) { o += p.beta * *y; }
@@ -859,7 +861,7 @@ __global__ void __launch_bounds__(256) linear_wq_plain_kernel(const GemvParams p
                 else
                 {
                     uint16_t* y = p.Y + yi;
-                    if (p.beta != 0.f) { o += p.beta * bf16_bits_to_float(*y); }
+                    if (p.beta != 0.f) { o = (p.out_f32 == 2u ? __bfloat162float(__float2bfloat16_rn(o)) : o) + p.beta * bf16_bits_to_float(*y); }
                     *y = __bfloat16_as_ushort(__float2bfloat16_rn(o));
                 }
             }

@@ -258,7 +258,7 @@ static int run_linear_wq(const GemvScratch* ws, int w_type, const void* W, const
     p.alpha = alpha;
     p.beta = beta;
     p.post_scale = 1.0f;
-    p.out_f32 = (flags & 4u) ? 1u : 0u;
+    p.out_f32 = (flags & 4u) ? 1u : ((flags & 8u) ? 2u : 0u);
     const bool pdl = (flags & 1u) != 0;
 
     int plan = plan_for(w_type, W, blk_scales, X, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n);
@@ -336,7 +336,7 @@ static int run_linear_wq_group(const GemvScratch* ws, int w_type, unsigned int c
         p.M = M_tokens;
         p.K = K;
         p.ldx = ldx;
-        p.out_f32 = (flags & 4u) ? 1u : 0u;
+        p.out_f32 = (flags & 4u) ? 1u : ((flags & 8u) ? 2u : 0u);
         p.n_seg = count;
         bool all_pow2 = true;
         for (unsigned int j = 0; j < count; j++) { all_pow2 = all_pow2 && is_pow2_scale(items[j].inv_scale); }
@@ -399,7 +399,7 @@ static int run_linear_wq_group(const GemvScratch* ws, int w_type, unsigned int c
             q.w_scale = items[j].inv_scale;
             q.alpha = items[j].alpha;
             q.beta = items[j].beta;
-            q.out_f32 = (flags & 4u) ? 1u : 0u;
+            q.out_f32 = (flags & 4u) ? 1u : ((flags & 8u) ? 2u : 0u);
         }
         const int r = launch_prefill(w_type, ps, count, ws->device, ws->sm_count, (int)((flags >> 8) & 7u), st);
         if (r != -2) { return r; }

@@ -92,7 +92,7 @@ static int launch_prefill_t(const void* X, unsigned int ldx, const PrefillParams
         feature_tiles += (g.N + tile_features - 1) / tile_features;
         // BF16 output with contiguous features and no accumulate: the epilogue writes whole tiles with TMA stores
         g.y_tma = 0;
-        if (!pp.out_f32 && g.beta == 0.f && g.ldy_n == 1 && (g.ldy_m % 8) == 0 && g.ldy_m >= (long long)g.N
+        if (pp.out_f32 != 1u && g.beta == 0.f && g.ldy_n == 1 && (g.ldy_m % 8) == 0 && g.ldy_m >= (long long)g.N
             && (reinterpret_cast<uintptr_t>(g.Y) & 15u) == 0
             && make_map_2d(&tmY.m[j], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, g.Y, g.N, pp.M, (unsigned long long)g.ldy_m * 2, PF_BM, y_box_rows,
                 false))

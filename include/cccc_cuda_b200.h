@@ -77,7 +77,10 @@ C_EXPORT void cuda_clear_last_error(void);
  * overlaps the tail of the previous kernel on the stream (X, Y are only touched after that
  * kernel has finished).  bit 2 = Y holds float32 instead of BF16 (same strides, in elements): the
  * unrounded result, which is what a row-parallel (K-split) shard hands to the all-reduce so that
- * the sum over shards is rounded to BF16 once.  bits 8-10 = tile shape of the M_tokens > 32 path,
+ * the sum over shards is rounded to BF16 once.  bit 3 = round alpha * product to BF16 before beta * Y
+ * is added: Y = bf16( bf16(alpha * W x) + beta * Y ), which with beta = 1 is the reference's linear
+ * followed by its residual add (two BF16 tensors, scripts/convert_weights.py:562, :582).
+ * bits 8-10 = tile shape of the M_tokens > 32 path,
  * for tests and tuning (0 = chosen by shape; 1-3 = one CTA per tile: 128 features x 128 tokens,
  * 128 x 256, 256 x 256; 4-6 = CTA pairs: 256 x 256, 512 features x 256 tokens, 256 x 512): every
  * value gives the same result bit for bit. */
@@ -185,6 +188,74 @@ C_EXPORT unsigned long long cuda_b200_fused_counter_bytes(void);
  * Asynchronous on `stream`. */
 C_EXPORT int cuda_argmax_bf16(const void* logits, unsigned int rows, unsigned int cols, unsigned long long ld,
     void* idx_out, void* val_out, void* stream);
+
+/* ---- additions: the ops between the linears of a decode layer -------------------------------- */
+
+/* Replaces cuda_rms_norm_fwd for BF16 rows (cccc-cuda/cuda_functions.h:55, kernel
+ * cuda_functions.cu:904-933): Y[r][i] = bf16( (x[r][i] * invstd_r) * scale[i] ), invstd_r =
+ * rsqrt(mean_i x[r][i]^2 + epsilon), the squares summed in the reference kernel's order.  scale may
+ * be NULL (1.0).  With residual != NULL the add that precedes the norm in a layer (R1 = X + O_out,
+ * scripts/convert_weights.py:567-572) is folded in: x = bf16(X + residual), stored to sum_out when
+ * that is not NULL (sum_out may alias X or residual).  Rows are contiguous (`inner` elements apart).
+ * Asynchronous on `stream`; flags bit 0 = programmatic dependent launch. */
+C_EXPORT int cuda_rms_norm_bf16(const void* X, const void* residual, void* sum_out, void* Y, const void* scale,
+    unsigned int rows, unsigned int inner, float epsilon, void* stream, unsigned int flags);
+
+/* Replaces cuda_rope_fwd for BF16 (cuda_functions.h:73, kernel cuda_functions.cu:1324-1344): half-rotate
+ * RoPE of X (D, T, 1, B) = [B][T][D] with table row t + pos_offset; tables are [rows][D/2] BF16
+ * (cccc/NetCifa.cpp:431-475). */
+C_EXPORT int cuda_rope_bf16(const void* X, void* Y, const void* cos_tab, const void* sin_tab, unsigned int D, unsigned int T,
+    unsigned int B, unsigned int pos_offset, void* stream, unsigned int flags);
+
+/* Replaces cuda_embed_fwd for BF16 tables (cuda_functions.h:97, kernel cuda_functions.cu:1574-1594):
+ * Y[t][:] = W[ids[t]][:].  ids are int32 on the device (the reference passes floats and casts; here
+ * the token comes straight from cuda_argmax_bf16).  An id outside [0, vocab) gives a zero row. */
+C_EXPORT int cuda_embed_bf16(const void* ids, const void* W, void* Y, unsigned int D, unsigned int n_tokens, unsigned int vocab,
+    void* stream, unsigned int flags);
+
+/* The gated MLP's activation in one pass: out = bf16( bf16( g * bf16(sigmoid(g)) ) * u ), which is the
+ * reference's silu (a BF16 sigmoid tensor times its input, cccc/MatrixEx.cpp:744-763) followed by
+ * elementMul (cccc/Matrix.cpp:1360-1386), with their three BF16 tensors' roundings.  Row strides in
+ * elements. */
+C_EXPORT int cuda_swiglu_bf16(const void* gate, const void* up, void* out, unsigned int rows, unsigned int cols,
+    unsigned int ld_gate, unsigned int ld_up, unsigned int ld_out, void* stream, unsigned int flags);
+
+/* Attention of ONE new token per sequence over a BF16 KV cache, with everything the reference runs
+ * between the q/k/v projections and the o projection folded into one launch
+ * (scripts/convert_weights.py:488-560): the per-head RMSNorm of q and k (Qwen3; NULL weights = none),
+ * RoPE at the token's position, the cache append (cccc/MatrixOp.cpp:237-276), and
+ * cccc/MatrixEx.cpp:3018-3104 with T_q = 1: scores = bf16(K q / sqrt(dk)), softmax probabilities
+ * rounded to BF16, out = bf16(V p).  No tiled or permuted copies of the cache and no score matrix in
+ * memory (the reference makes both, convert_weights.py:551-560, MatrixEx.cpp:3040-3050): each
+ * (sequence, kv head) is cut into up to 16 splits that run as one thread-block cluster and combine
+ * through distributed shared memory.  Query head h reads kv head h / (H / Hkv).
+ *   q, k, v  : the projections' outputs, [B] rows of H*head_dim, Hkv*head_dim, Hkv*head_dim BF16
+ *              values, row strides ldq/ldk/ldv in elements (they may be slices of one buffer)
+ *   caches   : [B][Hkv][T_max][head_dim] BF16
+ *   pos      : DEVICE int32 [B]: the row the new token is appended at (= tokens already cached);
+ *              rows 0..pos are attended.  pos >= T_max appends nothing and attends T_max rows.
+ *   tables   : RoPE cos / sin, [>= max pos + 1][head_dim / 2] BF16
+ *   out      : [B] rows of H*head_dim BF16, stride ldo
+ * head_dim 64 or 128; H / Hkv in {1, 2, 4, 8}; v and the caches 16-byte aligned, ldv % 8 == 0;
+ * anything else returns -1.  dk <= 0 means head_dim. */
+typedef struct cuda_attn_decode
+{
+    const void* q;
+    const void* k;
+    const void* v;
+    const void* q_norm;
+    const void* k_norm;
+    const void* cos_tab;
+    const void* sin_tab;
+    void* k_cache;
+    void* v_cache;
+    const void* pos;
+    void* out;
+    unsigned int ldq, ldk, ldv, ldo;
+    unsigned int B, H, Hkv, head_dim, T_max;
+    float epsilon, dk;
+} cuda_attn_decode;
+C_EXPORT int cuda_attn_decode_bf16(const cuda_attn_decode* a, void* stream, unsigned int flags);
 
 /* Tuning/diagnostic: returns which kernel cuda_gemm_wq_bf16 would pick for a shape
  * (0 = plain kernel, 1 = decode GEMV (M<=32), 2 = prefill tcgen05 GEMM) without launching. */

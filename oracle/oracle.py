@@ -22,8 +22,8 @@ FLOAT, DOUBLE, HALF, BFLOAT16, FP8_E4M3, FP8_E5M2, FP4_E2M1 = range(7)
 
 def build(force: bool = False) -> str:
     """Compile the C oracle (and, if the reference tree is mounted, oracle/_ref)."""
-    src = os.path.join(_HERE, "cccc_oracle.c")
-    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
+    srcs = [os.path.join(_HERE, "cccc_oracle.c"), os.path.join(_HERE, "decode_ops_oracle.c")]
+    if force or not os.path.exists(_LIB_PATH) or any(os.path.getmtime(_LIB_PATH) < os.path.getmtime(s) for s in srcs):
         subprocess.check_call(["make", "-s", "-C", _HERE, "oracle"])
     return _LIB_PATH
 
@@ -64,6 +64,16 @@ def lib() -> C.CDLL:
         L.oracle_cpu_path_dequant_sgemm.argtypes = [C.c_int, u8p, u8p, C.c_float, f32p, f32p, f32p] + [
             C.c_size_t] * 3 + [C.POINTER(C.c_double)] * 2
         L.oracle_num_threads.restype = C.c_int
+        i32p = C.POINTER(C.c_int32)
+        L.oracle_rms_norm_bf16.argtypes = [u16p, u16p, u16p, f32p, C.c_size_t, C.c_size_t, C.c_float]
+        L.oracle_rope_bf16.argtypes = [u16p, u16p, u16p, u16p] + [C.c_size_t] * 4
+        L.oracle_rope_tables_bf16.argtypes = [C.c_size_t, C.c_size_t, C.c_float, u16p, u16p]
+        L.oracle_embed_bf16.argtypes = [i32p, u16p, u16p, C.c_size_t, C.c_size_t]
+        L.oracle_silu_bf16.argtypes = [u16p, u16p, C.c_size_t]
+        L.oracle_mul_bf16.argtypes = [u16p, u16p, u16p, C.c_size_t]
+        L.oracle_add_bf16.argtypes = [u16p, u16p, u16p, C.c_size_t]
+        L.oracle_kv_append_bf16.argtypes = [u16p, u16p] + [C.c_size_t] * 4
+        L.oracle_attention_decode_bf16.argtypes = [u16p, u16p, u16p, u16p, f32p] + [C.c_size_t] * 5 + [i32p, C.c_float]
         _lib = L
     return _lib
 
@@ -218,3 +228,88 @@ def make_inputs(w_type: int, N: int, K: int, M: int, seed: int = 0, scaled: bool
             inv_scale = float(np.float32(absmax) / np.float32(maxval))
         Wq = float_to_fp8(w, w_type, fwd).reshape(-1)
     return Wq, blk, inv_scale, X
+
+
+# ---- the non-GEMM ops of the decode step (oracle/decode_ops_oracle.c) -----------------------------
+
+def _u16(a):
+    return np.ascontiguousarray(a, np.uint16)
+
+
+def rms_norm_bf16(X: np.ndarray, scale: np.ndarray | None, eps: float = 1e-6) -> np.ndarray:
+    """X: [outer, inner] BF16 bits; returns BF16 bits of the same shape."""
+    X = _u16(X)
+    outer, inner = int(np.prod(X.shape[:-1])), X.shape[-1]
+    Y = np.empty_like(X)
+    sc = None if scale is None else _u16(scale).reshape(-1)
+    lib().oracle_rms_norm_bf16(_p(X.reshape(-1), C.c_uint16), _p(Y.reshape(-1), C.c_uint16), _p(sc, C.c_uint16), None, outer,
+                               inner, eps)
+    return Y
+
+
+def rope_tables_bf16(T: int, d_head: int, base: float):
+    cos = np.empty((T, d_head // 2), np.uint16)
+    sin = np.empty((T, d_head // 2), np.uint16)
+    lib().oracle_rope_tables_bf16(T, d_head, base, _p(cos.reshape(-1), C.c_uint16), _p(sin.reshape(-1), C.c_uint16))
+    return cos, sin
+
+
+def rope_bf16(X: np.ndarray, cos: np.ndarray, sin: np.ndarray, pos_offset: int) -> np.ndarray:
+    """X: [B, T, D] BF16 bits (B independent slices, T consecutive positions starting at pos_offset)."""
+    X = _u16(X)
+    B, T, D = X.shape
+    Y = np.empty_like(X)
+    lib().oracle_rope_bf16(_p(X.reshape(-1), C.c_uint16), _p(Y.reshape(-1), C.c_uint16), _p(_u16(cos).reshape(-1), C.c_uint16),
+                           _p(_u16(sin).reshape(-1), C.c_uint16), D, T, B, pos_offset)
+    return Y
+
+
+def embed_bf16(ids: np.ndarray, W: np.ndarray) -> np.ndarray:
+    ids = np.ascontiguousarray(ids, np.int32).reshape(-1)
+    W = _u16(W)
+    Y = np.empty((ids.size, W.shape[1]), np.uint16)
+    lib().oracle_embed_bf16(ids.ctypes.data_as(C.POINTER(C.c_int32)), _p(W.reshape(-1), C.c_uint16), _p(Y.reshape(-1), C.c_uint16),
+                            W.shape[1], ids.size)
+    return Y
+
+
+def silu_bf16(X: np.ndarray) -> np.ndarray:
+    X = _u16(X)
+    Y = np.empty_like(X)
+    lib().oracle_silu_bf16(_p(X.reshape(-1), C.c_uint16), _p(Y.reshape(-1), C.c_uint16), X.size)
+    return Y
+
+
+def mul_bf16(A: np.ndarray, B: np.ndarray) -> np.ndarray:
+    A, B = _u16(A), _u16(B)
+    Y = np.empty_like(A)
+    lib().oracle_mul_bf16(_p(A.reshape(-1), C.c_uint16), _p(B.reshape(-1), C.c_uint16), _p(Y.reshape(-1), C.c_uint16), A.size)
+    return Y
+
+
+def add_bf16(A: np.ndarray, B: np.ndarray) -> np.ndarray:
+    A, B = _u16(A), _u16(B)
+    Y = np.empty_like(A)
+    lib().oracle_add_bf16(_p(A.reshape(-1), C.c_uint16), _p(B.reshape(-1), C.c_uint16), _p(Y.reshape(-1), C.c_uint16), A.size)
+    return Y
+
+
+def kv_append_bf16(x_new: np.ndarray, cache: np.ndarray, pos: int) -> None:
+    """x_new: [n_heads, D]; cache: [n_heads, T_max, D], updated in place."""
+    n_heads, T_max, D = cache.shape
+    assert cache.dtype == np.uint16 and cache.flags["C_CONTIGUOUS"]
+    lib().oracle_kv_append_bf16(_p(_u16(x_new).reshape(-1), C.c_uint16), _p(cache.reshape(-1), C.c_uint16), D, T_max, n_heads, pos)
+
+
+def attention_decode_bf16(Q: np.ndarray, Kc: np.ndarray, Vc: np.ndarray, pos: np.ndarray, dk: float | None = None):
+    """Q: [B, H, D]; caches: [B, Hkv, T_max, D]; pos: [B] newest valid row.  Returns (Y bits [B, H, D], y32)."""
+    Q, Kc, Vc = _u16(Q), _u16(Kc), _u16(Vc)
+    B, H, D = Q.shape
+    _, Hkv, T_max, _ = Kc.shape
+    pos = np.ascontiguousarray(pos, np.int32).reshape(-1)
+    Y = np.empty_like(Q)
+    y32 = np.empty(Q.shape, np.float32)
+    lib().oracle_attention_decode_bf16(_p(Q.reshape(-1), C.c_uint16), _p(Kc.reshape(-1), C.c_uint16), _p(Vc.reshape(-1), C.c_uint16),
+                                       _p(Y.reshape(-1), C.c_uint16), _p(y32.reshape(-1), C.c_float), B, H, Hkv, D, T_max,
+                                       pos.ctypes.data_as(C.POINTER(C.c_int32)), float(D if dk is None else dk))
+    return Y, y32

@@ -216,3 +216,35 @@ def test_float32_output_flag(wt, N, K, M):
     _, y32 = O.linear_wq_bf16(wt, W, blk, inv, X, N, M, K)
     got = (y.cpu().numpy() - 14.0) * 2.0
     assert np.allclose(got, y32, rtol=2e-4, atol=2e-4 * float(np.sqrt(np.mean(y32.astype(np.float64) ** 2))))
+
+
+@pytest.mark.parametrize("wt", WTS)
+@pytest.mark.parametrize("N,K,M", [(512, 1024, 1), (4096, 4096, 8), (300, 512, 20), (256, 512, 100), (200, 250 + 6, 3)])
+def test_residual_epilogue_rounds_the_product_first(wt, N, K, M):
+    """flags bit 3: Y = bf16( bf16(alpha * W x) + beta * Y ) - the reference's linear followed by its residual
+    add, two BF16 tensors (scripts/convert_weights.py:562, :582) - in every kernel (decode, prefill, plain)."""
+    import torch
+
+    c = capi()
+    if wt == O.FP4_E2M1 and K % 16:
+        pytest.skip("FP4 block scales need K % 16 == 0")
+    W, blk, inv, X = O.make_inputs(wt, N, K, M, seed=N + M, scaled=True, w_std=1.0 / np.sqrt(K))
+    rng = np.random.default_rng(M)
+    Y0 = O.f32_to_bf16_bits(rng.standard_normal((M, N)).astype(np.float32))
+    dY = to_dev(Y0.copy())
+    dW, dX = to_dev(W), to_dev(X)
+    dB = to_dev(blk) if blk is not None else None
+    assert c.gemm_wq_bf16(wt, dW, dB, inv, dX, dY, N, M, K, beta=1.0, flags=8) == 0 and c.check_error("res") == 0
+    lin_bits, y32 = O.linear_wq_bf16(wt, W, blk, inv, X, N, M, K)
+    want = O.add_bf16(lin_bits.reshape(M, N), Y0)
+    got = from_dev_u16(dY).reshape(M, N)
+    # the product differs from the oracle's only by FP32 summation order: where that does not move its BF16
+    # rounding the sum is bit-equal; elsewhere it is one BF16 step of the product away
+    gf, wf = O.bf16_bits_to_f32(got), O.bf16_bits_to_f32(want)
+    step = np.abs(O.bf16_bits_to_f32(lin_bits.reshape(M, N))) * 2.0 ** -7 + 1e-30
+    assert np.all(np.abs(gf - wf) <= step + np.abs(wf) * 2.0 ** -7)
+    assert (got != want).mean() < 5e-3
+    # and it is NOT the single-rounding form: bf16(acc + y0) differs in a visible share of the elements
+    single = O.f32_to_bf16_bits(y32 + O.bf16_bits_to_f32(Y0))
+    if N * M >= 4096:
+        assert (single != want).mean() > 1e-3

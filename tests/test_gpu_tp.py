@@ -117,6 +117,57 @@ def _worker(rank, world, port, q):
             for (dW, dX, inv, N, M, Ks, two), one in zip(prepared, outs):
                 results.append(("fused-mixed", rep, N, Ks, M, ok and bool(torch.equal(one.view(torch.int16), two.view(torch.int16))),
                                 0.0, 1.0))
+        # ---- the whole decode step, tensor parallel, against the unsharded oracle chain ----
+        dm = importlib.import_module("cccc_lite_b200.decode_model")
+        from tests.test_gpu_decode_model import make_model, oracle_step
+
+        cfg = dm.ModelConfig(hidden=1024, n_heads=16, n_kv_heads=8, head_dim=128, ffn=2048, vocab=4096, layers=2, rope_theta=1e4)
+        Tctx, Mb = 32, 2
+        for wt in (O.FP8_E5M2, O.FP4_E2M1):
+            w = make_model(wt, cfg, seed=11 + wt)
+            cos, sin = O.rope_tables_bf16(Tctx, cfg.head_dim, cfg.rope_theta)
+
+            def shard_lin(L3, kind, N, K):
+                W, blk, inv = L3
+                s = T.make_shard(kind, N, K, world, rank, wt)
+                Ws, bs = T.slice_weight(W, blk, s, N, K, wt)
+                return torch.from_numpy(Ws).cuda(), (torch.from_numpy(bs).cuda() if bs is not None else None), inv
+
+            def dev16(a):
+                return torch.from_numpy(a.view(np.int16)).cuda()
+
+            dw = dict(emb=dev16(w["emb"]), final_norm=dev16(w["final_norm"]), lm_head=shard_lin(w["lm_head"], "col", cfg.vocab, cfg.hidden),
+                      layers=[])
+            for L in w["layers"]:
+                d = dict(q=shard_lin(L["q"], "col", cfg.q_dim, cfg.hidden), k=shard_lin(L["k"], "col", cfg.kv_dim, cfg.hidden),
+                         v=shard_lin(L["v"], "col", cfg.kv_dim, cfg.hidden), o=shard_lin(L["o"], "row", cfg.hidden, cfg.q_dim),
+                         gate=shard_lin(L["gate"], "col", cfg.ffn, cfg.hidden), up=shard_lin(L["up"], "col", cfg.ffn, cfg.hidden),
+                         down=shard_lin(L["down"], "row", cfg.hidden, cfg.ffn))
+                d.update({k: dev16(L[k]) for k in ("attn_norm", "ffn_norm", "q_norm", "k_norm")})
+                dw["layers"].append(d)
+            model = dm.DecodeModel(capi, torch, cfg, wt, dw, dev16(cos), dev16(sin), Mb, Tctx, torch.device("cuda", rank), world=world,
+                                   rank=rank, fused_row_linear=fused, dist=dist)
+            Kc = [np.zeros((Mb, cfg.n_kv_heads, Tctx, cfg.head_dim), np.uint16) for _ in range(cfg.layers)]
+            Vc = [np.zeros((Mb, cfg.n_kv_heads, Tctx, cfg.head_dim), np.uint16) for _ in range(cfg.layers)]
+            pos = np.zeros(Mb, np.int32)
+            ids = np.array([3, 1000], np.int32)
+            for step in range(3):
+                want = oracle_step(wt, cfg, w, ids, pos, Kc, Vc, cos, sin)
+                model.ids.copy_(torch.from_numpy(ids))
+                model.pos.copy_(torch.from_numpy(pos))
+                model.step(Mb)
+                ok = capi.check_error("tp step") == 0
+                parts = [torch.empty_like(model.logits) for _ in range(world)]
+                dist.all_gather(parts, model.logits)
+                got = torch.cat(parts, dim=1)[:Mb].float().cpu().numpy()
+                rms = np.sqrt(np.mean(want.astype(np.float64) ** 2, axis=1, keepdims=True))
+                rel = float(np.max(np.abs(got - want) / np.maximum(np.abs(want), rms)))
+                _, cos_sim = rel_cos(got, want)
+                best = model.ids[:Mb].cpu().numpy()
+                same_choice = all(best[b] == int(np.argmax(got[b])) for b in range(Mb))
+                results.append(("tp-decode-step", wt, step, 0, Mb, ok and rel <= 1e-2 and cos_sim >= 0.9999 and same_choice, rel, cos_sim))
+                ids = np.argmax(want, axis=1).astype(np.int32)
+                pos = pos + 1
         # a shape the fused kernel does not take is refused, not mangled
         results.append(("fused-refuses", 0, 0, 0, 0, fused(O.FP8_E5M2, dW, dB, inv, dX, one, 64, 40, 64) == -1, 0.0, 1.0))
         q.put((rank, results))
