@@ -279,6 +279,20 @@ def run_step(torch, dist, capi, wt, calls, bufs, M, world, flags):
     return n_launch
 
 
+def build_chain_program(capi, wt, calls, M):
+    """The same chain recorded as a decode program: one persistent kernel per token
+    (cuda_decode_program_*).  Raises ValueError where the program kernel does not take the chain."""
+    prog = capi.DecodeProgram(wt, M)
+    for c in calls:
+        if prog.add_linears(c["group"], c["K"], c["src"], mode=capi.X_COPY) != 0:
+            prog.close()
+            raise ValueError(f"decode program does not take linear {c['name']}")
+    if prog.finalize() != 0:
+        prog.close()
+        raise ValueError("decode program: finalize failed")
+    return prog
+
+
 def start_watchdog(seconds: float):
     """A benchmark must never occupy a GPU indefinitely: if the process is still alive after `seconds`,
     say so on stdout and leave."""
@@ -366,17 +380,28 @@ def decode_step_model(torch, capi, dm, dims, wt, lin, world, rank, M_max, dev, b
     return model
 
 
-def time_decode_step(torch, dist, capi, model, dims, M, wtype, flags, reps, dev, stream, world):
+def time_decode_step(torch, dist, capi, model, dims, M, wtype, flags, reps, dev, stream, world, program=False):
     """Batch-M decode steps with every sequence's cache full (the new token goes to row CONTEXT-1 and
-    attention reads CONTEXT rows): CUDA-graph replay, CUDA events, max over ranks."""
+    attention reads CONTEXT rows): CUDA-graph replay (or, program=True, the recorded decode program: embedding,
+    one persistent kernel, arg-max), CUDA events, max over ranks."""
     with torch.cuda.stream(stream):
         model.pos.fill_(CONTEXT - 1)
         model.ids.copy_(torch.arange(model.B, dtype=torch.int32, device=dev) % 1000)
-        n = model.step(M, flags)
-        stream.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
-            model.step(M, flags)
+        if program:
+            model.build_program(M)
+            n = model.step_program(M)
+            stream.synchronize()
+
+            class Direct:
+                def replay(self):
+                    model.step_program(M)
+            g = Direct()
+        else:
+            n = model.step(M, flags)
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
+                model.step(M, flags)
         for _ in range(3):
             g.replay()
         stream.synchronize()
@@ -472,20 +497,32 @@ def gpu_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    prog = None
+    if world == 1 and M <= 2 and not args.no_program:
+        try:
+            prog = build_chain_program(capi, wt, calls, M)
+        except ValueError as e:
+            print(f"decode program not used: {e}", file=sys.stderr, flush=True)
+
     with torch.cuda.stream(stream):
         bufs["x"].copy_(x_host, non_blocking=True)
         launches_per_step = run_step(torch, dist, capi, wt, calls, bufs, M, world, flags)  # first call: workspace
         stream.synchronize()
         assert capi.check_error("bench warmup") == 0
         graph = None
-        if not args.no_graph:
+        if prog is not None:
+            launches_per_step = 1
+        elif not args.no_graph:
             graph = torch.cuda.CUDAGraph()
             bufs["x"].copy_(x_host, non_blocking=True)
             with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
                 run_step(torch, dist, capi, wt, calls, bufs, M, world, flags)
 
         def one_step():
-            if graph is not None:
+            if prog is not None:
+                if prog.launch(stream.cuda_stream) != 0:
+                    raise RuntimeError("decode program launch failed")
+            elif graph is not None:
                 graph.replay()
             else:
                 run_step(torch, dist, capi, wt, calls, bufs, M, world, flags)
@@ -566,7 +603,8 @@ def gpu_arm(args):
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16 x fp8_e5m2 -> f32 acc" if args.wtype != "fp4"
         else "bf16 x fp4_e2m1(block16,e4m3 scales) -> f32 acc", "data": "synthetic",
         "config": workload_config(args, dims, world),
-        "run": {"cuda_graph": graph is not None, "pdl": bool(args.pdl), "grouped_qkv_gateup": bool(args.group), "allreduce": allreduce,
+        "run": {"path": "decode program: the 145 grouped linears of a token as ONE persistent kernel (cuda_decode_program_*)" if prog is not None
+                else "one launch per grouped linear (cuda_gemm_wq_bf16 / _group)", "cuda_graph": graph is not None, "pdl": bool(args.pdl), "grouped_qkv_gateup": bool(args.group), "allreduce": allreduce,
                 "exchange_check": exchange_check if world > 1 else None, "timed_region_s": round(ms / 1e3, 3),
                 "linears_tok_per_s": round(M / (ms_per_step * 1e-3), 1)},
         "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": x_host.numel() * 2,
@@ -577,7 +615,7 @@ def gpu_arm(args):
                      "traffic_source": "ncu dram__bytes_read+write of one layer's launches over their algorithmic bytes "
                                        f"(traffic_ratio {ratio} in profiles/gemv_wq_kernel_qwen3_decode_m1.md), scaled to this step's bytes per launch",
                      "algorithmic_bytes_per_launch": int(round(alg_per_launch)), "peak_source": peak_src,
-                     "kernel": "gemv_wq_kernel", "launches_per_step": launches_per_step,
+                     "kernel": "decode_program_kernel" if prog is not None else "gemv_wq_kernel", "launches_per_step": launches_per_step,
                      "avg_launch_us": round(ms_per_step * 1e3 / launches_per_step, 3)},
         "clocks": clocks,
     }
@@ -592,18 +630,27 @@ def gpu_arm(args):
             for mb in (1, 32):
                 steps[f"batch{mb}"] = time_decode_step(torch, dist, capi, model, dims, mb, args.wtype, flags, 30 if mb == 1 else 8, dev, stream,
                                                        world)
+            if world == 1 and not args.no_program:
+                for mb in (1, 2):
+                    try:
+                        steps[f"batch{mb}_program"] = time_decode_step(torch, dist, capi, model, dims, mb, args.wtype, flags, 30, dev, stream, world,
+                                                                       program=True)
+                    except ValueError as e:
+                        steps[f"batch{mb}_program"] = {"unavailable": str(e)}
             assert capi.check_error("decode step") == 0
             steps["note"] = ("36-layer Qwen3-8B-shaped decode step: embedding, RMSNorm, q/k norm + RoPE + cache append + attention over "
                              f"{CONTEXT} BF16 rows, o + residual, RMSNorm, gate/up, SwiGLU, down + residual, final norm, lm_head, arg-max; "
                              "bytes = linears + K and V rows read")
             out["decode_step"] = steps
-            out["gpu_launches"] += sum(v["launches_per_step"] for k, v in steps.items() if k.startswith("batch"))
+            out["gpu_launches"] += sum(v.get("launches_per_step", 0) for k, v in steps.items() if k.startswith("batch"))
             del model
         except Exception as e:
             out["decode_step"] = {"error": f"{type(e).__name__}: {e}"}
     if rank == 0 and world == 1:
         graph = None
         if not args.no_extras and args.wtype != "fp4" and M == 1:
+            if prog is not None:
+                out["run"]["by_launches"] = time_chain(torch, capi, wt, lin, dims, 1, args.wtype, flags, 40, dev, stream)
             out["decode_by_m"] = [time_chain(torch, capi, wt, lin, dims, m, args.wtype, flags, 40, dev, stream) for m in (4, 16, 32)]
             try:
                 out["ref_gpu"] = ref_gpu_probe(torch, capi, dims, dev)
@@ -919,6 +966,7 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip decode_by_m, fp4 and ref_gpu")
     ap.add_argument("--no-decode-step", action="store_true")
+    ap.add_argument("--no-program", action="store_true", help="issue the chain launch by launch even where the decode program takes it")
     ap.add_argument("--watchdog", type=float, default=540.0, help="seconds after which a stuck run exits by itself")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

@@ -75,6 +75,23 @@ SYMBOLS["cuda_embed_bf16"] = (_i, [_vp, _vp, _vp, _u, _u, _u, _vp, _u])
 SYMBOLS["cuda_swiglu_bf16"] = (_i, [_vp, _vp, _vp, _u, _u, _u, _u, _u, _vp, _u])
 SYMBOLS["cuda_attn_decode_bf16"] = (_i, [C.POINTER(AttnDecode), _vp, _u])
 
+
+
+class DecodeInput(C.Structure):
+    """cuda_decode_input of include/cccc_cuda_b200.h."""
+    _fields_ = [("mode", C.c_int), ("x", C.c_void_p), ("ldx", C.c_uint), ("x2", C.c_void_p), ("ldx2", C.c_uint),
+                ("norm_weight", C.c_void_p), ("epsilon", C.c_float)]
+
+
+X_COPY, X_RMSNORM, X_SWIGLU = 0, 1, 2
+SYMBOLS["cuda_decode_program_create"] = (_i, [C.POINTER(C.c_void_p), _i, _u])
+SYMBOLS["cuda_decode_program_add_linears"] = (_i, [_vp, _u, C.POINTER(WqLinear), C.POINTER(DecodeInput), _u, _u])
+SYMBOLS["cuda_decode_program_add_attention"] = (_i, [_vp, C.POINTER(AttnDecode)])
+SYMBOLS["cuda_decode_program_finalize"] = (_i, [_vp])
+SYMBOLS["cuda_decode_program_launch"] = (_i, [_vp, _vp])
+SYMBOLS["cuda_decode_program_phases"] = (_u, [_vp])
+SYMBOLS["cuda_decode_program_destroy"] = (None, [_vp])
+
 _lib = None
 
 
@@ -296,6 +313,48 @@ def make_attn_decode(*, q, k, v, k_cache, v_cache, pos, out, cos_tab, sin_tab, B
 
 def attn_decode_bf16(desc, stream=None, flags: int = 0) -> int:
     return lib().cuda_attn_decode_bf16(C.byref(desc), _stream(stream), flags)
+
+
+class DecodeProgram:
+    """A recorded decode step that runs as one persistent kernel (cuda_decode_program_*)."""
+
+    def __init__(self, w_type: int, M: int):
+        self._h = C.c_void_p()
+        rc = lib().cuda_decode_program_create(C.byref(self._h), w_type, M)
+        if rc != 0:
+            raise ValueError(f"cuda_decode_program_create: {rc}")
+        self._keep = []
+
+    def add_linears(self, group, K: int, x, *, mode: int = X_COPY, ldx: int | None = None, x2=None, ldx2: int | None = None,
+                    norm_weight=None, eps: float = 1e-6, flags: int = 0) -> int:
+        d = DecodeInput(mode, _ptr(x), K if ldx is None else ldx, _ptr(x2), K if ldx2 is None else ldx2, _ptr(norm_weight), eps)
+        self._keep.append((group, x, x2, norm_weight))
+        return lib().cuda_decode_program_add_linears(self._h, len(group), group, C.byref(d), K, flags)
+
+    def add_attention(self, desc) -> int:
+        self._keep.append(desc)
+        return lib().cuda_decode_program_add_attention(self._h, C.byref(desc))
+
+    def finalize(self) -> int:
+        return lib().cuda_decode_program_finalize(self._h)
+
+    def launch(self, stream=None) -> int:
+        return lib().cuda_decode_program_launch(self._h, _stream(stream))
+
+    @property
+    def phases(self) -> int:
+        return int(lib().cuda_decode_program_phases(self._h))
+
+    def close(self):
+        if self._h:
+            lib().cuda_decode_program_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 def argmax_bf16(logits, rows: int, cols: int, idx_out, val_out=None, ld: int | None = None, stream: int | None = None) -> int:

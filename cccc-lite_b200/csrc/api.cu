@@ -5,6 +5,7 @@
 
 #include <atomic>
 #include <mutex>
+#include <vector>
 
 namespace b200
 {
@@ -66,6 +67,16 @@ unsigned int* cuda_b200_status_word()
     return ws ? ws->scratch.status : nullptr;
 }
 
+// Functions to run when one of the library's bounded waits ran out (they put device-side counters of
+// longer-lived objects back to zero).
+static std::mutex g_hook_mutex;
+static std::vector<void (*)(int)> g_reset_hooks;
+void register_reset_hook(void (*fn)(int device))
+{
+    std::lock_guard<std::mutex> lock(g_hook_mutex);
+    g_reset_hooks.push_back(fn);
+}
+
 int report_launch(const char* label)
 {
     const cudaError_t e = cudaGetLastError();
@@ -98,6 +109,12 @@ int sync_and_report(const char* label)
             fprintf(stderr, "%s kernel launch failed: a bounded wait ran out (status %u)\n", label, st);
             // A run that gave up may have left arrival counters behind: start clean again.
             cudaMemset(g_ws[dev].base.load(std::memory_order_acquire), 0, 8192);
+            std::vector<void (*)(int)> hooks;
+            {
+                std::lock_guard<std::mutex> lock(g_hook_mutex);
+                hooks = g_reset_hooks;
+            }
+            for (auto fn : hooks) { fn(dev); }
             return 1;
         }
     }

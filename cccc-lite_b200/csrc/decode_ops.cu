@@ -92,13 +92,6 @@ __global__ void __launch_bounds__(256) embed_bf16_kernel(const int* __restrict__
 }
 
 // ---- SwiGLU ----------------------------------------------------------------------------------------
-// out = bf16( bf16( g * bf16(sigmoid(g)) ) * u ): the reference's silu (a BF16 sigmoid tensor times
-// the input, MatrixEx.cpp:744-763) followed by elementMul (Matrix.cpp:1360-1386).
-__device__ __forceinline__ float swiglu_one(float g, float u)
-{
-    const float s = bf16_round(1.0f / (1.0f + expf(-g)));
-    return bf16_round(__fmul_rn(bf16_round(__fmul_rn(g, s)), u));
-}
 __global__ void __launch_bounds__(256) swiglu_bf16_kernel(const uint16_t* __restrict__ G, const uint16_t* __restrict__ U,
     uint16_t* __restrict__ O, unsigned int cols, unsigned int ldg, unsigned int ldu, unsigned int ldo)
 {

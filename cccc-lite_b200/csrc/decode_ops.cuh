@@ -29,14 +29,9 @@ __device__ __forceinline__ uint16_t bf16_bits(float f) { return __bfloat16_as_us
 // thread t accumulates x[t], x[t+256], ... with one fused multiply-add each, then the 256 partial
 // sums are combined by a halving tree.  part: rows * 256 floats of shared memory.  On return
 // part[row * 256] holds the sum of row `row`; all 256 threads of the team must call.
-__device__ __forceinline__ void team_sum_squares(const float* xs, float* part, unsigned int rows, unsigned int inner, unsigned int tid)
+// The halving tree over the 256 per-thread partial sums of each row (part[row * 256 + thread]).
+__device__ __forceinline__ void team_tree_sum(float* part, unsigned int rows, unsigned int tid)
 {
-    for (unsigned int r = 0; r < rows; r++)
-    {
-        float s = 0.f;
-        for (unsigned int i = tid; i < inner; i += kTeam) { s = __fmaf_rn(xs[r * inner + i], xs[r * inner + i], s); }
-        part[r * kTeam + tid] = s;
-    }
     team_sync();
     for (unsigned int s = kTeam / 2; s > 0; s >>= 1)
     {
@@ -46,6 +41,16 @@ __device__ __forceinline__ void team_sum_squares(const float* xs, float* part, u
         }
         team_sync();
     }
+}
+__device__ __forceinline__ void team_sum_squares(const float* xs, float* part, unsigned int rows, unsigned int inner, unsigned int tid)
+{
+    for (unsigned int r = 0; r < rows; r++)
+    {
+        float s = 0.f;
+        for (unsigned int i = tid; i < inner; i += kTeam) { s = __fmaf_rn(xs[r * inner + i], xs[r * inner + i], s); }
+        part[r * kTeam + tid] = s;
+    }
+    team_tree_sum(part, rows, tid);
 }
 
 // invstd of the reference: rsqrtf(sum / inner + eps).
@@ -61,6 +66,17 @@ __device__ __forceinline__ void rope_pair(float xl, float xr, float c, float s, 
     yl = bf16_round(__fmaf_rn(xl, c, -__fmul_rn(xr, s)));
     yr = bf16_round(__fmaf_rn(xr, c, __fmul_rn(xl, s)));
 }
+
+// out = bf16( bf16( g * bf16(sigmoid(g)) ) * u ): the reference's silu (a BF16 sigmoid tensor times
+// the input, MatrixEx.cpp:744-763) followed by elementMul (Matrix.cpp:1360-1386).
+__device__ __forceinline__ float swiglu_one(float g, float u)
+{
+    const float s = bf16_round(1.0f / (1.0f + expf(-g)));
+    return bf16_round(__fmul_rn(bf16_round(__fmul_rn(g, s)), u));
+}
+
+// 16-bit load that never comes from this SM's L1 (data another CTA of the same kernel may have written)
+__device__ __forceinline__ float ld_bf16_cg(const uint16_t* p) { return bf16_bits_to_float(__ldcg(p)); }
 
 // ---- attention of one new token per sequence ------------------------------------------------------
 struct AttnDecodeParams
@@ -128,7 +144,7 @@ __device__ __forceinline__ void attn_prologue(const AttnDecodeParams& p, AttnSme
     const uint16_t* k = p.k + (size_t)b * p.ldk + (size_t)kvh * HD;
     for (unsigned int i = tid; i < (G + 1) * HD; i += kTeam)
     {
-        sm.xin[i] = bf16_bits_to_float(i < G * HD ? q[i] : k[i - G * HD]);
+        sm.xin[i] = ld_bf16_cg(i < G * HD ? q + i : k + (i - G * HD));
     }
     team_sync();
     if (p.q_norm != nullptr || p.k_norm != nullptr) { team_sum_squares(sm.xin, sm.part, G + 1, HD, tid); }
@@ -160,7 +176,7 @@ __device__ __forceinline__ void attn_prologue(const AttnDecodeParams& p, AttnSme
         for (unsigned int i = tid; i < HD; i += kTeam)
         {
             kc[i] = bf16_bits(sm.kn[i]);
-            vc[i] = v[i];
+            vc[i] = __ldcg(v + i);
         }
     }
 }

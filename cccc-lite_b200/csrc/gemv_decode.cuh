@@ -363,6 +363,108 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
         : "memory");
 }
 
+// One k step (64 bytes of every weight row of the stage) of one consumer warp: dequantise the rows of
+// its RT row tiles, load its activation fragments, issue the MMAs.  st: shared-memory address of the
+// stage's weights (scales behind them); xt: address of the activation slabs of this stage, laid out
+// [128-byte slab][token][128 B]; wr: this warp's position along the rows; g, t: lane >> 2, lane & 3.
+template <class Cfg, bool SCALED>
+__device__ __forceinline__ void gemv_k_step(float (&acc)[Cfg::RT][Cfg::MT][2][4], const uint32_t st, const uint32_t xt,
+    const unsigned int step, const unsigned int wr, const unsigned int g, const unsigned int t, const float w_scale)
+{
+    constexpr int WT = Cfg::WT, MT = Cfg::MT, RT = Cfg::RT, R = Cfg::R;
+    constexpr int AREGS = (WT == DT_FP4) ? 16 : 8;    // bf16x2 registers per weight row per k step
+    // ---- weights: rows (g, g+8) of each of my RT tiles, 16 bytes per row ----
+    uint32_t A[RT][2][AREGS];
+#pragma unroll
+    for (int rt = 0; rt < RT; rt++)
+    {
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+        {
+            const unsigned int row = (wr * RT + rt) * 16 + h * 8 + g;
+            const uint4 wv = lds128(st + (step * R + row) * 64 + t * 16);
+            const uint32_t w[4] = { wv.x, wv.y, wv.z, wv.w };
+            if (WT == DT_FP4)
+            {
+                uint32_t m01[2];
+                fp4_block_multipliers(
+                    lds_u16(st + Cfg::W_BYTES + ((step >> 1) * R + row) * 16 + (step & 1u) * 8 + t * 2), m01[0], m01[1]);
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                {
+                    uint32_t r4[4];
+                    dequant_fp4x8(w[i], m01[i >> 1], r4);
+#pragma unroll
+                    for (int q = 0; q < 4; q++) { A[rt][h][(4 * i + q) % AREGS] = r4[q]; }
+                }
+            }
+            else
+            {
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                {
+                    dequant_fp8x4<WT, SCALED>(w[i], w_scale, A[rt][h][(2 * i) % AREGS], A[rt][h][(2 * i + 1) % AREGS]);
+                }
+            }
+        }
+    }
+    // ---- activations of my token column and the MMAs ----
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+    {
+        const unsigned int token = mt * 8 + g;
+        // token rows past M were zero-filled by the TMA; rows past the box do not exist
+        const bool live = token < (unsigned int)Cfg::XB;
+        const unsigned int swz = Cfg::XSWZ ? (token & 7u) : 0u;
+        if (WT == DT_FP4)
+        {
+            uint4 XBr[4];
+            const uint32_t xrow = xt + ((step * 2 + (t >> 1)) * Cfg::XB + token) * 128;
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+            {
+                // eight activations (x0..x7) -> (x0,x4)(x1,x5)(x2,x6)(x3,x7), the pairing of the
+                // dequantised nibbles
+                const unsigned int c = (t & 1u) * 4 + i;
+                const uint4 v = live ? lds128(xrow + ((c ^ swz) << 4)) : make_uint4(0, 0, 0, 0);
+                XBr[i].x = prmt(v.x, v.z, 0x5410u);
+                XBr[i].y = prmt(v.x, v.z, 0x7632u);
+                XBr[i].z = prmt(v.y, v.w, 0x5410u);
+                XBr[i].w = prmt(v.y, v.w, 0x7632u);
+            }
+#pragma unroll
+            for (int rt = 0; rt < RT; rt++)
+            {
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                {
+                    mma_bf16_16816(acc[rt][mt][0], A[rt][0][(4 * i) % AREGS], A[rt][1][(4 * i) % AREGS],
+                        A[rt][0][(4 * i + 1) % AREGS], A[rt][1][(4 * i + 1) % AREGS], XBr[i].x, XBr[i].y);
+                    mma_bf16_16816(acc[rt][mt][1], A[rt][0][(4 * i + 2) % AREGS], A[rt][1][(4 * i + 2) % AREGS],
+                        A[rt][0][(4 * i + 3) % AREGS], A[rt][1][(4 * i + 3) % AREGS], XBr[i].z, XBr[i].w);
+                }
+            }
+        }
+        else
+        {
+            const uint32_t xrow = xt + (step * Cfg::XB + token) * 128;
+            const uint4 x0 = live ? lds128(xrow + (((2 * t) ^ swz) << 4)) : make_uint4(0, 0, 0, 0);
+            const uint4 x1 = live ? lds128(xrow + (((2 * t + 1) ^ swz) << 4)) : make_uint4(0, 0, 0, 0);
+            const uint32_t B[8] = { x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w };
+#pragma unroll
+            for (int rt = 0; rt < RT; rt++)
+            {
+#pragma unroll
+                for (int q = 0; q < 4; q++)
+                {
+                    mma_bf16_16816(acc[rt][mt][q & 1], A[rt][0][2 * q], A[rt][1][2 * q], A[rt][0][2 * q + 1],
+                        A[rt][1][2 * q + 1], B[2 * q], B[2 * q + 1]);
+                }
+            }
+        }
+    }
+}
+
 // ---- the kernel ------------------------------------------------------------------------------------
 template <class Cfg, bool SCALED>
 __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
@@ -516,98 +618,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, Cfg::OCC)
             const unsigned int nsteps = kval / Cfg::KSTEP;    // beyond K the TMA fills zeros; skip them
             const uint32_t st = smem_u32(stages + (size_t)s * Cfg::STAGE_BYTES);
             const uint32_t xt = st + Cfg::X_OFFSET;
-            auto do_step = [&](unsigned int step) {
-                // ---- weights: rows (g, g+8) of each of my RT tiles, 16 bytes per row ----
-                uint32_t A[RT][2][AREGS];
-#pragma unroll
-                for (int rt = 0; rt < RT; rt++)
-                {
-#pragma unroll
-                    for (int h = 0; h < 2; h++)
-                    {
-                        const unsigned int row = (wr * RT + rt) * 16 + h * 8 + g;
-                        const uint4 wv = lds128(st + (step * R + row) * 64 + t * 16);
-                        const uint32_t w[4] = { wv.x, wv.y, wv.z, wv.w };
-                        if (WT == DT_FP4)
-                        {
-                            uint32_t m01[2];
-                            fp4_block_multipliers(
-                                lds_u16(st + Cfg::W_BYTES + ((step >> 1) * R + row) * 16 + (step & 1u) * 8 + t * 2), m01[0], m01[1]);
-#pragma unroll
-                            for (int i = 0; i < 4; i++)
-                            {
-                                uint32_t r4[4];
-                                dequant_fp4x8(w[i], m01[i >> 1], r4);
-#pragma unroll
-                                for (int q = 0; q < 4; q++) { A[rt][h][(4 * i + q) % AREGS] = r4[q]; }
-                            }
-                        }
-                        else
-                        {
-#pragma unroll
-                            for (int i = 0; i < 4; i++)
-                            {
-                                dequant_fp8x4<WT, SCALED>(w[i], w_scale, A[rt][h][(2 * i) % AREGS], A[rt][h][(2 * i + 1) % AREGS]);
-                            }
-                        }
-                    }
-                }
-                // ---- activations of my token column and the MMAs ----
-#pragma unroll
-                for (int mt = 0; mt < MT; mt++)
-                {
-                    const unsigned int token = mt * 8 + g;
-                    // token rows past M were zero-filled by the TMA; rows past the box do not exist
-                    const bool live = token < (unsigned int)Cfg::XB;
-                    const unsigned int swz = Cfg::XSWZ ? (token & 7u) : 0u;
-                    if (WT == DT_FP4)
-                    {
-                        uint4 XBr[4];
-                        const uint32_t xrow = xt + ((step * 2 + (t >> 1)) * Cfg::XB + token) * 128;
-#pragma unroll
-                        for (int i = 0; i < 4; i++)
-                        {
-                            // eight activations (x0..x7) -> (x0,x4)(x1,x5)(x2,x6)(x3,x7), the pairing of the
-                            // dequantised nibbles
-                            const unsigned int c = (t & 1u) * 4 + i;
-                            const uint4 v = live ? lds128(xrow + ((c ^ swz) << 4)) : make_uint4(0, 0, 0, 0);
-                            XBr[i].x = prmt(v.x, v.z, 0x5410u);
-                            XBr[i].y = prmt(v.x, v.z, 0x7632u);
-                            XBr[i].z = prmt(v.y, v.w, 0x5410u);
-                            XBr[i].w = prmt(v.y, v.w, 0x7632u);
-                        }
-#pragma unroll
-                        for (int rt = 0; rt < RT; rt++)
-                        {
-#pragma unroll
-                            for (int i = 0; i < 4; i++)
-                            {
-                                mma_bf16_16816(acc[rt][mt][0], A[rt][0][(4 * i) % AREGS], A[rt][1][(4 * i) % AREGS],
-                                    A[rt][0][(4 * i + 1) % AREGS], A[rt][1][(4 * i + 1) % AREGS], XBr[i].x, XBr[i].y);
-                                mma_bf16_16816(acc[rt][mt][1], A[rt][0][(4 * i + 2) % AREGS], A[rt][1][(4 * i + 2) % AREGS],
-                                    A[rt][0][(4 * i + 3) % AREGS], A[rt][1][(4 * i + 3) % AREGS], XBr[i].z, XBr[i].w);
-                            }
-                        }
-                    }
-                    else
-                    {
-                        const uint32_t xrow = xt + (step * Cfg::XB + token) * 128;
-                        const uint4 x0 = live ? lds128(xrow + (((2 * t) ^ swz) << 4)) : make_uint4(0, 0, 0, 0);
-                        const uint4 x1 = live ? lds128(xrow + (((2 * t + 1) ^ swz) << 4)) : make_uint4(0, 0, 0, 0);
-                        const uint32_t B[8] = { x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w };
-#pragma unroll
-                        for (int rt = 0; rt < RT; rt++)
-                        {
-#pragma unroll
-                            for (int q = 0; q < 4; q++)
-                            {
-                                mma_bf16_16816(acc[rt][mt][q & 1], A[rt][0][2 * q], A[rt][1][2 * q], A[rt][0][2 * q + 1],
-                                    A[rt][1][2 * q + 1], B[2 * q], B[2 * q + 1]);
-                            }
-                        }
-                    }
-                }
-                        };
+            auto do_step = [&](unsigned int step) { gemv_k_step<Cfg, SCALED>(acc, st, xt, step, wr, g, t, w_scale); };
             constexpr int SPW = (Cfg::SKS + WK - 1) / WK;    // k steps per warp in a full stage
             if (nsteps == (unsigned int)Cfg::SKS)
             {

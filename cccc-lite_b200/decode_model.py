@@ -180,6 +180,59 @@ class DecodeModel:
             self.ids[:M] = self.cand_all[:, :M, 1].gather(0, first.unsqueeze(0)).squeeze(0).to(t.int32)
         return n
 
+    # ---- the same step as ONE persistent kernel (cuda_decode_program_*), one GPU, M <= 2 ----
+    def build_program(self, M: int):
+        """Records the step's layers, final norm and lm_head as a decode program; embedding and arg-max stay
+        separate launches around it.  Raises ValueError where the program kernel does not take the model."""
+        if self.world > 1:
+            raise ValueError("the decode program runs on one GPU")
+        c, C = self.cfg, self.c
+        prog = C.DecodeProgram(self.wt, M)
+        RES = 8
+
+        def ok(rc, what):
+            if rc != 0:
+                prog.close()
+                raise ValueError(f"decode program: {what} not taken ({rc})")
+
+        groups = []
+        for P in self._plan(M):
+            L = P["L"]
+            ok(prog.add_linears(P["qkv"], c.hidden, self.x, mode=C.X_RMSNORM, norm_weight=L["attn_norm"], eps=c.eps), "q+k+v")
+            ok(prog.add_attention(P["attn"]), "attention")
+            W, S, inv = L["o"]
+            go = C.make_group([dict(W=W, S=S, inv=inv, N=c.hidden, Y=self.x, beta=1.0)], self.q_loc)
+            ok(prog.add_linears(go, self.q_loc, self.att, mode=C.X_COPY, flags=RES), "o")
+            ok(prog.add_linears(P["gu"], c.hidden, self.x, mode=C.X_RMSNORM, norm_weight=L["ffn_norm"], eps=c.eps), "gate+up")
+            W, S, inv = L["down"]
+            gd = C.make_group([dict(W=W, S=S, inv=inv, N=c.hidden, Y=self.x, beta=1.0)], self.ffn_loc)
+            ok(prog.add_linears(gd, self.ffn_loc, self.gu, mode=C.X_SWIGLU, ldx=2 * self.ffn_loc, x2=self.gu.data_ptr() + self.ffn_loc * 2,
+                                ldx2=2 * self.ffn_loc, flags=RES), "down")
+            groups += [go, gd]
+        W, S, inv = self.w["lm_head"]
+        gh = C.make_group([dict(W=W, S=S, inv=inv, N=self.vocab_loc, Y=self.logits)], c.hidden)
+        ok(prog.add_linears(gh, c.hidden, self.x, mode=C.X_RMSNORM, norm_weight=self.w["final_norm"], eps=c.eps), "lm_head")
+        ok(prog.finalize(), "finalize")
+        self._programs = getattr(self, "_programs", {})
+        self._programs[M] = (prog, groups, gh)
+        return prog
+
+    def step_program(self, M: int, from_ids: bool = True) -> int:
+        """One decode step through the recorded program: embedding, ONE kernel, arg-max.  Same inputs and
+        outputs as step()."""
+        c, C = self.cfg, self.c
+        prog = self._programs[M][0]
+        n = 0
+        if from_ids:
+            if C.embed_bf16(self.ids, self.w["emb"], self.x, c.hidden, M, c.vocab) != 0:
+                raise RuntimeError("embed failed")
+            n += 1
+        if prog.launch() != 0:
+            raise RuntimeError("decode program launch failed")
+        if C.argmax_bf16(self.logits, M, self.vocab_loc, self.ids, self.best) != 0:
+            raise RuntimeError("argmax failed")
+        return n + 2
+
     def kv_bytes_full(self, M: int, context: int) -> int:
         """Bytes of K and V rows a step of the WHOLE model (all ranks) reads when every sequence has `context` cached rows."""
         c = self.cfg

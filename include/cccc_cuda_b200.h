@@ -257,6 +257,50 @@ typedef struct cuda_attn_decode
 } cuda_attn_decode;
 C_EXPORT int cuda_attn_decode_bf16(const cuda_attn_decode* a, void* stream, unsigned int flags);
 
+/* ---- additions: a whole decode step as one kernel ------------------------------------------- */
+
+/* No counterpart in the reference (it issues about 40 ops per layer, each followed by a device
+ * synchronisation: cccc/MatrixOp.cpp:12-64, cccc-cuda/cuda_functions.cu:26-40).  A decode step at batch
+ * 1 or 2 is a chain of ~150 dependent GEMVs of 4-100 MB; issued one by one, HBM idles for microseconds
+ * around every launch.  A "decode program" records the chain once - linears with the op that produces
+ * their input, attention - and runs it as ONE persistent kernel per step: one CTA per SM walks the list,
+ * the weight stream of the next linear is already in flight through shared memory while the CTAs meet
+ * at the end of the current one.  Results are those of the separate calls (the same arithmetic in the
+ * same order wherever the schedules coincide).
+ *   create        : w_type 4, 5 or 6 for every linear of the program; M_tokens 1 or 2.
+ *   add_linears   : 1-3 linears that share their input (fields as cuda_gemm_wq_bf16_group).  `in` says
+ *                   how the input is made: mode 0 = x itself ([M][ldx] BF16, 16-byte aligned, ldx % 8 == 0);
+ *                   mode 1 = RMSNorm of x with norm_weight (NULL = 1) and epsilon, as cuda_rms_norm_bf16;
+ *                   mode 2 = SwiGLU of x (gate) and x2 (up), as cuda_swiglu_bf16.  flags bit 2 (float32
+ *                   output) and bit 3 (residual epilogue) as cuda_gemm_wq_bf16.  K % 64 == 0 (FP4: 256),
+ *                   weights 16-byte aligned with ldw % 16 == 0 (FP4: block scales, ldw % 256 == 0).
+ *   add_attention : as cuda_attn_decode_bf16 with B = M_tokens, head_dim 128 and H = 4 Hkv.
+ *   finalize      : uploads the program and allocates its scratch (the only step that allocates; make it
+ *                   outside any stream capture).  Buffers named in the program must stay alive.
+ *   launch        : one cooperative kernel on `stream`.  Launches of one program must not overlap.
+ * Phases follow each other in the order added; each one sees everything the earlier ones wrote.
+ * Every function returns 0, 1 (CUDA error) or -1 (an argument the program kernel does not take: use the
+ * separate entry points for that step). */
+typedef struct cuda_decode_program cuda_decode_program;
+typedef struct cuda_decode_input
+{
+    int mode;
+    const void* x;
+    unsigned int ldx;
+    const void* x2;
+    unsigned int ldx2;
+    const void* norm_weight;
+    float epsilon;
+} cuda_decode_input;
+C_EXPORT int cuda_decode_program_create(cuda_decode_program** out, int w_type, unsigned int M_tokens);
+C_EXPORT int cuda_decode_program_add_linears(cuda_decode_program* p, unsigned int count, const cuda_wq_linear* linears,
+    const cuda_decode_input* in, unsigned int K, unsigned int flags);
+C_EXPORT int cuda_decode_program_add_attention(cuda_decode_program* p, const cuda_attn_decode* a);
+C_EXPORT int cuda_decode_program_finalize(cuda_decode_program* p);
+C_EXPORT int cuda_decode_program_launch(cuda_decode_program* p, void* stream);
+C_EXPORT unsigned int cuda_decode_program_phases(const cuda_decode_program* p);
+C_EXPORT void cuda_decode_program_destroy(cuda_decode_program* p);
+
 /* Tuning/diagnostic: returns which kernel cuda_gemm_wq_bf16 would pick for a shape
  * (0 = plain kernel, 1 = decode GEMV (M<=32), 2 = prefill tcgen05 GEMM) without launching. */
 C_EXPORT int cuda_gemm_wq_bf16_plan(int w_type, const void* W, const void* blk_scales, const void* X,

