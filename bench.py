@@ -498,7 +498,7 @@ def gpu_arm(args):
         return float(t.item())
 
     prog = None
-    if world == 1 and M <= 2 and not args.no_program:
+    if world == 1 and M <= 2 and args.program:
         try:
             prog = build_chain_program(capi, wt, calls, M)
         except ValueError as e:
@@ -630,7 +630,7 @@ def gpu_arm(args):
             for mb in (1, 32):
                 steps[f"batch{mb}"] = time_decode_step(torch, dist, capi, model, dims, mb, args.wtype, flags, 30 if mb == 1 else 8, dev, stream,
                                                        world)
-            if world == 1 and not args.no_program:
+            if world == 1:
                 for mb in (1, 2):
                     try:
                         steps[f"batch{mb}_program"] = time_decode_step(torch, dist, capi, model, dims, mb, args.wtype, flags, 30, dev, stream, world,
@@ -966,7 +966,8 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip decode_by_m, fp4 and ref_gpu")
     ap.add_argument("--no-decode-step", action="store_true")
-    ap.add_argument("--no-program", action="store_true", help="issue the chain launch by launch even where the decode program takes it")
+    ap.add_argument("--program", action="store_true",
+                    help="headline chain through cuda_decode_program_* (one persistent kernel per token) instead of launch by launch")
     ap.add_argument("--watchdog", type=float, default=540.0, help="seconds after which a stuck run exits by itself")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

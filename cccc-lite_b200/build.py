@@ -59,10 +59,36 @@ def build_host(force: bool = False) -> str:
     return HOST_LIB
 
 
+OBJ_DIR = os.path.join(HERE, "build")    # git-ignored object files: only changed translation units are recompiled
+
+
+def _object_stale(src: str, obj: str) -> bool:
+    if not os.path.exists(obj):
+        return True
+    t = os.path.getmtime(obj)
+    deps = [src] + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(HERE, "..", "include", "*.h"))
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
+    """Compiles every translation unit of csrc/ for sm_100a (in parallel, only the stale ones) and links the library."""
     if force or stale():
-        cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + sources()
-        subprocess.check_call(cmd)
+        from concurrent.futures import ThreadPoolExecutor
+
+        os.makedirs(OBJ_DIR, exist_ok=True)
+        compile_flags = [f for f in FLAGS if f != "-shared"]
+        extra = os.environ.get("B200_NVCC_EXTRA", "").split()
+        jobs = []
+        for src in sources():
+            obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
+            if force or extra or _object_stale(src, obj):
+                jobs.append([NVCC] + compile_flags + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", "-o", obj, src])
+        with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as pool:
+            for rc in pool.map(subprocess.call, jobs):
+                if rc != 0:
+                    raise subprocess.CalledProcessError(rc, "nvcc")
+        objs = [os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o") for src in sources()]
+        subprocess.check_call([NVCC, "-shared", "-cudart", "shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB] + objs)
     build_host(force)
     return LIB
 

@@ -124,24 +124,23 @@ __global__ void __launch_bounds__(kTeam) attn_decode_kernel(const AttnDecodePara
     ts = (ts + 31u) & ~31u;
     const unsigned int t0 = min(rank * ts, T), t1 = min(t0 + ts, T);
     const bool owner = pos >= t0 && pos < t1;
-    attn_prologue<G, HD>(p, sm, b, kvh, pos, owner, tid);
-    attn_scores<G, HD>(p, sm, b, kvh, t0, t1, ts_cap, pos, owner, tid);
+    attn_scores<G, HD>(p, sm, b, kvh, t0, t1, ts_cap, pos, owner, tid);    // (runs the prologue too)
     cluster.sync();
-    if (tid < G)
-    {
-        float gmax = -INFINITY;
-        for (unsigned int r = 0; r < S; r++) { gmax = fmaxf(gmax, cluster.map_shared_rank(sm.ml, r)[2 * tid]); }
-        float L = 0.f;
-        for (unsigned int r = 0; r < S; r++)
+    attn_pv<G, HD>(p, sm, b, kvh, t0, t1, ts_cap, owner ? pos : 0xFFFFFFFFu, tid, [&]() {
+        if (tid < G)
         {
-            const float* ml = cluster.map_shared_rank(sm.ml, r);
-            if (ml[2 * tid + 1] > 0.f) { L += ml[2 * tid + 1] * __expf(ml[2 * tid] - gmax); }
+            float gmax = -INFINITY;
+            for (unsigned int r = 0; r < S; r++) { gmax = fmaxf(gmax, cluster.map_shared_rank(sm.ml, r)[2 * tid]); }
+            float L = 0.f;
+            for (unsigned int r = 0; r < S; r++)
+            {
+                const float* ml = cluster.map_shared_rank(sm.ml, r);
+                if (ml[2 * tid + 1] > 0.f) { L += ml[2 * tid + 1] * __expf(ml[2 * tid] - gmax); }
+            }
+            sm.gl[2 * tid] = gmax;
+            sm.gl[2 * tid + 1] = 1.0f / L;
         }
-        sm.gl[2 * tid] = gmax;
-        sm.gl[2 * tid + 1] = 1.0f / L;
-    }
-    team_sync();
-    attn_pv<G, HD>(p, sm, b, kvh, t0, t1, ts_cap, owner ? pos : 0xFFFFFFFFu, tid);
+    });
     cluster.sync();
     if (rank == 0)
     {
@@ -325,8 +324,10 @@ C_EXPORT int cuda_attn_decode_bf16(const cuda_attn_decode* a, void* stream, unsi
     if (a->B == 0 || a->H == 0) { return 0; }
     if (!a->q || !a->k || !a->v || !a->cos_tab || !a->sin_tab || !a->k_cache || !a->v_cache || !a->pos || !a->out) { return -1; }
     if (a->Hkv == 0 || (a->H % a->Hkv) != 0 || a->T_max == 0 || a->B > 65535u || a->Hkv > 65535u) { return -1; }
-    if ((a->ldv % 8) != 0 || (reinterpret_cast<uintptr_t>(a->v) & 15u) != 0 || (reinterpret_cast<uintptr_t>(a->k_cache) & 15u) != 0
-        || (reinterpret_cast<uintptr_t>(a->v_cache) & 15u) != 0)
+    auto misaligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) != 0; };
+    if ((a->ldq % 8) != 0 || (a->ldk % 8) != 0 || (a->ldv % 8) != 0 || misaligned(a->q) || misaligned(a->k) || misaligned(a->v)
+        || misaligned(a->k_cache) || misaligned(a->v_cache) || misaligned(a->cos_tab) || misaligned(a->sin_tab)
+        || (a->q_norm && misaligned(a->q_norm)) || (a->k_norm && misaligned(a->k_norm)))
     {
         return -1;
     }

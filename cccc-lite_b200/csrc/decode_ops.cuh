@@ -29,11 +29,14 @@ __device__ __forceinline__ uint16_t bf16_bits(float f) { return __bfloat16_as_us
 // thread t accumulates x[t], x[t+256], ... with one fused multiply-add each, then the 256 partial
 // sums are combined by a halving tree.  part: rows * 256 floats of shared memory.  On return
 // part[row * 256] holds the sum of row `row`; all 256 threads of the team must call.
-// The halving tree over the 256 per-thread partial sums of each row (part[row * 256 + thread]).
+// The halving tree over the 256 per-thread partial sums of each row (part[row * 256 + thread]):
+// p[t] += p[t + s] for s = 128, 64, ..., 1, exactly the additions of the reference's kernel.  The
+// levels that cross warps go through shared memory; the last five stay inside warp 0, where
+// p[t] += p[t + s] is a shuffle-down (lanes >= s compute values that are never used again).
 __device__ __forceinline__ void team_tree_sum(float* part, unsigned int rows, unsigned int tid)
 {
     team_sync();
-    for (unsigned int s = kTeam / 2; s > 0; s >>= 1)
+    for (unsigned int s = kTeam / 2; s >= 32; s >>= 1)
     {
         if (tid < s)
         {
@@ -41,6 +44,17 @@ __device__ __forceinline__ void team_tree_sum(float* part, unsigned int rows, un
         }
         team_sync();
     }
+    if (tid < 32)
+    {
+        for (unsigned int r = 0; r < rows; r++)
+        {
+            float v = part[r * kTeam + tid];
+#pragma unroll
+            for (int s = 16; s > 0; s >>= 1) { v += __shfl_down_sync(0xFFFFFFFFu, v, s); }
+            if (tid == 0) { part[r * kTeam] = v; }
+        }
+    }
+    team_sync();
 }
 __device__ __forceinline__ void team_sum_squares(const float* xs, float* part, unsigned int rows, unsigned int inner, unsigned int tid)
 {
@@ -110,6 +124,7 @@ struct AttnSmem
     float* gl;      // [G][2]    the sequence's max and 1/sum
     float* opart;   // [G][HD]   this split's partial output
     float* red;     // [kSlots2][G][HD]
+    float* wq;      // [HD] q-norm weights, [HD] k-norm weights, [HD/2] cos row, [HD/2] sin row
     float* sc;      // [G][ts_cap] scores, then probabilities
     __device__ AttnSmem(float* base, unsigned int ts_cap)
     {
@@ -121,7 +136,8 @@ struct AttnSmem
         gl = ml + 2 * G;
         opart = gl + 2 * G;
         red = opart + G * HD;
-        sc = red + kSlots2 * G * HD;
+        wq = red + kSlots2 * G * HD;
+        sc = wq + 3 * HD;
         (void)ts_cap;
     }
 };
@@ -129,22 +145,81 @@ template <int G, int HD>
 __host__ __device__ constexpr size_t attn_smem_floats(unsigned int ts_cap)
 {
     return (size_t)G * HD + HD + (size_t)(G + 1) * HD + (size_t)(G + 1) * kTeam + 4 * G + (size_t)G * HD
-        + (size_t)(kTeam / (HD / 8)) * G * HD + (size_t)G * ts_cap;
+        + (size_t)(kTeam / (HD / 8)) * G * HD + 3 * HD + (size_t)G * ts_cap;
+}
+
+__device__ __forceinline__ void unpack8(const uint4 v, float (&f)[8])
+{
+    const uint32_t w[4] = { v.x, v.y, v.z, v.w };
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+    {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
 }
 
 // Prologue of a split: the G query heads of kv head `kvh` of sequence b are normalised (optional)
 // and rotated into sm.qs; the split that owns row `pos` also normalises and rotates the new key,
 // appends it and the new value to the caches (MatrixOp.cpp:237-276) and keeps the key in sm.kn.
+// Every global input (q heads, k head, the two norm weights, the cos and sin rows of `pos`) is
+// fetched in ONE round trip, one 16-byte piece per thread; q and k rows must be 16-byte aligned.
 template <int G, int HD>
 __device__ __forceinline__ void attn_prologue(const AttnDecodeParams& p, AttnSmem<G, HD>& sm, unsigned int b, unsigned int kvh,
     unsigned int pos, bool owner, unsigned int tid)
 {
     constexpr int HALF = HD / 2;
-    const uint16_t* q = p.q + (size_t)b * p.ldq + (size_t)kvh * G * HD;
-    const uint16_t* k = p.k + (size_t)b * p.ldk + (size_t)kvh * HD;
-    for (unsigned int i = tid; i < (G + 1) * HD; i += kTeam)
+    constexpr unsigned int NQ = (G + 1) * HD / 8, NW = HD / 8, NT = HALF / 8;
+    static_assert(NQ + 2 * NW + 2 * NT <= kTeam, "one piece per thread");
     {
-        sm.xin[i] = ld_bf16_cg(i < G * HD ? q + i : k + (i - G * HD));
+        const uint16_t* q = p.q + (size_t)b * p.ldq + (size_t)kvh * G * HD;
+        const uint16_t* k = p.k + (size_t)b * p.ldk + (size_t)kvh * HD;
+        const uint16_t* src = nullptr;
+        float* dst = nullptr;
+        bool fresh = false;    // written by the previous phase or kernel: not through this SM's L1
+        unsigned int i = tid;
+        if (i < NQ)
+        {
+            src = i < G * HD / 8 ? q + i * 8 : k + (i - G * HD / 8) * 8;
+            dst = sm.xin + i * 8;
+            fresh = true;
+        }
+        else if ((i -= NQ) < NW)
+        {
+            src = p.q_norm ? p.q_norm + i * 8 : nullptr;
+            dst = sm.wq + i * 8;
+        }
+        else if ((i -= NW) < NW)
+        {
+            src = p.k_norm ? p.k_norm + i * 8 : nullptr;
+            dst = sm.wq + HD + i * 8;
+        }
+        else if ((i -= NW) < NT)
+        {
+            src = p.cos_tab + (size_t)pos * HALF + i * 8;
+            dst = sm.wq + 2 * HD + i * 8;
+        }
+        else if ((i -= NT) < NT)
+        {
+            src = p.sin_tab + (size_t)pos * HALF + i * 8;
+            dst = sm.wq + 2 * HD + HALF + i * 8;
+        }
+        if (dst != nullptr)
+        {
+            float f[8];
+            if (src != nullptr)
+            {
+                const uint4 v = fresh ? __ldcg(reinterpret_cast<const uint4*>(src)) : __ldg(reinterpret_cast<const uint4*>(src));
+                unpack8(v, f);
+            }
+            else
+            {
+#pragma unroll
+                for (int e = 0; e < 8; e++) { f[e] = 1.f; }
+            }
+#pragma unroll
+            for (int e = 0; e < 8; e++) { dst[e] = f[e]; }
+        }
     }
     team_sync();
     if (p.q_norm != nullptr || p.k_norm != nullptr) { team_sum_squares(sm.xin, sm.part, G + 1, HD, tid); }
@@ -152,17 +227,15 @@ __device__ __forceinline__ void attn_prologue(const AttnDecodeParams& p, AttnSme
     for (unsigned int i = tid; i < (G + 1) * HD; i += kTeam)
     {
         const unsigned int r = i / HD, d = i - r * HD;
-        const uint16_t* w = r < G ? p.q_norm : p.k_norm;
-        if (w != nullptr) { sm.xin[i] = rms_apply(sm.xin[i], rms_invstd(sm.part[r * kTeam], HD, p.eps), bf16_bits_to_float(w[d])); }
+        const bool has = r < G ? p.q_norm != nullptr : p.k_norm != nullptr;
+        if (has) { sm.xin[i] = rms_apply(sm.xin[i], rms_invstd(sm.part[r * kTeam], HD, p.eps), sm.wq[(r < G ? 0 : HD) + d]); }
     }
     team_sync();
     for (unsigned int i = tid; i < (G + 1) * HALF; i += kTeam)
     {
         const unsigned int r = i / HALF, d = i - r * HALF;
-        const float c = bf16_bits_to_float(p.cos_tab[(size_t)pos * HALF + d]);
-        const float s = bf16_bits_to_float(p.sin_tab[(size_t)pos * HALF + d]);
         float yl, yr;
-        rope_pair(sm.xin[r * HD + d], sm.xin[r * HD + HALF + d], c, s, yl, yr);
+        rope_pair(sm.xin[r * HD + d], sm.xin[r * HD + HALF + d], sm.wq[2 * HD + d], sm.wq[2 * HD + HALF + d], yl, yr);
         float* dst = r < G ? sm.qs + r * HD : sm.kn;
         dst[d] = yl;
         dst[HALF + d] = yr;
@@ -181,42 +254,21 @@ __device__ __forceinline__ void attn_prologue(const AttnDecodeParams& p, AttnSme
     }
 }
 
-__device__ __forceinline__ void unpack8(const uint4 v, float (&f)[8])
-{
-    const uint32_t w[4] = { v.x, v.y, v.z, v.w };
-#pragma unroll
-    for (int i = 0; i < 4; i++)
-    {
-        f[2 * i] = __uint_as_float(w[i] << 16);
-        f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-    }
-}
-
-// Scores of the rows [t0, t1) of one kv head against the G rotated queries:
-// sm.sc[g][t - t0] = bf16(scale * K[t] . q_g) (the reference's BF16 score tensor,
-// MatrixEx.cpp:3056), and this split's maximum and sum of exp(score - maximum) per head in sm.ml.
-// Eight lanes share a row (two 16-byte pieces each for HD = 128), 32 rows per pass.
-template <int G, int HD>
+// Prologue and scores of the rows [t0, t1) of one kv head against the G rotated queries:
+// sm.sc[g][t - t0] = bf16(scale * K[t] . q_g) (the reference's BF16 score tensor, MatrixEx.cpp:3056),
+// and this split's maximum and sum of exp(score - maximum) per head in sm.ml.  Eight lanes share a
+// row (two 16-byte pieces each for HD = 128), 32 rows per pass, UNROLL passes in flight.  The first
+// batch of K rows is requested BEFORE the prologue runs: the cache does not depend on q, so the DRAM
+// latency of the first batch and the prologue's own round trip overlap.
+template <int G, int HD, int UNROLL = (G <= 4 ? 8 : 4)>
 __device__ __forceinline__ void attn_scores(const AttnDecodeParams& p, AttnSmem<G, HD>& sm, unsigned int b, unsigned int kvh,
     unsigned int t0, unsigned int t1, unsigned int ts_cap, unsigned int pos, bool owner, unsigned int tid)
 {
     constexpr int CPL = HD / 64;    // 16-byte pieces per lane
     const unsigned int sub = tid & 7u, slot = tid >> 3;
-    float qf[G][CPL][8];
-#pragma unroll
-    for (int g = 0; g < G; g++)
-#pragma unroll
-        for (int c = 0; c < CPL; c++)
-#pragma unroll
-            for (int e = 0; e < 8; e++) { qf[g][c][e] = sm.qs[g * HD + (sub + 8 * c) * 8 + e]; }
     const uint16_t* Kb = p.k_cache + ((size_t)b * p.Hkv + kvh) * p.T_max * HD;
-    float mx[G];
-#pragma unroll
-    for (int g = 0; g < G; g++) { mx[g] = -INFINITY; }
-    constexpr int UNROLL = 4;
-    for (unsigned int tb = t0; tb < t1; tb += 32 * UNROLL)
-    {
-        uint4 kv[UNROLL][CPL];
+    uint4 kv[UNROLL][CPL];
+    auto fetch = [&](unsigned int tb) {
 #pragma unroll
         for (int u = 0; u < UNROLL; u++)
         {
@@ -228,6 +280,22 @@ __device__ __forceinline__ void attn_scores(const AttnDecodeParams& p, AttnSmem<
                                                             : make_uint4(0, 0, 0, 0);
             }
         }
+    };
+    fetch(t0);
+    attn_prologue<G, HD>(p, sm, b, kvh, pos, owner, tid);
+    float qf[G][CPL][8];
+#pragma unroll
+    for (int g = 0; g < G; g++)
+#pragma unroll
+        for (int c = 0; c < CPL; c++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) { qf[g][c][e] = sm.qs[g * HD + (sub + 8 * c) * 8 + e]; }
+    float mx[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) { mx[g] = -INFINITY; }
+    for (unsigned int tb = t0; tb < t1; tb += 32 * UNROLL)
+    {
+        if (tb != t0) { fetch(tb); }
 #pragma unroll
         for (int u = 0; u < UNROLL; u++)
         {
@@ -310,15 +378,34 @@ __device__ __forceinline__ void attn_scores(const AttnDecodeParams& p, AttnSmem<
 }
 
 // Probabilities and P*V for the rows [t0, t1): p = bf16(exp(score - max) / sum) with the
-// sequence-wide max and 1/sum in sm.gl (the reference's BF16 softmax tensor, MatrixEx.cpp:3091),
-// then opart[g][d] = sum_t V[t][d] * p[g][t] in FP32.  HD/8 lanes share a row (16 bytes each).
-template <int G, int HD>
+// sequence-wide max and 1/sum (the reference's BF16 softmax tensor, MatrixEx.cpp:3091), then
+// opart[g][d] = sum_t V[t][d] * p[g][t] in FP32.  HD/8 lanes share a row (16 bytes each).
+// `stats` produces the sequence-wide (max, 1/sum) into sm.gl; it runs AFTER the first batch of V
+// rows has been requested, because V does not depend on it.
+template <int G, int HD, class Stats>
 __device__ __forceinline__ void attn_pv(const AttnDecodeParams& p, AttnSmem<G, HD>& sm, unsigned int b, unsigned int kvh,
-    unsigned int t0, unsigned int t1, unsigned int ts_cap, unsigned int pos_row, unsigned int tid)
+    unsigned int t0, unsigned int t1, unsigned int ts_cap, unsigned int pos_row, unsigned int tid, Stats stats)
 {
     constexpr int LPR = HD / 8;             // lanes per row
     constexpr int SLOTS = kTeam / LPR;      // rows per pass
+    constexpr int UNROLL = 8;
     const unsigned int n = t1 > t0 ? t1 - t0 : 0;
+    const unsigned int sub = tid % LPR, slot = tid / LPR;
+    const uint16_t* Vb = p.v_cache + ((size_t)b * p.Hkv + kvh) * p.T_max * HD;
+    uint4 vv[UNROLL];
+    auto fetch = [&](unsigned int tb) {
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++)
+        {
+            const unsigned int t = tb + u * SLOTS + slot;
+            // the row this call appended comes from the projection output, not back from the cache
+            const uint16_t* vrow = t == pos_row ? p.v + (size_t)b * p.ldv + (size_t)kvh * HD : Vb + (size_t)t * HD;
+            vv[u] = t < t1 ? __ldcg(reinterpret_cast<const uint4*>(vrow) + sub) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    fetch(t0);
+    stats();
+    team_sync();
 #pragma unroll
     for (int g = 0; g < G; g++)
     {
@@ -329,25 +416,14 @@ __device__ __forceinline__ void attn_pv(const AttnDecodeParams& p, AttnSmem<G, H
         }
     }
     team_sync();
-    const unsigned int sub = tid % LPR, slot = tid / LPR;
-    const uint16_t* Vb = p.v_cache + ((size_t)b * p.Hkv + kvh) * p.T_max * HD;
     float acc[G][8];
 #pragma unroll
     for (int g = 0; g < G; g++)
 #pragma unroll
         for (int e = 0; e < 8; e++) { acc[g][e] = 0.f; }
-    constexpr int UNROLL = 4;
     for (unsigned int tb = t0; tb < t1; tb += SLOTS * UNROLL)
     {
-        uint4 vv[UNROLL];
-#pragma unroll
-        for (int u = 0; u < UNROLL; u++)
-        {
-            const unsigned int t = tb + u * SLOTS + slot;
-            // the row this call appended comes from the projection output, not back from the cache
-            const uint16_t* vrow = t == pos_row ? p.v + (size_t)b * p.ldv + (size_t)kvh * HD : Vb + (size_t)t * HD;
-            vv[u] = t < t1 ? __ldcg(reinterpret_cast<const uint4*>(vrow) + sub) : make_uint4(0, 0, 0, 0);
-        }
+        if (tb != t0) { fetch(tb); }
 #pragma unroll
         for (int u = 0; u < UNROLL; u++)
         {

@@ -35,6 +35,7 @@ struct cuda_decode_program
     std::vector<CUtensorMap> maps;
     std::vector<float> inv_scales;    // per segment, in phase order (the split into w_scale / post_scale is made at finalise)
     bool any_unscalable = false;      // an FP8 scale that is not a power of two
+    bool fma = false;                 // CUDA-core k steps (no per-weight multiplier needed): decided at finalise
     unsigned int max_K = 0;
     unsigned int attn_items = 0, attn_heads = 0;
     size_t attn_smem = 0;
@@ -62,14 +63,18 @@ void reset_programs(int device)
     std::lock_guard<std::mutex> lock(g_prog_mutex);
     for (cuda_decode_program* p : g_programs)
     {
-        if (p->device == device && p->d_words) { cudaMemset(p->d_words, 0, p->words * sizeof(unsigned int)); }
+        if (p->device == device && p->d_words)
+        {
+            cudaMemset(p->d_words, 0, p->words * sizeof(unsigned int));
+            p->hd.epoch = 0;
+        }
     }
 }
 
-template <int WT, bool SCALED>
+template <int WT, bool SCALED, bool FMA>
 int launch_program(cuda_decode_program* p, cudaStream_t stream)
 {
-    auto kernel = decode_program_kernel<WT, SCALED, 4>;
+    auto kernel = decode_program_kernel<WT, SCALED, 4, FMA>;
     static std::atomic<bool> attr_set[64];
     if (!attr_set[p->device].load(std::memory_order_acquire))
     {
@@ -87,6 +92,7 @@ int launch_program(cuda_decode_program* p, cudaStream_t stream)
         report_launch("decode_program");
         return 1;
     }
+    p->hd.epoch++;    // the kernel's arrival targets are relative to the launches before it
     return 0;
 }
 }    // namespace
@@ -118,8 +124,10 @@ C_EXPORT int cuda_decode_program_add_linears(cuda_decode_program* p, unsigned in
     const bool fp4 = p->w_type == DT_FP4;
     if (in->mode < 0 || in->mode > 2 || !in->x || (in->mode == (int)XM_SWIGLU && !in->x2)) { return -1; }
     // what the TMA-fed kernel takes: whole k steps, 16-byte aligned rows
-    if ((K % (fp4 ? 256u : 64u)) != 0) { return -1; }
-    if (in->mode == (int)XM_COPY && (((uintptr_t)in->x & 15u) != 0 || (in->ldx % 8) != 0)) { return -1; }
+    if ((K % (fp4 ? 256u : 64u)) != 0 || K > 16384u) { return -1; }
+    // the team reads its inputs with 16-byte loads
+    if (((uintptr_t)in->x & 15u) != 0 || (in->ldx % 8) != 0) { return -1; }
+    if (in->mode == (int)XM_SWIGLU && (((uintptr_t)in->x2 & 15u) != 0 || (in->ldx2 % 8) != 0)) { return -1; }
     using Cfg = ChainCfg<DT_E5M2>;
     ProgPhase ph;
     memset(&ph, 0, sizeof(ph));
@@ -128,6 +136,13 @@ C_EXPORT int cuda_decode_program_add_linears(cuda_decode_program* p, unsigned in
     ph.K = K;
     ph.x_mode = (unsigned)in->mode;
     ph.out_mode = (flags & 4u) ? 1u : ((flags & 8u) ? 2u : 0u);
+    ph.paired = (flags & 16u) ? 1u : 0u;
+    if (ph.paired
+        && (count != 2 || lin[0].N_out != lin[1].N_out || (lin[0].N_out % 16) != 0 || lin[0].beta != 0.f || lin[1].beta != 0.f || ph.out_mode != 0))
+    {
+        return -1;
+    }
+    const unsigned int box_rows = ph.paired ? 16u : (unsigned)ChainCfg<DT_E5M2>::R;
     ph.x_src = (const uint16_t*)in->x;
     ph.x_src2 = (const uint16_t*)in->x2;
     ph.norm_w = (const uint16_t*)in->norm_weight;
@@ -146,7 +161,10 @@ C_EXPORT int cuda_decode_program_add_linears(cuda_decode_program* p, unsigned in
             continue;
         }
         const cuda_wq_linear& L = lin[j];
-        if (!L.W || !L.Y || L.N_out == 0 || ((uintptr_t)L.W & 15u) != 0 || (L.ldw % (fp4 ? 256u : 16u)) != 0) { return -1; }
+        if (!L.W || (!L.Y && !(ph.paired && j == 1)) || L.N_out == 0 || ((uintptr_t)L.W & 15u) != 0 || (L.ldw % (fp4 ? 256u : 16u)) != 0)
+        {
+            return -1;
+        }
         if (fp4 && (!L.blk_scales || ((uintptr_t)L.blk_scales & 15u) != 0)) { return -1; }
         g.W = (const uint8_t*)L.W;
         g.blk = fp4 ? (const uint8_t*)L.blk_scales : nullptr;
@@ -157,14 +175,22 @@ C_EXPORT int cuda_decode_program_add_linears(cuda_decode_program* p, unsigned in
         g.ldy_n = L.ldy_n;
         g.alpha = L.alpha;
         g.beta = L.beta;
-        g.rb_begin = ph.n_row_blocks;
-        ph.n_row_blocks += (L.N_out + Cfg::R - 1) / Cfg::R;
+        if (ph.paired)
+        {
+            g.rb_begin = j == 0 ? 0u : 0xFFFFFFFFu;    // one list of row blocks: 16 gate rows + the same 16 up rows each
+            if (j == 0) { ph.n_row_blocks = L.N_out / 16; }
+        }
+        else
+        {
+            g.rb_begin = ph.n_row_blocks;
+            ph.n_row_blocks += (L.N_out + Cfg::R - 1) / Cfg::R;
+        }
         if (!fp4 && !chain_pow2_scale(L.inv_scale)) { p->any_unscalable = true; }
         CUtensorMap mw, ms;
         const unsigned long long ldw_bytes = fp4 ? L.ldw / 2 : L.ldw;
-        if (!make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, L.W, 64, L.N_out, kbytes / 64, ldw_bytes, Cfg::R, SKS, false)) { return -1; }
+        if (!make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, L.W, 64, L.N_out, kbytes / 64, ldw_bytes, box_rows, SKS, false)) { return -1; }
         ms = mw;
-        if (fp4 && !make_map(&ms, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, L.blk_scales, 16, L.N_out, K / 256, L.ldw / 16, Cfg::R, SKS / 2, false))
+        if (fp4 && !make_map(&ms, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, L.blk_scales, 16, L.N_out, K / 256, L.ldw / 16, box_rows, SKS / 2, false))
         {
             return -1;
         }
@@ -187,7 +213,13 @@ C_EXPORT int cuda_decode_program_add_attention(cuda_decode_program* p, const cud
     if (!p || p->finalized || !a) { return -1; }
     if (!a->q || !a->k || !a->v || !a->cos_tab || !a->sin_tab || !a->k_cache || !a->v_cache || !a->pos || !a->out) { return -1; }
     if (a->B != p->M || a->Hkv == 0 || a->H != 4 * a->Hkv || a->head_dim != 128 || a->T_max == 0) { return -1; }
-    if ((a->ldv % 8) != 0 || ((uintptr_t)a->v & 15u) != 0 || ((uintptr_t)a->k_cache & 15u) != 0 || ((uintptr_t)a->v_cache & 15u) != 0) { return -1; }
+    auto misaligned = [](const void* ptr) { return ((uintptr_t)ptr & 15u) != 0; };
+    if ((a->ldq % 8) != 0 || (a->ldk % 8) != 0 || (a->ldv % 8) != 0 || misaligned(a->q) || misaligned(a->k) || misaligned(a->v)
+        || misaligned(a->k_cache) || misaligned(a->v_cache) || misaligned(a->cos_tab) || misaligned(a->sin_tab)
+        || (a->q_norm && misaligned(a->q_norm)) || (a->k_norm && misaligned(a->k_norm)))
+    {
+        return -1;
+    }
     const unsigned int heads = a->B * a->Hkv;
     if (heads > (unsigned)p->sm_count) { return -1; }
     unsigned int S = 1;
@@ -246,6 +278,9 @@ C_EXPORT int cuda_decode_program_finalize(cuda_decode_program* p)
     if (ns > (size_t)Cfg::kMaxStages) { ns = Cfg::kMaxStages; }
     p->smem = Cfg::HEADER_BYTES + ns * stage + u_bytes;
 
+    // Weights that need no per-weight multiplier (FP4 block scales; FP8 with power-of-two scales) take the
+    // CUDA-core k steps, which outrun the legacy tensor-core path at one or two tokens.
+    p->fma = fp4 || !p->any_unscalable;
     // the split of each dequant multiplier into what is applied per weight and what after the sums, and
     // the schedule of each linear phase
     size_t si = 0;
@@ -258,7 +293,7 @@ C_EXPORT int cuda_decode_program_finalize(cuda_decode_program* p)
             if (fp4)
             {
                 ph.seg[j].w_scale = 1.0f;
-                ph.seg[j].post_scale = 65536.0f;    // the FP4 dequantiser leaves 2^-16 in every weight
+                ph.seg[j].post_scale = p->fma ? 1.0f : 65536.0f;    // the tensor-core FP4 dequantiser leaves 2^-16 in every weight
             }
             else if (p->any_unscalable)
             {
@@ -272,11 +307,11 @@ C_EXPORT int cuda_decode_program_finalize(cuda_decode_program* p)
             }
         }
         // whole row blocks per CTA unless that leaves most SMs idle for long; then (row block, k stage) items
-        // in equal runs with the FP32 fix-up, whose extra hop costs about 1.5 us at the end of the phase
+        // in equal runs with the FP32 fix-up, whose store / fence / atomic / reload chains cost about 4 us of a phase
         const double block_bytes = (double)Cfg::R * (double)(fp4 ? ph.K / 2 + ph.K / 16 : ph.K);
         const double rounds = (double)((ph.n_row_blocks + grid - 1) / grid);
         const double t_whole = rounds * block_bytes / 45e9;
-        const double t_split = 1.5e-6 + (double)ph.n_row_blocks * block_bytes / ((double)grid * 42e9);
+        const double t_split = 4.0e-6 + (double)ph.n_row_blocks * block_bytes / ((double)grid * 42e9);
         ph.gran = (t_whole <= t_split) ? ph.n_kstages : 1u;
     }
 
@@ -321,6 +356,7 @@ C_EXPORT int cuda_decode_program_finalize(cuda_decode_program* p)
     h.n_phases = (unsigned)p->phases.size();
     h.M = p->M;
     h.n_stages = (unsigned)ns;
+    h.epoch = 0;
     h.xbuf_bytes = (unsigned)xbuf;
     p->finalized = true;
     {
@@ -335,9 +371,10 @@ C_EXPORT int cuda_decode_program_launch(cuda_decode_program* p, void* stream)
 {
     if (!p || !p->finalized) { return -1; }
     cudaStream_t st = (cudaStream_t)stream;
-    if (p->w_type == DT_FP4) { return launch_program<DT_FP4, false>(p, st); }
-    if (p->w_type == DT_E5M2) { return p->any_unscalable ? launch_program<DT_E5M2, true>(p, st) : launch_program<DT_E5M2, false>(p, st); }
-    return p->any_unscalable ? launch_program<DT_E4M3, true>(p, st) : launch_program<DT_E4M3, false>(p, st);
+    // no per-weight multiplier (FP4 block scales; power-of-two FP8 scales): CUDA-core k steps; else tensor-core k steps
+    if (p->w_type == DT_FP4) { return launch_program<DT_FP4, false, true>(p, st); }
+    if (p->w_type == DT_E5M2) { return p->fma ? launch_program<DT_E5M2, false, true>(p, st) : launch_program<DT_E5M2, true, false>(p, st); }
+    return p->fma ? launch_program<DT_E4M3, false, true>(p, st) : launch_program<DT_E4M3, true, false>(p, st);
 }
 
 C_EXPORT unsigned int cuda_decode_program_phases(const cuda_decode_program* p) { return p ? (unsigned)p->phases.size() : 0u; }
@@ -364,3 +401,4 @@ C_EXPORT void cuda_decode_program_destroy(cuda_decode_program* p)
     cudaFree(p->d_attn_partial);
     delete p;
 }
+

@@ -36,9 +36,10 @@ enum : unsigned int
     XM_SWIGLU = 2      // X = swiglu(x_src, x_src2)
 };
 
-// Tile configuration of the chain: up to 2 tokens, 32 rows x 1024 k per stage (16 k steps of 64 bytes).
+// Tile configuration of the chain: up to 2 tokens, 32 rows x 2048 k per stage (32 k steps of 64 bytes; measured
+// better than twice as many stages of half the size: four k steps per warp and stage keep more loads in flight).
 template <int WT>
-using ChainCfg = GemvCfg<WT, 1, 2, 1, 8, 16, 2, 1>;
+using ChainCfg = GemvCfg<WT, 1, 2, 1, 8, 32, 2, 1>;
 constexpr int kChainMaxTokens = 2;
 constexpr int kChainThreads = 32 * 9;
 
@@ -49,6 +50,8 @@ struct ProgPhase
     unsigned int n_seg, K, n_kstages, n_row_blocks, total_items, gran;
     unsigned int x_mode, out_mode;    // out_mode: 0 BF16, 1 float32, 2 BF16 with the product rounded before beta * Y is added
     unsigned int map_base;            // index of the phase's tensor maps: W0, S0, W1, S1, W2, S2
+    unsigned int paired;              // 1: seg[0] = gate, seg[1] = up with equal N; a row block is 16 rows of each, and the
+                                      // epilogue writes swiglu(gate, up) to seg[0].Y (nothing else is stored)
     unsigned int ldx, ldx2;
     float eps;
     const uint16_t* x_src;
@@ -70,8 +73,9 @@ struct ProgHeader
     float* partials;            // stream-K scratch: [grid][2][tile]
     unsigned int* counters;     // [grid], zero between launches
     unsigned int* status;       // the library's status word
-    unsigned int* sync;         // [0]: phase arrivals of this launch (the last CTA of the launch resets it)
+    unsigned int* sync;         // [0]: phase arrivals of all launches so far
     unsigned int n_phases, M, n_stages;
+    unsigned int epoch;         // launches of this program so far: the arrival counter is never reset, targets move on
     unsigned int xbuf_bytes;    // bytes of the input buffer (2 token rows of the largest K), a multiple of 1024
 };
 
@@ -81,75 +85,252 @@ __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p)
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void tensormap_acquire(const CUtensorMap* m)
-{
-    asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(m) : "memory");
-}
 
 // The input of a LINEAR phase, built by the team in the [64-element slab][token][128 B] layout the k-step
-// code reads (the layout a TMA box of two token rows would have).  Rows beyond M are zero.
+// code reads (the layout a TMA box of two token rows would have).  Rows beyond M are zero.  All global
+// loads are 16-byte loads issued before anything waits on them: what another CTA wrote a moment ago
+// comes from L2, about a microsecond away, and one round trip is all this should cost.
 __device__ __forceinline__ void chain_build_x(const ProgPhase& P, unsigned int M, unsigned char* xb, float* part, unsigned int tid)
 {
     constexpr unsigned int XB = kChainMaxTokens;
-    const unsigned int K = P.K;
+    constexpr unsigned int kVec = 4;    // 16-byte pieces in flight per thread and pass (a pass covers 8192 elements)
+    const unsigned int K = P.K, nvec = K / 8;
     auto slot = [&](unsigned int m, unsigned int k) { return xb + (((size_t)(k >> 6) * XB + m) << 7) + ((k & 63u) << 1); };
     for (unsigned int m = M; m < XB; m++)
     {
-        for (unsigned int i = tid; i < K / 8; i += kTeam) { *reinterpret_cast<uint4*>(slot(m, i * 8)) = make_uint4(0, 0, 0, 0); }
+        for (unsigned int i = tid; i < nvec; i += kTeam) { *reinterpret_cast<uint4*>(slot(m, i * 8)) = make_uint4(0, 0, 0, 0); }
     }
-    if (P.x_mode == XM_COPY)
+    if (P.x_mode == XM_SWIGLU)
     {
         for (unsigned int m = 0; m < M; m++)
         {
-            const uint4* src = reinterpret_cast<const uint4*>(P.x_src + (size_t)m * P.ldx);
-            for (unsigned int i = tid; i < K / 8; i += kTeam) { *reinterpret_cast<uint4*>(slot(m, i * 8)) = __ldcg(src + i); }
-        }
-    }
-    else if (P.x_mode == XM_RMSNORM)
-    {
-        // cccc-cuda/cuda_functions.cu:904-933: thread t sums x[t], x[t + 256], ... with a fused multiply-add each
-        for (unsigned int m = 0; m < M; m++)
-        {
-            const uint16_t* x = P.x_src + (size_t)m * P.ldx;
-            float s = 0.f;
-            for (unsigned int i = tid; i < K; i += kTeam)
+            const uint4* g = reinterpret_cast<const uint4*>(P.x_src + (size_t)m * P.ldx);
+            const uint4* u = reinterpret_cast<const uint4*>(P.x_src2 + (size_t)m * P.ldx2);
+            for (unsigned int base = 0; base < nvec; base += kVec * kTeam)
             {
-                const float v = ld_bf16_cg(x + i);
-                s = __fmaf_rn(v, v, s);
+                uint4 gv[kVec], uv[kVec];
+#pragma unroll
+                for (unsigned int q = 0; q < kVec; q++)
+                {
+                    const unsigned int i = base + tid + q * kTeam;
+                    gv[q] = i < nvec ? __ldcg(g + i) : make_uint4(0, 0, 0, 0);
+                    uv[q] = i < nvec ? __ldcg(u + i) : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (unsigned int q = 0; q < kVec; q++)
+                {
+                    const unsigned int i = base + tid + q * kTeam;
+                    if (i < nvec)
+                    {
+                        float gf[8], uf[8];
+                        unpack8(gv[q], gf);
+                        unpack8(uv[q], uf);
+                        uint32_t o[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e++)
+                        {
+                            o[e] = (uint32_t)bf16_bits(swiglu_one(gf[2 * e], uf[2 * e])) | ((uint32_t)bf16_bits(swiglu_one(gf[2 * e + 1], uf[2 * e + 1])) << 16);
+                        }
+                        *reinterpret_cast<uint4*>(slot(m, i * 8)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
             }
-            part[m * kTeam + tid] = s;
         }
-        team_tree_sum(part, M, tid);
-        for (unsigned int m = 0; m < M; m++)
+        return;
+    }
+    // COPY, and the first half of RMSNORM: the raw rows go into their slots
+    const bool norm = P.x_mode == XM_RMSNORM;
+    for (unsigned int m = 0; m < M; m++)
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(P.x_src + (size_t)m * P.ldx);
+        for (unsigned int base = 0; base < nvec; base += kVec * kTeam)
         {
-            const uint16_t* x = P.x_src + (size_t)m * P.ldx;
-            const float invstd = rms_invstd(part[m * kTeam], K, P.eps);
-            for (unsigned int i = tid; i < K; i += kTeam)
+            uint4 v[kVec];
+#pragma unroll
+            for (unsigned int q = 0; q < kVec; q++)
             {
-                const float sc = P.norm_w ? bf16_bits_to_float(__ldg(P.norm_w + i)) : 1.f;
-                *reinterpret_cast<uint16_t*>(slot(m, i)) = bf16_bits(rms_apply(ld_bf16_cg(x + i), invstd, sc));
+                const unsigned int i = base + tid + q * kTeam;
+                v[q] = i < nvec ? __ldcg(src + i) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (unsigned int q = 0; q < kVec; q++)
+            {
+                const unsigned int i = base + tid + q * kTeam;
+                if (i < nvec) { *reinterpret_cast<uint4*>(slot(m, i * 8)) = v[q]; }
+            }
+        }
+    }
+    if (!norm) { return; }
+    // cccc-cuda/cuda_functions.cu:904-933: thread t sums x[t], x[t + 256], ... with a fused multiply-add each, then
+    // a halving tree; y = bf16((x * invstd) * scale).  The sums read the rows back from shared memory in that
+    // order.  The norm weights of the first pass are fetched before the sums so that their latency hides there.
+    const uint4* wsrc = reinterpret_cast<const uint4*>(P.norm_w);
+    uint4 wv[kVec];
+#pragma unroll
+    for (unsigned int q = 0; q < kVec; q++)
+    {
+        const unsigned int i = tid + q * kTeam;
+        wv[q] = (wsrc != nullptr && i < nvec) ? __ldg(wsrc + i) : make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
+    }
+    team_sync();
+    for (unsigned int m = 0; m < M; m++)
+    {
+        float s = 0.f;
+#pragma unroll 8
+        for (unsigned int i = tid; i < K; i += kTeam)
+        {
+            const float xv = bf16_bits_to_float(*reinterpret_cast<const uint16_t*>(slot(m, i)));
+            s = __fmaf_rn(xv, xv, s);
+        }
+        part[m * kTeam + tid] = s;
+    }
+    team_tree_sum(part, M, tid);
+    for (unsigned int m = 0; m < M; m++)
+    {
+        const float invstd = rms_invstd(part[m * kTeam], K, P.eps);
+        for (unsigned int base = 0; base < nvec; base += kVec * kTeam)
+        {
+#pragma unroll
+            for (unsigned int q = 0; q < kVec; q++)
+            {
+                const unsigned int i = base + tid + q * kTeam;
+                if (i < nvec)
+                {
+                    uint4* px = reinterpret_cast<uint4*>(slot(m, i * 8));
+                    const uint4 w4 = base == 0 ? wv[q] : (wsrc != nullptr ? __ldg(wsrc + i) : wv[q]);
+                    float xf[8], wf[8];
+                    unpack8(*px, xf);
+                    unpack8(w4, wf);
+                    uint32_t o[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++)
+                    {
+                        o[e] = (uint32_t)bf16_bits(rms_apply(xf[2 * e], invstd, wf[2 * e]))
+                            | ((uint32_t)bf16_bits(rms_apply(xf[2 * e + 1], invstd, wf[2 * e + 1])) << 16);
+                    }
+                    *px = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+            }
+        }
+    }
+}
+
+// One segment (consecutive k stages of one row block) of this CTA's run: wait for each stage, run the k
+// steps of this warp, hand the stage back, and leave this warp's partial sums in red[wk][token][row].
+// MODE 0: tensor-core k step (any scale); MODE 1 / 2: CUDA-core k step for one / two tokens.
+template <class Cfg, bool SCALED, int MODE>
+__device__ __forceinline__ bool chain_consume_segment(const unsigned int seg, const unsigned int ks0, const unsigned int K, unsigned int& it,
+    const unsigned int NS, unsigned char* stages, const unsigned int stage_bytes, uint64_t* full_bar, uint64_t* empty_bar,
+    volatile unsigned int* sh_flags, unsigned int* status, const uint32_t xbuf_addr, float* red, const float w_scale, bool ok,
+    const unsigned int wr, const unsigned int wk, const unsigned int lane, const bool paired, const float w_scale_second)
+{
+    constexpr int RT = Cfg::RT, MT = Cfg::MT, WK = Cfg::WK, R = Cfg::R;
+    constexpr unsigned int TILE = R * 8 * MT;
+    constexpr int NT = MODE == 2 ? 2 : 1;
+    constexpr int SPW = (Cfg::SKS + WK - 1) / WK;
+    const unsigned int g = lane >> 2, t = lane & 3;
+    float acc[RT][MT][2][4];
+    float facc[RT][2][NT];
+    if (MODE == 0)
+    {
+#pragma unroll
+        for (int a = 0; a < RT; a++)
+#pragma unroll
+            for (int b = 0; b < MT; b++)
+#pragma unroll
+                for (int c = 0; c < 2; c++)
+#pragma unroll
+                    for (int d = 0; d < 4; d++) { acc[a][b][c][d] = 0.f; }
+    }
+    else
+    {
+#pragma unroll
+        for (int a = 0; a < RT; a++)
+#pragma unroll
+            for (int b = 0; b < 2; b++)
+#pragma unroll
+                for (int c = 0; c < NT; c++) { facc[a][b][c] = 0.f; }
+    }
+    for (unsigned int j = 0; j < seg; j++, it++)
+    {
+        const unsigned int s = it % NS;
+        if (ok && (sh_flags[0] != 0 || !mbar_wait_bounded(full_bar + s, (it / NS) & 1u)))
+        {
+            ok = false;
+            if (sh_flags[0] == 0)
+            {
+                atomicMax(status, (unsigned int)ST_TIMEOUT_FULL);
+                sh_flags[0] = 1;
+            }
+        }
+        if (!ok) { continue; }
+        const unsigned int ks = ks0 + j;
+        const unsigned int kval = min((unsigned int)Cfg::SKE, K - ks * Cfg::SKE);
+        const unsigned int nsteps = kval / Cfg::KSTEP;    // beyond K the TMA fills zeros; skip them
+        const uint32_t st = smem_u32(stages + (size_t)s * stage_bytes);
+        const uint32_t xt = xbuf_addr + ks * (Cfg::XSLABS * Cfg::XB * 128);
+        if (nsteps == (unsigned int)Cfg::SKS)
+        {
+#pragma unroll
+            for (int u = 0; u < SPW; u++)
+            {
+                if (MODE == 0) { gemv_k_step<Cfg, SCALED>(acc, st, xt, wk + u * WK, wr, g, t, w_scale, paired, w_scale_second); }
+                else { gemv_k_step_fma<Cfg, NT>(facc, st, xt, wk + u * WK, wr, g, t, paired); }
+            }
+        }
+        else
+        {
+            for (unsigned int step = wk; step < nsteps; step += WK)
+            {
+                if (MODE == 0) { gemv_k_step<Cfg, SCALED>(acc, st, xt, step, wr, g, t, w_scale, paired, w_scale_second); }
+                else { gemv_k_step_fma<Cfg, NT>(facc, st, xt, step, wr, g, t, paired); }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(empty_bar + s); }
+    }
+    float* myred = red + wk * TILE;
+    if (MODE == 0)
+    {
+#pragma unroll
+        for (int rt = 0; rt < RT; rt++)
+        {
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++)
+            {
+                const unsigned int row = (wr * RT + rt) * 16 + g;
+                const unsigned int tok = mt * 8 + 2 * t;
+                myred[tok * R + row] = acc[rt][mt][0][0] + acc[rt][mt][1][0];
+                myred[(tok + 1) * R + row] = acc[rt][mt][0][1] + acc[rt][mt][1][1];
+                myred[tok * R + row + 8] = acc[rt][mt][0][2] + acc[rt][mt][1][2];
+                myred[(tok + 1) * R + row + 8] = acc[rt][mt][0][3] + acc[rt][mt][1][3];
             }
         }
     }
     else
     {
-        for (unsigned int m = 0; m < M; m++)
-        {
-            const uint16_t* g = P.x_src + (size_t)m * P.ldx;
-            const uint16_t* u = P.x_src2 + (size_t)m * P.ldx2;
-            for (unsigned int i = tid; i < K; i += kTeam)
-            {
-                *reinterpret_cast<uint16_t*>(slot(m, i)) = bf16_bits(swiglu_one(ld_bf16_cg(g + i), ld_bf16_cg(u + i)));
-            }
-        }
+        // the four lanes of a row hold the four quarters of each 64-byte k step: add them in a fixed order
+#pragma unroll
+        for (int rt = 0; rt < RT; rt++)
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+#pragma unroll
+                for (int m = 0; m < NT; m++)
+                {
+                    float v = facc[rt][h][m];
+                    v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+                    v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
+                    if (t == 0) { myred[m * R + (wr * RT + rt) * 16 + h * 8 + g] = v; }
+                }
     }
+    return ok;
 }
 
-template <int WT, bool SCALED, int G>
+template <int WT, bool SCALED, int G, bool FMA>
 __global__ void __launch_bounds__(kChainThreads, 1) decode_program_kernel(const ProgHeader hd)
 {
     using Cfg = ChainCfg<WT>;
-    constexpr int RT = Cfg::RT, MT = Cfg::MT, WK = Cfg::WK, R = Cfg::R, HD = 128;
+    constexpr int MT = Cfg::MT, WK = Cfg::WK, R = Cfg::R, HD = 128;
     constexpr int kConsumerWarps = Cfg::NCW;
     constexpr unsigned int STAGE = ((Cfg::W_BYTES + Cfg::S_BYTES + 1023) / 1024) * 1024;
     constexpr unsigned int TILE = R * 8 * MT;
@@ -194,12 +375,8 @@ __global__ void __launch_bounds__(kChainThreads, 1) decode_program_kernel(const 
             if (P.kind != PH_LINEAR) { continue; }
             const ItemRange items = cta_items(cta, grid, P.total_items, P.gran);
             if (items.end == items.beg) { continue; }
+            // the tensor maps were written by the host before the launch: no proxy fence is needed to use them
             const CUtensorMap* maps = hd.maps + P.map_base;
-            for (unsigned int j = 0; j < P.n_seg; j++)
-            {
-                tensormap_acquire(maps + 2 * j);
-                if (WT == DT_FP4) { tensormap_acquire(maps + 2 * j + 1); }
-            }
             const unsigned int rb1 = P.seg[1].rb_begin, rb2 = P.seg[2].rb_begin, nk = P.n_kstages;
             for (unsigned int item = items.beg; item < items.end; item++, it++)
             {
@@ -212,15 +389,31 @@ __global__ void __launch_bounds__(kChainThreads, 1) decode_program_kernel(const 
                     break;
                 }
                 const unsigned int rb = item / nk, ks = item % nk;
-                const unsigned int j = (rb >= rb1 ? 1u : 0u) + (rb >= rb2 ? 1u : 0u);
-                const unsigned int rbb = j == 0 ? 0u : (j == 1 ? rb1 : rb2);
-                const int row0 = (int)((rb - rbb) * R);
                 unsigned char* st = stages + (size_t)s * STAGE;
                 mbar_expect_tx(full_bar + s, Cfg::W_BYTES + Cfg::S_BYTES);
-                tma_load_3d_hint(st, maps + 2 * j, 0, row0, (int)(ks * Cfg::SKS), full_bar + s, pol_stream);
-                if (WT == DT_FP4)
+                if (P.paired)
                 {
-                    tma_load_3d_hint(st + Cfg::W_BYTES, maps + 2 * j + 1, 0, row0, (int)(ks * (Cfg::SKS / 2)), full_bar + s, pol_stream);
+                    // 16 rows of the gate matrix, then the same 16 rows of the up matrix
+                    const int row0 = (int)(rb * 16);
+                    tma_load_3d_hint(st, maps, 0, row0, (int)(ks * Cfg::SKS), full_bar + s, pol_stream);
+                    tma_load_3d_hint(st + Cfg::W_BYTES / 2, maps + 2, 0, row0, (int)(ks * Cfg::SKS), full_bar + s, pol_stream);
+                    if (WT == DT_FP4)
+                    {
+                        tma_load_3d_hint(st + Cfg::W_BYTES, maps + 1, 0, row0, (int)(ks * (Cfg::SKS / 2)), full_bar + s, pol_stream);
+                        tma_load_3d_hint(st + Cfg::W_BYTES + Cfg::S_BYTES / 2, maps + 3, 0, row0, (int)(ks * (Cfg::SKS / 2)), full_bar + s,
+                            pol_stream);
+                    }
+                }
+                else
+                {
+                    const unsigned int j = (rb >= rb1 ? 1u : 0u) + (rb >= rb2 ? 1u : 0u);
+                    const unsigned int rbb = j == 0 ? 0u : (j == 1 ? rb1 : rb2);
+                    const int row0 = (int)((rb - rbb) * R);
+                    tma_load_3d_hint(st, maps + 2 * j, 0, row0, (int)(ks * Cfg::SKS), full_bar + s, pol_stream);
+                    if (WT == DT_FP4)
+                    {
+                        tma_load_3d_hint(st + Cfg::W_BYTES, maps + 2 * j + 1, 0, row0, (int)(ks * (Cfg::SKS / 2)), full_bar + s, pol_stream);
+                    }
                 }
                 mbar_arrive(full_bar + s);
             }
@@ -241,7 +434,6 @@ __global__ void __launch_bounds__(kChainThreads, 1) decode_program_kernel(const 
     }
 
     // =========================== consumer team ===========================
-    const unsigned int g = lane >> 2, t = lane & 3;
     const unsigned int wr = warp / WK, wk = warp % WK;
     const unsigned int ctid = threadIdx.x;
     bool ok = true;
@@ -254,10 +446,10 @@ __global__ void __launch_bounds__(kChainThreads, 1) decode_program_kernel(const 
             // every CTA has finished the previous phase: its outputs are this phase's inputs
             if (ctid == 0 && ok)
             {
-                const unsigned int target = ph * grid;
+                const unsigned int target = (hd.epoch * hd.n_phases + ph) * grid;    // wraps with the counter
                 const unsigned long long t0 = global_timer_ns();
                 unsigned int spins = 0;
-                while (ld_acquire_gpu(hd.sync) < target)
+                while ((int)(ld_acquire_gpu(hd.sync) - target) < 0)
                 {
                     if ((++spins & 0x3Fu) == 0
                         && (sh_flags[0] != 0 || *reinterpret_cast<volatile unsigned int*>(hd.status) != 0 || global_timer_ns() - t0 > kWaitLimitNs))
@@ -289,70 +481,38 @@ __global__ void __launch_bounds__(kChainThreads, 1) decode_program_kernel(const 
                 const unsigned int ks0 = item0 % P.n_kstages;
                 const unsigned int seg = min(P.n_kstages - ks0, n_items - done);
                 const bool first_segment = (done == 0);
-                const unsigned int lj = (rb >= P.seg[1].rb_begin ? 1u : 0u) + (rb >= P.seg[2].rb_begin ? 1u : 0u);
+                const unsigned int lj = P.paired ? 0u : (rb >= P.seg[1].rb_begin ? 1u : 0u) + (rb >= P.seg[2].rb_begin ? 1u : 0u);
                 const GemvSeg& L = P.seg[lj];
                 const float w_scale = L.w_scale;
-                float acc[RT][MT][2][4];
-#pragma unroll
-                for (int a = 0; a < RT; a++)
-#pragma unroll
-                    for (int b = 0; b < MT; b++)
-#pragma unroll
-                        for (int c = 0; c < 2; c++)
-#pragma unroll
-                            for (int d = 0; d < 4; d++) { acc[a][b][c][d] = 0.f; }
-                for (unsigned int j = 0; j < seg; j++, it++, done++)
+                if (FMA)
                 {
-                    const unsigned int s = it % NS;
-                    if (ok && (sh_flags[0] != 0 || !mbar_wait_bounded(full_bar + s, (it / NS) & 1u)))
-                    {
-                        ok = false;
-                        if (sh_flags[0] == 0)
-                        {
-                            atomicMax(hd.status, (unsigned int)ST_TIMEOUT_FULL);
-                            sh_flags[0] = 1;
-                        }
-                    }
-                    if (!ok) { continue; }
-                    const unsigned int ks = ks0 + j;
-                    const unsigned int kval = min((unsigned int)Cfg::SKE, P.K - ks * Cfg::SKE);
-                    const unsigned int nsteps = kval / Cfg::KSTEP;
-                    const uint32_t st = smem_u32(stages + (size_t)s * STAGE);
-                    const uint32_t xt = smem_u32(xbuf) + ks * (Cfg::XSLABS * Cfg::XB * 128);
-                    constexpr int SPW = (Cfg::SKS + WK - 1) / WK;
-                    if (nsteps == (unsigned int)Cfg::SKS)
-                    {
-#pragma unroll
-                        for (int u = 0; u < SPW; u++) { gemv_k_step<Cfg, SCALED>(acc, st, xt, wk + u * WK, wr, g, t, w_scale); }
-                    }
-                    else
-                    {
-                        for (unsigned int step = wk; step < nsteps; step += WK) { gemv_k_step<Cfg, SCALED>(acc, st, xt, step, wr, g, t, w_scale); }
-                    }
-                    __syncwarp();
-                    if (lane == 0) { mbar_arrive(empty_bar + s); }
+                    ok = hd.M == 1 ? chain_consume_segment<Cfg, SCALED, 1>(seg, ks0, P.K, it, NS, stages, STAGE, full_bar, empty_bar, sh_flags,
+                                         hd.status, smem_u32(xbuf), red, w_scale, ok, wr, wk, lane, P.paired != 0, P.seg[1].w_scale)
+                                   : chain_consume_segment<Cfg, SCALED, 2>(seg, ks0, P.K, it, NS, stages, STAGE, full_bar, empty_bar, sh_flags,
+                                         hd.status, smem_u32(xbuf), red, w_scale, ok, wr, wk, lane, P.paired != 0, P.seg[1].w_scale);
                 }
-
-                // ---- end of the segment: combine the k-split warps, then write or hand over ----
-                float* myred = red + wk * TILE;
-#pragma unroll
-                for (int rt = 0; rt < RT; rt++)
+                else
                 {
-#pragma unroll
-                    for (int mt = 0; mt < MT; mt++)
-                    {
-                        const unsigned int row = (wr * RT + rt) * 16 + g;
-                        const unsigned int tok = mt * 8 + 2 * t;
-                        myred[tok * R + row] = acc[rt][mt][0][0] + acc[rt][mt][1][0];
-                        myred[(tok + 1) * R + row] = acc[rt][mt][0][1] + acc[rt][mt][1][1];
-                        myred[tok * R + row + 8] = acc[rt][mt][0][2] + acc[rt][mt][1][2];
-                        myred[(tok + 1) * R + row + 8] = acc[rt][mt][0][3] + acc[rt][mt][1][3];
-                    }
+                    ok = chain_consume_segment<Cfg, SCALED, 0>(seg, ks0, P.K, it, NS, stages, STAGE, full_bar, empty_bar, sh_flags, hd.status,
+                        smem_u32(xbuf), red, w_scale, ok, wr, wk, lane, P.paired != 0, P.seg[1].w_scale);
                 }
+                done += seg;
                 team_sync();
-                const unsigned int n_out = hd.M * R;
+                const unsigned int n_out = P.paired ? hd.M * 16u : hd.M * R;
                 const bool full = (ks0 == 0 && seg == P.n_kstages);
-                const unsigned int n0 = (rb - L.rb_begin) * R;
+                const unsigned int n0 = P.paired ? rb * 16u : (rb - L.rb_begin) * R;
+                // paired: entry e = (token m, row r < 16) -> gate sum at [m][r], up sum at [m][r + 16] of the tile
+                auto tile_index = [&](unsigned int e) { return P.paired ? (e >> 4) * R + (e & 15u) : e; };
+                auto store_pair = [&](unsigned int e, float gsum, float usum) {
+                    const unsigned int m = e >> 4, n = n0 + (e & 15u);
+                    if (n < L.N)
+                    {
+                        const GemvSeg& U = P.seg[1];
+                        const float gv = bf16_round(L.alpha * (gsum * L.post_scale));
+                        const float uv = bf16_round(U.alpha * (usum * U.post_scale));
+                        L.Y[(long long)m * L.ldy_m + (long long)n * L.ldy_n] = bf16_bits(swiglu_one(gv, uv));
+                    }
+                };
                 auto store_out = [&](unsigned int e, float v) {
                     const unsigned int m = e / R, r = e - m * R;
                     const unsigned int n = n0 + r;
@@ -380,10 +540,17 @@ __global__ void __launch_bounds__(kChainThreads, 1) decode_program_kernel(const 
                     {
                         for (unsigned int e = ctid; e < n_out; e += kTeam)
                         {
-                            float v = 0.f;
+                            const unsigned int ti = tile_index(e);
+                            float v = 0.f, v2 = 0.f;
 #pragma unroll
-                            for (int w = 0; w < WK; w++) { v += red[w * TILE + e]; }
-                            store_out(e, v);
+                            for (int w = 0; w < WK; w++) { v += red[w * TILE + ti]; }
+                            if (P.paired)
+                            {
+#pragma unroll
+                                for (int w = 0; w < WK; w++) { v2 += red[w * TILE + ti + 16]; }
+                                store_pair(e, v, v2);
+                            }
+                            else { store_out(e, v); }
                         }
                     }
                 }
@@ -392,7 +559,7 @@ __global__ void __launch_bounds__(kChainThreads, 1) decode_program_kernel(const 
                     float* mine = hd.partials + ((size_t)cta * 2 + (first_segment ? 0 : 1)) * TILE;
                     if (ok)
                     {
-                        for (unsigned int e = ctid; e < n_out; e += kTeam)
+                        for (unsigned int e = ctid; e < hd.M * R; e += kTeam)
                         {
                             float v = 0.f;
 #pragma unroll
@@ -420,13 +587,17 @@ __global__ void __launch_bounds__(kChainThreads, 1) decode_program_kernel(const 
                     {
                         for (unsigned int e = ctid; e < n_out; e += kTeam)
                         {
-                            float v = 0.f;
+                            const unsigned int ti = tile_index(e);
+                            float v = 0.f, v2 = 0.f;
                             for (unsigned int c = c_first; c <= c_last; c++)
                             {
                                 const unsigned int slot = (cta_items(c, grid, P.total_items, P.gran).beg / P.n_kstages == rb) ? 0u : 1u;
-                                v += __ldcg(hd.partials + ((size_t)c * 2 + slot) * TILE + e);
+                                const float* part = hd.partials + ((size_t)c * 2 + slot) * TILE;
+                                v += __ldcg(part + ti);
+                                if (P.paired) { v2 += __ldcg(part + ti + 16); }
                             }
-                            store_out(e, v);
+                            if (P.paired) { store_pair(e, v, v2); }
+                            else { store_out(e, v); }
                         }
                         if (ctid == 0) { hd.counters[c_first] = 0; }
                     }
@@ -453,28 +624,27 @@ __global__ void __launch_bounds__(kChainThreads, 1) decode_program_kernel(const 
                 const bool owner = pos >= t0 && pos < t1;
                 if (P.kind == PH_ATTN_SCORES)
                 {
-                    attn_prologue<G, HD>(A, sm, b, kvh, pos, owner, ctid);
-                    attn_scores<G, HD>(A, sm, b, kvh, t0, t1, ts_cap, pos, owner, ctid);
+                    attn_scores<G, HD, 4>(A, sm, b, kvh, t0, t1, ts_cap, pos, owner, ctid);    // (runs the prologue too; 4 passes in flight: 168 registers)
                     if (ctid < 2 * G) { __stcg(P.attn_stats + (size_t)cta * 2 * G + ctid, sm.ml[ctid]); }
                 }
                 else
                 {
-                    if (ctid < G)
-                    {
-                        const float* st = P.attn_stats + (size_t)bh * S * 2 * G;
-                        float gmax = -INFINITY;
-                        for (unsigned int r = 0; r < S; r++) { gmax = fmaxf(gmax, __ldcg(st + r * 2 * G + 2 * ctid)); }
-                        float Lsum = 0.f;
-                        for (unsigned int r = 0; r < S; r++)
+                    attn_pv<G, HD>(A, sm, b, kvh, t0, t1, ts_cap, owner ? pos : 0xFFFFFFFFu, ctid, [&]() {
+                        if (ctid < G)
                         {
-                            const float l = __ldcg(st + r * 2 * G + 2 * ctid + 1);
-                            if (l > 0.f) { Lsum += l * __expf(__ldcg(st + r * 2 * G + 2 * ctid) - gmax); }
+                            const float* st = P.attn_stats + (size_t)bh * S * 2 * G;
+                            float gmax = -INFINITY;
+                            for (unsigned int r = 0; r < S; r++) { gmax = fmaxf(gmax, __ldcg(st + r * 2 * G + 2 * ctid)); }
+                            float Lsum = 0.f;
+                            for (unsigned int r = 0; r < S; r++)
+                            {
+                                const float l = __ldcg(st + r * 2 * G + 2 * ctid + 1);
+                                if (l > 0.f) { Lsum += l * __expf(__ldcg(st + r * 2 * G + 2 * ctid) - gmax); }
+                            }
+                            sm.gl[2 * ctid] = gmax;
+                            sm.gl[2 * ctid + 1] = 1.0f / Lsum;
                         }
-                        sm.gl[2 * ctid] = gmax;
-                        sm.gl[2 * ctid + 1] = 1.0f / Lsum;
-                    }
-                    team_sync();
-                    attn_pv<G, HD>(A, sm, b, kvh, t0, t1, ts_cap, owner ? pos : 0xFFFFFFFFu, ctid);
+                    });
                     float* mine = P.attn_partial + (size_t)cta * G * HD;
                     for (unsigned int i = ctid; i < G * HD; i += kTeam) { __stcg(mine + i, sm.opart[i]); }
                     team_sync();
@@ -505,12 +675,8 @@ __global__ void __launch_bounds__(kChainThreads, 1) decode_program_kernel(const 
 
         // ---- this CTA has finished the phase ----
         team_sync();
-        if (ctid == 0)
-        {
-            __threadfence();
-            const unsigned int old = atomicAdd(hd.sync, 1u);
-            if (old == hd.n_phases * grid - 1) { *hd.sync = 0; }    // the very last arrival of the launch: ready for the next one
-        }
+        // (the barrier above orders the team's writes before thread 0's release, which is cumulative over them)
+        if (ctid == 0) { asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(hd.sync) : "memory"); }
     }
 }
 

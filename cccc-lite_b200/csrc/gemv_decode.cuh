@@ -367,9 +367,24 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
 // its RT row tiles, load its activation fragments, issue the MMAs.  st: shared-memory address of the
 // stage's weights (scales behind them); xt: address of the activation slabs of this stage, laid out
 // [128-byte slab][token][128 B]; wr: this warp's position along the rows; g, t: lane >> 2, lane & 3.
+// paired: the stage holds two 16-row boxes of two different matrices one after the other (rows 0-15 and
+// 16-31 of the block) instead of one 32-row box, each laid out [k step][16 rows][64 B].
+template <class Cfg>
+__device__ __forceinline__ uint32_t stage_row_addr(const uint32_t st, const unsigned int step, const unsigned int row, const bool paired)
+{
+    return paired ? st + (row >> 4) * (Cfg::SKS * 16 * 64) + (step * 16 + (row & 15u)) * 64 : st + (step * Cfg::R + row) * 64;
+}
+template <class Cfg>
+__device__ __forceinline__ uint32_t stage_scale_addr(const uint32_t st, const unsigned int step, const unsigned int row, const bool paired)
+{
+    return paired ? st + Cfg::W_BYTES + (row >> 4) * ((Cfg::SKS / 2) * 16 * 16) + ((step >> 1) * 16 + (row & 15u)) * 16 + (step & 1u) * 8
+                  : st + Cfg::W_BYTES + ((step >> 1) * Cfg::R + row) * 16 + (step & 1u) * 8;
+}
+
 template <class Cfg, bool SCALED>
 __device__ __forceinline__ void gemv_k_step(float (&acc)[Cfg::RT][Cfg::MT][2][4], const uint32_t st, const uint32_t xt,
-    const unsigned int step, const unsigned int wr, const unsigned int g, const unsigned int t, const float w_scale)
+    const unsigned int step, const unsigned int wr, const unsigned int g, const unsigned int t, const float w_scale,
+    const bool paired = false, const float w_scale_second = 1.0f)
 {
     constexpr int WT = Cfg::WT, MT = Cfg::MT, RT = Cfg::RT, R = Cfg::R;
     constexpr int AREGS = (WT == DT_FP4) ? 16 : 8;    // bf16x2 registers per weight row per k step
@@ -382,13 +397,12 @@ __device__ __forceinline__ void gemv_k_step(float (&acc)[Cfg::RT][Cfg::MT][2][4]
         for (int h = 0; h < 2; h++)
         {
             const unsigned int row = (wr * RT + rt) * 16 + h * 8 + g;
-            const uint4 wv = lds128(st + (step * R + row) * 64 + t * 16);
+            const uint4 wv = lds128(stage_row_addr<Cfg>(st, step, row, paired) + t * 16);
             const uint32_t w[4] = { wv.x, wv.y, wv.z, wv.w };
             if (WT == DT_FP4)
             {
                 uint32_t m01[2];
-                fp4_block_multipliers(
-                    lds_u16(st + Cfg::W_BYTES + ((step >> 1) * R + row) * 16 + (step & 1u) * 8 + t * 2), m01[0], m01[1]);
+                fp4_block_multipliers(lds_u16(stage_scale_addr<Cfg>(st, step, row, paired) + t * 2), m01[0], m01[1]);
 #pragma unroll
                 for (int i = 0; i < 4; i++)
                 {
@@ -403,7 +417,7 @@ __device__ __forceinline__ void gemv_k_step(float (&acc)[Cfg::RT][Cfg::MT][2][4]
 #pragma unroll
                 for (int i = 0; i < 4; i++)
                 {
-                    dequant_fp8x4<WT, SCALED>(w[i], w_scale, A[rt][h][(2 * i) % AREGS], A[rt][h][(2 * i + 1) % AREGS]);
+                    dequant_fp8x4<WT, SCALED>(w[i], (paired && rt == 1) ? w_scale_second : w_scale, A[rt][h][(2 * i) % AREGS], A[rt][h][(2 * i + 1) % AREGS]);
                 }
             }
         }
@@ -459,6 +473,104 @@ __device__ __forceinline__ void gemv_k_step(float (&acc)[Cfg::RT][Cfg::MT][2][4]
                 {
                     mma_bf16_16816(acc[rt][mt][q & 1], A[rt][0][2 * q], A[rt][1][2 * q], A[rt][0][2 * q + 1],
                         A[rt][1][2 * q + 1], B[2 * q], B[2 * q + 1]);
+                }
+            }
+        }
+    }
+}
+
+// The same k step on the CUDA cores, for one or two tokens.  On B200 the legacy mma.sync path issues
+// one m16n8k16 per ~8 clocks per SM whatever the token count, which caps a GEMV at ~32 weight bytes
+// per clock per SM; with one or two tokens plain FP32 fused multiply-adds do better: every lane
+// widens the 16 bytes it loaded to FP32 (exact: the decoded weight IS the BF16 operand when no
+// per-weight multiplier applies, and table * block scale for FP4) and accumulates w * x per token in
+// FP32, which is what the tensor core does with the BF16 operands.  Only for weights that need no
+// per-weight multiplier (per-tensor scale a power of two, folded in after the sums, or FP4 block
+// scales).  acc[rt][h][m]: row (rt*16 + h*8 + g) of this warp's rows, token m, this lane's k slice.
+template <class Cfg, int NT>
+__device__ __forceinline__ void gemv_k_step_fma(float (&acc)[Cfg::RT][2][NT], const uint32_t st, const uint32_t xt,
+    const unsigned int step, const unsigned int wr, const unsigned int g, const unsigned int t, const bool paired = false)
+{
+    constexpr int WT = Cfg::WT, RT = Cfg::RT, R = Cfg::R;
+    constexpr int NX = (WT == DT_FP4) ? 32 : 16;    // activations per lane and k step
+    static_assert(!Cfg::XSWZ, "the CUDA-core k step reads the unswizzled two-token layout");
+    float xf[NT][NX];
+#pragma unroll
+    for (int m = 0; m < NT; m++)
+    {
+        const uint32_t xrow = (WT == DT_FP4) ? xt + ((step * 2 + (t >> 1)) * Cfg::XB + m) * 128 + (t & 1u) * 64
+                                             : xt + (step * Cfg::XB + m) * 128 + t * 32;
+#pragma unroll
+        for (int c = 0; c < NX / 8; c++)
+        {
+            const uint4 v = lds128(xrow + c * 16);
+            const uint32_t w[4] = { v.x, v.y, v.z, v.w };
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+            {
+                xf[m][c * 8 + 2 * i] = __uint_as_float(w[i] << 16);
+                xf[m][c * 8 + 2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+            }
+        }
+    }
+#pragma unroll
+    for (int rt = 0; rt < RT; rt++)
+    {
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+        {
+            const unsigned int row = (wr * RT + rt) * 16 + h * 8 + g;
+            const uint4 wv = lds128(stage_row_addr<Cfg>(st, step, row, paired) + t * 16);
+            const uint32_t w[4] = { wv.x, wv.y, wv.z, wv.w };
+            if (WT == DT_FP4)
+            {
+                // two blocks of 16 nibbles, one E4M3 multiplier each; table * multiplier is exact in FP16
+                const uint32_t two = lds_u16(stage_scale_addr<Cfg>(st, step, row, paired) + t * 2);
+                uint32_t s2[2];
+                asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(s2[0]) : "h"((uint16_t)((two & 0xFFu) * 0x0101u)));
+                asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(s2[1]) : "h"((uint16_t)((two >> 8) * 0x0101u)));
+#pragma unroll
+                for (int i = 0; i < 16; i++)
+                {
+                    const uint16_t b = (uint16_t)((w[i >> 2] >> (8 * (i & 3))) & 0xFFu);
+                    uint32_t h2, p2;
+                    asm("{\n\t.reg .b8 lo, hi;\n\tmov.b16 {lo, hi}, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, lo;\n\t}" : "=r"(h2) : "h"(b));
+                    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(p2) : "r"(h2), "r"(s2[i >> 3]));
+                    const float2 f = half2_bits_to_float2(p2);
+#pragma unroll
+                    for (int m = 0; m < NT; m++)
+                    {
+                        acc[rt][h][m] = __fmaf_rn(f.x, xf[m][2 * i], acc[rt][h][m]);
+                        acc[rt][h][m] = __fmaf_rn(f.y, xf[m][2 * i + 1], acc[rt][h][m]);
+                    }
+                }
+            }
+            else
+            {
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                {
+                    uint32_t h01, h23;
+                    if (WT == DT_E5M2)
+                    {
+                        h01 = prmt(w[i], 0u, 0x1404u);
+                        h23 = prmt(w[i], 0u, 0x3424u);
+                    }
+                    else
+                    {
+                        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h01) : "h"((uint16_t)(w[i] & 0xFFFFu)));
+                        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h23) : "h"((uint16_t)(w[i] >> 16)));
+                    }
+                    const float2 f01 = half2_bits_to_float2(h01);
+                    const float2 f23 = half2_bits_to_float2(h23);
+#pragma unroll
+                    for (int m = 0; m < NT; m++)
+                    {
+                        acc[rt][h][m] = __fmaf_rn(f01.x, xf[m][4 * i], acc[rt][h][m]);
+                        acc[rt][h][m] = __fmaf_rn(f01.y, xf[m][4 * i + 1], acc[rt][h][m]);
+                        acc[rt][h][m] = __fmaf_rn(f23.x, xf[m][4 * i + 2], acc[rt][h][m]);
+                        acc[rt][h][m] = __fmaf_rn(f23.y, xf[m][4 * i + 3], acc[rt][h][m]);
+                    }
                 }
             }
         }

@@ -203,12 +203,14 @@ class DecodeModel:
             W, S, inv = L["o"]
             go = C.make_group([dict(W=W, S=S, inv=inv, N=c.hidden, Y=self.x, beta=1.0)], self.q_loc)
             ok(prog.add_linears(go, self.q_loc, self.att, mode=C.X_COPY, flags=RES), "o")
-            ok(prog.add_linears(P["gu"], c.hidden, self.x, mode=C.X_RMSNORM, norm_weight=L["ffn_norm"], eps=c.eps), "gate+up")
+            # gate and up as one paired phase whose epilogue writes swiglu(gate, up) straight into self.h
+            (Wg, Sg, ig), (Wu, Su, iu) = L["gate"], L["up"]
+            gp = C.make_group([dict(W=Wg, S=Sg, inv=ig, N=self.ffn_loc, Y=self.h), dict(W=Wu, S=Su, inv=iu, N=self.ffn_loc, Y=self.h)], c.hidden)
+            ok(prog.add_linears(gp, c.hidden, self.x, mode=C.X_RMSNORM, norm_weight=L["ffn_norm"], eps=c.eps, flags=16), "gate+up")
             W, S, inv = L["down"]
             gd = C.make_group([dict(W=W, S=S, inv=inv, N=c.hidden, Y=self.x, beta=1.0)], self.ffn_loc)
-            ok(prog.add_linears(gd, self.ffn_loc, self.gu, mode=C.X_SWIGLU, ldx=2 * self.ffn_loc, x2=self.gu.data_ptr() + self.ffn_loc * 2,
-                                ldx2=2 * self.ffn_loc, flags=RES), "down")
-            groups += [go, gd]
+            ok(prog.add_linears(gd, self.ffn_loc, self.h, mode=C.X_COPY, flags=RES), "down")
+            groups += [go, gp, gd]
         W, S, inv = self.w["lm_head"]
         gh = C.make_group([dict(W=W, S=S, inv=inv, N=self.vocab_loc, Y=self.logits)], c.hidden)
         ok(prog.add_linears(gh, c.hidden, self.x, mode=C.X_RMSNORM, norm_weight=self.w["final_norm"], eps=c.eps), "lm_head")

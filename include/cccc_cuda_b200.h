@@ -269,15 +269,21 @@ C_EXPORT int cuda_attn_decode_bf16(const cuda_attn_decode* a, void* stream, unsi
  * same order wherever the schedules coincide).
  *   create        : w_type 4, 5 or 6 for every linear of the program; M_tokens 1 or 2.
  *   add_linears   : 1-3 linears that share their input (fields as cuda_gemm_wq_bf16_group).  `in` says
- *                   how the input is made: mode 0 = x itself ([M][ldx] BF16, 16-byte aligned, ldx % 8 == 0);
- *                   mode 1 = RMSNorm of x with norm_weight (NULL = 1) and epsilon, as cuda_rms_norm_bf16;
- *                   mode 2 = SwiGLU of x (gate) and x2 (up), as cuda_swiglu_bf16.  flags bit 2 (float32
- *                   output) and bit 3 (residual epilogue) as cuda_gemm_wq_bf16.  K % 64 == 0 (FP4: 256),
- *                   weights 16-byte aligned with ldw % 16 == 0 (FP4: block scales, ldw % 256 == 0).
+ *                   how the input is made: mode 0 = x itself; mode 1 = RMSNorm of x with norm_weight (NULL
+ *                   = 1) and epsilon, as cuda_rms_norm_bf16; mode 2 = SwiGLU of x (gate) and x2 (up), as
+ *                   cuda_swiglu_bf16.  x, x2: [M][ld] BF16, 16-byte aligned, ld % 8 == 0.  flags bit 2
+ *                   (float32 output) and bit 3 (residual epilogue) as cuda_gemm_wq_bf16; bit 4: the two
+ *                   linears are the gate and up projections of a gated MLP (equal N_out, a multiple of 16,
+ *                   beta 0): only swiglu(bf16(gate), bf16(up)) is stored, as cuda_swiglu_bf16 would give
+ *                   it, at linears[0].Y (linears[1].Y is not used).  K % 64 == 0 (FP4:
+ *                   256), K <= 16384, weights 16-byte aligned with ldw % 16 == 0 (FP4: block scales, ldw %
+ *                   256 == 0).
  *   add_attention : as cuda_attn_decode_bf16 with B = M_tokens, head_dim 128 and H = 4 Hkv.
  *   finalize      : uploads the program and allocates its scratch (the only step that allocates; make it
  *                   outside any stream capture).  Buffers named in the program must stay alive.
- *   launch        : one cooperative kernel on `stream`.  Launches of one program must not overlap.
+ *   launch        : one cooperative kernel on `stream`.  Launches of one program must not overlap, and each
+ *                   carries its sequence number as an argument: issue them directly, do not replay one
+ *                   from a captured graph.
  * Phases follow each other in the order added; each one sees everything the earlier ones wrote.
  * Every function returns 0, 1 (CUDA error) or -1 (an argument the program kernel does not take: use the
  * separate entry points for that step). */

@@ -165,6 +165,43 @@ def test_prefill_kernels_dequantise_bit_exactly(wt, variant, M):
         run_onehot(wt, W, S, inv, D, N, K, M, positions, flags=c.flag_prefill_variant(variant))
 
 
+@pytest.mark.parametrize("wt,inv", [(O.FP8_E5M2, 1.0), (O.FP8_E5M2, 0.25), (O.FP8_E5M2, 0.37), (O.FP8_E4M3, 1.0), (O.FP8_E4M3, 0.37),
+                                    (O.FP4_E2M1, 1.0)])
+@pytest.mark.parametrize("M", [1, 2])
+def test_decode_program_dequantises_bit_exactly(wt, inv, M):
+    """The persistent decode-program kernel has k steps of its own (CUDA-core FMAs for weights without a
+    per-weight multiplier, tensor-core steps otherwise): the same one-hot check, every k position."""
+    import torch
+
+    c = capi()
+    N, K = (508, 512) if wt == O.FP4_E2M1 else (512, 512)
+    if wt == O.FP4_E2M1:
+        W, S = fp4_matrix(N, K)
+    else:
+        W, S = fp8_matrix(wt, N, K), None
+    D = expected_bits(wt, W, S, inv, N, K)
+    dW = to_dev(W.reshape(-1))
+    dS = to_dev(S.reshape(-1)) if S is not None else None
+    dD = torch.from_numpy(D.view(np.int16)).cuda()
+    X = torch.zeros(M, K, dtype=torch.int16, device="cuda")
+    Y = torch.zeros(M, N, dtype=torch.int16, device="cuda")
+    grp = c.make_group([dict(W=dW, S=dS, inv=inv, N=N, Y=Y)], K)
+    prog = c.DecodeProgram(wt, M)
+    assert prog.add_linears(grp, K, X) == 0 and prog.finalize() == 0
+    for ks in all_positions(K, M):
+        kt = torch.from_numpy(np.asarray(ks, np.int64)).cuda()
+        X.zero_()
+        X[torch.arange(M, device="cuda"), kt] = ONE
+        Y.fill_(0x7FC0)
+        assert prog.launch() == 0
+        want = dD[:, kt].t().contiguous()
+        g = torch.where(Y == -32768, torch.zeros_like(Y), Y)
+        w = torch.where(want == -32768, torch.zeros_like(want), want)
+        assert torch.equal(g, w), (wt, inv, M, ks.tolist())
+    assert c.check_error("program one-hot") == 0
+    prog.close()
+
+
 def c_plan(wt, W, S, N, M, K):
     import torch
 
