@@ -52,7 +52,7 @@ def build_host(force: bool = False) -> str:
     """The C++ host layer (Matrix / Cublas / GpuControl mirror) on top of the CUDA library."""
     if force or host_stale():
         cuda = os.path.dirname(os.path.dirname(NVCC))
-        cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", f"-I{cuda}/include", "-o", HOST_LIB]
+        cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-pthread", "-shared", "-fvisibility=hidden", f"-I{cuda}/include", "-o", HOST_LIB]
         cmd += sorted(glob.glob(os.path.join(HOST_DIR, "*.cpp")))
         cmd += [f"-L{HERE}", "-lcccc-cuda-b200", f"-L{cuda}/lib64", "-lcublas", "-lcudart", "-Wl,-rpath,$ORIGIN"]
         subprocess.check_call(cmd)

@@ -139,6 +139,14 @@ void BinWriter::add(const std::string& key, const void* data, size_t len)
     entries_.emplace_back(key, std::vector<uint8_t>((const uint8_t*)data, (const uint8_t*)data + len));
 }
 
+void BinWriter::addQuantised(const std::string& name, const WeightShard& shard)
+{
+    const char* suffix = shard.dtype == FP8_E4M3 ? "fp8_e4m3" : shard.dtype == FP8_E5M2 ? "fp8_e5m2" : "fp4_e2m1";
+    add(std::string("weight_") + suffix + "_" + name, shard.weights.data(), shard.weights.size());
+    if (shard.dtype != FP4_E2M1) { add("scale_" + name, &shard.quant_scale, sizeof(float)); }
+    if (!shard.block_scales.empty()) { add("blockscale_" + name, shard.block_scales.data(), shard.block_scales.size()); }
+}
+
 bool BinWriter::save(const std::string& path) const
 {
     std::string index;
@@ -189,10 +197,48 @@ bool loadWeightShard(const BinFile& f, const std::string& name, int N, int K, ch
     std::string key;
     DataType dt;
     if (!f.findTypedWeight(name, &key, &dt)) { return fail("weight '" + name + "' not found"); }
-    if (dt != FP8_E4M3 && dt != FP8_E5M2 && dt != FP4_E2M1) { return fail("weight '" + name + "' is not quantised"); }
     if (world < 1 || rank < 0 || rank >= world) { return fail("bad rank"); }
-    const uint64_t per = dt == FP4_E2M1 ? 2 : 1;    // elements per byte
     const uint64_t total = (uint64_t)N * (uint64_t)K;
+    if (dt == BFLOAT16 || dt == HALF || dt == FLOAT)
+    {
+        // An unquantised tensor (the reference's BF16 / float checkpoints): the shard's raw elements, which the
+        // caller quantises on the GPU (Net::quantizeWeights, cccc/Net.cpp:1142-1233).
+        const uint64_t eb = dt == FLOAT ? 4 : 2;
+        if (f.entry(key).length != total * eb) { return fail("weight '" + name + "' does not hold N*K elements"); }
+        int n0 = 0, n1 = N, k0 = 0, k1 = K;
+        if (kind == 'c')
+        {
+            if (N % world) { return fail("N does not divide over the ranks"); }
+            n0 = rank * (N / world);
+            n1 = n0 + N / world;
+        }
+        else if (kind == 'r')
+        {
+            if (K % (world * 256)) { return fail("K does not divide over the ranks in whole k steps"); }
+            k0 = rank * (K / world);
+            k1 = k0 + K / world;
+        }
+        else { return fail("kind must be 'c' or 'r'"); }
+        out->dtype = dt;
+        out->n = n1 - n0;
+        out->k = k1 - k0;
+        out->quant_scale = 1.0f;
+        out->block_scales.clear();
+        const uint64_t row_bytes = (uint64_t)out->k * eb;
+        out->weights.resize((uint64_t)out->n * row_bytes);
+        if (kind == 'c')
+        {
+            if (!f.read(key, (uint64_t)n0 * K * eb, out->weights.size(), out->weights.data())) { return fail("short read"); }
+            return true;
+        }
+        for (int n = 0; n < N; n++)
+        {
+            if (!f.read(key, ((uint64_t)n * K + k0) * eb, row_bytes, out->weights.data() + (uint64_t)n * row_bytes)) { return fail("short read"); }
+        }
+        return true;
+    }
+    if (dt != FP8_E4M3 && dt != FP8_E5M2 && dt != FP4_E2M1) { return fail("weight '" + name + "' has a type this loader does not take"); }
+    const uint64_t per = dt == FP4_E2M1 ? 2 : 1;    // elements per byte
     if (f.entry(key).length != total / per) { return fail("weight '" + name + "' does not hold N*K elements"); }
     const bool fp4 = dt == FP4_E2M1;
     const std::string skey = "blockscale_" + name;

@@ -52,10 +52,16 @@ private:
     mutable uint64_t bytes_read_ = 0;
 };
 
+struct WeightShard;
+
 class BinWriter
 {
 public:
     void add(const std::string& key, const void* data, size_t len);
+    // A quantised tensor under the keys the loaders look up: "weight_<suffix>_<name>" (suffix of
+    // cccc/Net.cpp:222-248 for the shard's type), "scale_<name>" (float32 dequant multiplier, FP8) and
+    // "blockscale_<name>" (E4M3 bytes, FP4).
+    void addQuantised(const std::string& name, const WeightShard& shard);
     bool save(const std::string& path) const;
 
 private:

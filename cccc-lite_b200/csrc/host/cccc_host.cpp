@@ -1,5 +1,7 @@
 #include "cccc_host.h"
 
+#include <algorithm>
+
 #include "../../../include/cccc_cuda_b200.h"
 
 #include <cmath>
@@ -320,7 +322,25 @@ void Matrix::mulBatched(const Matrix& A, const Matrix& B, Matrix& R, MatrixTrans
     }
 }
 
-void Matrix::quantizeWeights(DataType target)
+float Cublas::absmax(const float* x, size_t n)
+{
+    if (n == 0 || !handle_) { return 0.f; }
+    float best = 0.f;
+    // cublasIsamax takes an int count: larger tensors go in pieces
+    for (size_t off = 0; off < n; off += (size_t)1 << 30)
+    {
+        const int len = (int)std::min(n - off, (size_t)1 << 30);
+        int idx = 0;
+        if (cublasIsamax(handle_, len, x + off, 1, &idx) != CUBLAS_STATUS_SUCCESS || idx < 1) { continue; }
+        float v = 0.f;
+        cudaMemcpyAsync(&v, x + off + (idx - 1), sizeof(float), cudaMemcpyDeviceToHost, stream_);
+        cudaStreamSynchronize(stream_);
+        best = std::fmax(best, std::fabs(v));
+    }
+    return best;
+}
+
+void Matrix::quantizeWeights(DataType target, const std::function<float(float)>& combine_absmax)
 {
     if (!Cublas::isQuantized(target) || !owns_ || !gpu_) { return; }
     if (dt_ != FLOAT && dt_ != BFLOAT16) { return; }
@@ -329,7 +349,12 @@ void Matrix::quantizeWeights(DataType target)
     const size_t n = getDataSize();
     // Matrix.cpp:310-318: work from a float copy
     float* fbuf = (float*)gpu_->malloc(n * sizeof(float));
-    if (!fbuf) { return; }
+    if (!fbuf)
+    {
+        // the other ranks wait in the combine: take part in it before giving up
+        if (combine_absmax && target != FP4_E2M1) { combine_absmax(0.f); }
+        return;
+    }
     if (dt_ == FLOAT) { cudaMemcpy(fbuf, data_, n * sizeof(float), cudaMemcpyDeviceToDevice); }
     else { cuda_convert(data_, (int)dt_, fbuf, (int)FLOAT, (unsigned)n, 1.0f); }
     if (target == FP4_E2M1)
@@ -348,10 +373,8 @@ void Matrix::quantizeWeights(DataType target)
     else
     {
         // Matrix.cpp:340-350: absmax -> forward scale maxval/absmax, stored multiplier absmax/maxval
-        std::vector<float> host(n);
-        cudaMemcpy(host.data(), fbuf, n * sizeof(float), cudaMemcpyDeviceToHost);
-        float absmax = 0.f;
-        for (float v : host) { absmax = std::fmax(absmax, std::fabs(v)); }
+        float absmax = gpu_->cublas_->absmax(fbuf, n);
+        if (combine_absmax) { absmax = combine_absmax(absmax); }
         const float maxval = target == FP8_E4M3 ? 448.f : 57344.f;
         float fwd = 1.f;
         quant_scale_ = 1.f;

@@ -10,6 +10,7 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <functional>
 #include <map>
 #include <memory>
 
@@ -39,6 +40,12 @@ enum MatrixTransType
     MATRIX_TRANS = 1,
 };
 
+// cccc/types.h:36-60: the 16-bit storage type (bit pattern only here)
+struct bfloat16
+{
+    uint16_t bits;
+};
+
 class GpuControl;
 
 // The quantised GEMM dispatcher.  One per GpuControl, as in the reference.
@@ -63,6 +70,24 @@ public:
     void gemm(MatrixTransType TransA, MatrixTransType TransB, int M, int N, int K, float alpha, const void* A, DataType typeA,
         int lda, float invScaleA, const void* B, DataType typeB, int ldb, float invScaleB, float beta, void* C, DataType typeC,
         int ldc, float act_scale = 0.0f, const uint8_t* blk_scA = nullptr, const uint8_t* blk_scB = nullptr);
+
+    // The typed overloads of cccc/cublas_real.h:599-685 (quantised weight as A) and :688-752 (as B): BF16 activations
+    // and output, weight_type says how the bytes of the uint8_t operand decode.  They forward to the dispatcher above,
+    // so the fused kernel serves them where the reference dequantises and calls cublasGemmEx (:673-684, :740-751).
+    void gemm(MatrixTransType TransA, MatrixTransType TransB, int M, int N, int K, float alpha, const uint8_t* A, int lda,
+        const bfloat16* B, int ldb, float beta, bfloat16* C, int ldc, float inv_scale = 1.0f, DataType weight_type = FP8_E4M3,
+        float act_scale = 0.0f)
+    {
+        gemm(TransA, TransB, M, N, K, alpha, A, weight_type, lda, inv_scale, B, BFLOAT16, ldb, 1.0f, beta, C, BFLOAT16, ldc, act_scale);
+    }
+    void gemm(MatrixTransType TransA, MatrixTransType TransB, int M, int N, int K, float alpha, const bfloat16* A, int lda,
+        const uint8_t* B, int ldb, float beta, bfloat16* C, int ldc, float inv_scale = 1.0f, DataType weight_type = FP8_E4M3,
+        float act_scale = 0.0f)
+    {
+        gemm(TransA, TransB, M, N, K, alpha, A, BFLOAT16, lda, 1.0f, B, weight_type, ldb, inv_scale, beta, C, BFLOAT16, ldc, act_scale);
+    }
+    // Largest |x| of n floats on the device, as Matrix::quantizeWeights finds it (cublasIsamax, cccc/Matrix.cpp:340-343).
+    float absmax(const float* x, size_t n);
 
     int fusedCalls() const { return fused_calls_; }
     int fallbackCalls() const { return fallback_calls_; }
@@ -139,8 +164,10 @@ public:
         float r = 0);
     // In-place weight quantisation with the reference's rules (Matrix.cpp:301-355): FP8 per-tensor
     // scale maxval/absmax with the stored multiplier absmax/maxval; FP4 block 16 with E4M3 scales.
-    // The matrix must hold FLOAT or BFLOAT16 data it owns.
-    void quantizeWeights(DataType target);
+    // The matrix must hold FLOAT or BFLOAT16 data it owns.  combine_absmax (optional) maps this matrix's absmax to
+    // the one to use: a tensor-parallel shard passes its value in and gets the whole tensor's back, because the
+    // per-tensor FP8 scale is shared by the shards.
+    void quantizeWeights(DataType target, const std::function<float(float)>& combine_absmax = {});
     // Upload pre-quantised bytes (Matrix.cpp:357-375).
     void loadQuantizedDirect(const void* host_bytes, size_t n_bytes, DataType dt, float quant_scale);
 

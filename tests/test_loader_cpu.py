@@ -39,7 +39,7 @@ def write_container(path, entries):
 
 
 def load(L, f, name, N, K, kind, world, rank):
-    w = np.zeros(N * K, np.uint8)
+    w = np.zeros(N * K * 4, np.uint8)    # room for a float tensor
     s = np.zeros(N * K // 16 + 1, np.uint8)
     qs = C.c_float(0)
     dims = (C.c_int * 3)()
@@ -104,7 +104,7 @@ def test_loader_refuses_bad_requests(container, tmp_path):
     path, N, K, _, _ = container
     h, L = H()
     f = L.cccc_host_bin_open(path.encode())
-    for args, word in ((("missing", N, K, "c", 1, 0), "not found"), (("norm", 2, 4, "c", 1, 0), "not quantised"),
+    for args, word in ((("missing", N, K, "c", 1, 0), "not found"), (("norm", 2, 5, "c", 1, 0), "N*K"),
                        (("layers.0.q_proj", N + 1, K, "c", 1, 0), "N*K"), (("layers.0.q_proj", N, K, "c", 3, 0), "divide"),
                        (("layers.0.q_proj", N, K, "r", 32, 0), "k steps"), (("layers.0.down_proj", N, K, "r", 8, 0), "k steps"),
                        (("layers.0.q_proj", N, K, "x", 1, 0), "kind"), (("layers.0.q_proj", N, K, "c", 2, 2), "rank")):
@@ -119,6 +119,33 @@ def test_loader_refuses_bad_requests(container, tmp_path):
     open(t, "wb").write(b"NOT A BIN" + data[9:])
     assert not L.cccc_host_bin_open(t.encode())
     assert not L.cccc_host_bin_open(str(tmp_path / "absent.bin").encode())
+
+
+def test_unquantised_tensors_load_as_raw_shards(tmp_path):
+    """BF16 / float checkpoints (quantised on the GPU after loading): a column shard is a run of rows, a row shard
+    one run per row, in the tensor's own element type."""
+    h, L = H()
+    N, K = 8, 1024
+    rng = np.random.default_rng(5)
+    Wb = rng.integers(0, 1 << 16, (N, K)).astype(np.uint16)
+    Wf = rng.standard_normal((N, K)).astype(np.float32)
+    path = str(tmp_path / "raw.bin")
+    write_container(path, {"weight_bf16_a": Wb.tobytes(), "weight_float_b": Wf.tobytes()})
+    f = L.cccc_host_bin_open(path.encode())
+    for name, W, dt in (("a", Wb, O.BFLOAT16), ("b", Wf, O.FLOAT)):
+        for world in (1, 2, 4):
+            for rank in range(world):
+                rc, w, _, qs, dims, err = load(L, f, name, N, K, "c", world, rank)
+                want = W[rank * N // world:(rank + 1) * N // world]
+                assert rc == 0 and dims == [dt, N // world, K] and qs == 1.0, err
+                assert w[:want.nbytes].tobytes() == want.tobytes()
+                rc, w, _, qs, dims, err = load(L, f, name, N, K, "r", world, rank)
+                want = np.ascontiguousarray(W[:, rank * K // world:(rank + 1) * K // world])
+                assert rc == 0 and dims == [dt, N, K // world], err
+                assert w[:want.nbytes].tobytes() == want.tobytes()
+    rc, *_, err = load(L, f, "a", N, K, "r", 8, 0)
+    assert rc == -1 and "k steps" in err
+    L.cccc_host_bin_close(f)
 
 
 def test_writer_round_trip(tmp_path):
