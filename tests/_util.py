@@ -80,9 +80,11 @@ def ref_cuda_lib():
     return L
 
 
-def ref_gemm_lib():
-    """The reference's Cublas::gemm dispatcher behind a C-ABI (oracle/_ref), or None."""
-    path = os.path.join(REF_DIR, "libref_gpu_gemm.so")
+def ref_gemm_lib(patched: bool = False):
+    """The reference's Cublas::gemm dispatcher behind a C-ABI (oracle/_ref), or None.  patched: the same
+    dispatcher compiled from the reference's header with the two call sites changed as the integration notes
+    ask (oracle/patch_reference.py) and linked against cccc-cuda-b200 ahead of the reference's cccc-cuda."""
+    path = os.path.join(REF_DIR, "libref_gpu_gemm_patched.so" if patched else "libref_gpu_gemm.so")
     if not os.path.exists(path):
         return None
     L = C.CDLL(path)
