@@ -7,6 +7,7 @@
 #include "gemv_decode.cuh"
 #include "tensor_map.cuh"
 #include "prefill_launch.cuh"
+#include "gemm_stream.cuh"
 
 #include <atomic>
 #include <cmath>
@@ -192,8 +193,12 @@ enum
 {
     PLAN_PLAIN = 0,
     PLAN_DECODE = 1,
-    PLAN_PREFILL = 2
+    PLAN_PREFILL = 2,
+    PLAN_STREAM = 3
 };
+
+// flags bits 8-10 == 7: take the streaming tensor-core kernel whenever it accepts the shape (tests, tuning)
+constexpr unsigned int kVariantStream = 7u;
 
 static inline bool al16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
 
@@ -263,6 +268,12 @@ static int run_linear_wq(const GemvScratch* ws, int w_type, const void* W, const
 
     int plan = plan_for(w_type, W, blk_scales, X, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n);
     if (decode_only && plan != PLAN_DECODE) { return -1; }
+    if (!decode_only && (plan == PLAN_STREAM || (((flags >> 8) & 7u) == kVariantStream && plan != PLAN_PLAIN)))
+    {
+        const int r = launch_stream(w_type, &p, 1, ws->device, ws->sm_count, st, pdl);
+        if (r != -2) { return r; }
+        if (plan == PLAN_STREAM) { plan = M_tokens <= 32 ? PLAN_DECODE : PLAN_PREFILL; }
+    }
     if (plan == PLAN_DECODE)
     {
         int r;
@@ -317,13 +328,51 @@ struct GroupItem
 static int run_linear_wq_group(const GemvScratch* ws, int w_type, unsigned int count, const GroupItem* items, const void* X,
     unsigned int M_tokens, unsigned int K, unsigned int ldx, cudaStream_t st, unsigned int flags)
 {
+    // the streaming tensor-core kernel takes up to three members as one grid
+    bool one_stream = count >= 1 && count <= (unsigned)PF_MAX_GROUP;
+    bool want_stream = ((flags >> 8) & 7u) == kVariantStream;
+    for (unsigned int j = 0; j < count && one_stream; j++)
+    {
+        const int plan = items[j].N_out == 0 ? PLAN_PLAIN
+                                             : plan_for(w_type, items[j].W, items[j].blk_scales, X, items[j].Y, items[j].N_out, M_tokens, K,
+                                                   items[j].ldw, ldx, items[j].ldy_m, items[j].ldy_n);
+        one_stream = plan != PLAN_PLAIN;
+        want_stream = want_stream || plan == PLAN_STREAM;
+    }
+    if (one_stream && want_stream)
+    {
+        GemvParams ps[PF_MAX_GROUP];
+        memset(ps, 0, sizeof(ps));
+        for (unsigned int j = 0; j < count; j++)
+        {
+            GemvParams& q = ps[j];
+            q.W = (const uint8_t*)items[j].W;
+            q.blk = (w_type == DT_FP4) ? (const uint8_t*)items[j].blk_scales : nullptr;
+            q.X = (const uint16_t*)X;
+            q.Y = (uint16_t*)items[j].Y;
+            q.status = ws->status;
+            q.N = items[j].N_out;
+            q.M = M_tokens;
+            q.K = K;
+            q.ldw = items[j].ldw;
+            q.ldx = ldx;
+            q.ldy_m = items[j].ldy_m;
+            q.ldy_n = items[j].ldy_n;
+            q.w_scale = items[j].inv_scale;
+            q.alpha = items[j].alpha;
+            q.beta = items[j].beta;
+            q.out_f32 = (flags & 4u) ? 1u : ((flags & 8u) ? 2u : 0u);
+        }
+        const int r = launch_stream(w_type, ps, count, ws->device, ws->sm_count, st, (flags & 1u) != 0);
+        if (r != -2) { return r; }
+    }
     bool one_launch = count >= 1 && count <= (unsigned)kMaxGroup && M_tokens <= 32;
     for (unsigned int j = 0; j < count && one_launch; j++)
     {
         one_launch = items[j].N_out != 0
             && plan_for(w_type, items[j].W, items[j].blk_scales, X, items[j].Y, items[j].N_out, M_tokens, K, items[j].ldw, ldx,
                    items[j].ldy_m, items[j].ldy_n)
-                == PLAN_DECODE;
+                != PLAN_PLAIN;
     }
     if (one_launch)
     {
@@ -375,7 +424,7 @@ static int run_linear_wq_group(const GemvScratch* ws, int w_type, unsigned int c
         one_prefill = items[j].N_out != 0
             && plan_for(w_type, items[j].W, items[j].blk_scales, X, items[j].Y, items[j].N_out, M_tokens, K, items[j].ldw, ldx,
                    items[j].ldy_m, items[j].ldy_n)
-                == PLAN_PREFILL;
+                != PLAN_PLAIN;
     }
     if (one_prefill)
     {

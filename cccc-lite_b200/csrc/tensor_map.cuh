@@ -35,7 +35,7 @@ static EncodeTiledFn encode_tiled_fn()
 // A box {inner, box_rows, box_runs} therefore lands in shared memory as [run][row][inner].
 static bool make_map(CUtensorMap* map, CUtensorMapDataType dt, unsigned int elem_bytes, const void* base, unsigned int inner,
     unsigned long long rows, unsigned long long runs, unsigned long long row_stride_bytes, unsigned int box_rows,
-    unsigned int box_runs, bool swizzle128)
+    unsigned int box_runs, bool swizzle128, bool swizzle64 = false)
 {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) { return false; }
@@ -44,8 +44,8 @@ static bool make_map(CUtensorMap* map, CUtensorMapDataType dt, unsigned int elem
     const cuuint32_t box[3] = { inner, box_rows, box_runs };
     const cuuint32_t estr[3] = { 1, 1, 1 };
     const CUresult r = fn(map, dt, 3, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : (swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
+        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
 
