@@ -199,15 +199,14 @@ enum
 
 // flags bits 8-10 == 7: take the streaming tensor-core kernel whenever it accepts the shape (tests, tuning)
 constexpr unsigned int kVariantStream = 7u;
+// flags bit 11: never take the streaming kernel (the decode kernel up to 32 tokens, the prefill kernel above)
+constexpr unsigned int kFlagNoStream = 0x800u;
 
 static inline bool al16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
 
-static int plan_for(int w_type, const void* W, const void* blk, const void* X, const void* Y, unsigned int N, unsigned int M,
-    unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m, unsigned int ldy_n)
+static int plan_base(int w_type, const void* W, const void* blk, const void* X, unsigned int N, unsigned int M, unsigned int K, unsigned int ldw,
+    unsigned int ldx, unsigned int ldy_m, unsigned int ldy_n)
 {
-    (void)Y;
-    (void)ldy_m;
-    (void)ldy_n;
     if (N == 0 || M == 0 || K == 0) { return PLAN_PLAIN; }
     if (!al16(W) || !al16(X) || (ldx % 8) != 0) { return PLAN_PLAIN; }
     if (M > 32)
@@ -223,9 +222,25 @@ static int plan_for(int w_type, const void* W, const void* blk, const void* X, c
     {
         if ((K % 64) != 0 || (ldw % 16) != 0) { return PLAN_PLAIN; }
     }
-    if (M <= 32) { return PLAN_DECODE; }
-    if (prefill_supported(w_type, N, M, K, ldw, ldx, ldy_m, ldy_n)) { return PLAN_PREFILL; }
-    return PLAN_PLAIN;
+    return PLAN_DECODE;
+}
+
+// Measured on B200 (4096 x 4096, 12288 x 4096, 4096 x 12288; FP8 and FP4): up to 8 tokens the decode kernel's
+// dot products keep up with the weight stream and its persistent CTAs waste nothing between tiles; from 9
+// tokens on the streaming tensor-core kernel is faster (1.1x at 16 tokens, 1.4-2x at 32, 2-7x at 64-128, where
+// the alternative is the prefill kernel's compute-shaped tiles).
+constexpr unsigned int kStreamMinTokens = 9, kStreamMaxTokens = 128;
+
+static int plan_for(int w_type, const void* W, const void* blk, const void* X, const void* Y, unsigned int N, unsigned int M,
+    unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m, unsigned int ldy_n)
+{
+    (void)Y;
+    const int base = plan_base(w_type, W, blk, X, N, M, K, ldw, ldx, ldy_m, ldy_n);
+    if (base != PLAN_PLAIN && M >= kStreamMinTokens && M <= kStreamMaxTokens && stream_supported(w_type, blk, N, M, K, ldw, ldx))
+    {
+        return PLAN_STREAM;
+    }
+    return base;
 }
 
 
@@ -267,8 +282,12 @@ static int run_linear_wq(const GemvScratch* ws, int w_type, const void* W, const
     const bool pdl = (flags & 1u) != 0;
 
     int plan = plan_for(w_type, W, blk_scales, X, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n);
+    // the exchange lives in the decode kernel; flags bit 11 asks for the kernels that were there before the streaming one
+    const unsigned int variant = (flags >> 8) & 7u;
+    const bool no_stream = (flags & kFlagNoStream) != 0 || (variant >= 1 && variant <= 6);    // a prefill tile shape was asked for
+    if (plan == PLAN_STREAM && (decode_only || no_stream)) { plan = M_tokens <= 32 ? PLAN_DECODE : PLAN_PREFILL; }
     if (decode_only && plan != PLAN_DECODE) { return -1; }
-    if (!decode_only && (plan == PLAN_STREAM || (((flags >> 8) & 7u) == kVariantStream && plan != PLAN_PLAIN)))
+    if (!decode_only && (plan == PLAN_STREAM || (variant == kVariantStream && plan != PLAN_PLAIN)))
     {
         const int r = launch_stream(w_type, &p, 1, ws->device, ws->sm_count, st, pdl);
         if (r != -2) { return r; }
@@ -331,6 +350,7 @@ static int run_linear_wq_group(const GemvScratch* ws, int w_type, unsigned int c
     // the streaming tensor-core kernel takes up to three members as one grid
     bool one_stream = count >= 1 && count <= (unsigned)PF_MAX_GROUP;
     bool want_stream = ((flags >> 8) & 7u) == kVariantStream;
+    if ((flags & kFlagNoStream) != 0 || (((flags >> 8) & 7u) >= 1 && ((flags >> 8) & 7u) <= 6)) { one_stream = false; }
     for (unsigned int j = 0; j < count && one_stream; j++)
     {
         const int plan = items[j].N_out == 0 ? PLAN_PLAIN

@@ -80,10 +80,12 @@ C_EXPORT void cuda_clear_last_error(void);
  * the sum over shards is rounded to BF16 once.  bit 3 = round alpha * product to BF16 before beta * Y
  * is added: Y = bf16( bf16(alpha * W x) + beta * Y ), which with beta = 1 is the reference's linear
  * followed by its residual add (two BF16 tensors, scripts/convert_weights.py:562, :582).
- * bits 8-10 = tile shape of the M_tokens > 32 path,
- * for tests and tuning (0 = chosen by shape; 1-3 = one CTA per tile: 128 features x 128 tokens,
- * 128 x 256, 256 x 256; 4-6 = CTA pairs: 256 x 256, 512 features x 256 tokens, 256 x 512): every
- * value gives the same result bit for bit. */
+ * bits 8-10 = kernel choice for tests and tuning (0 = chosen by shape: the decode kernel up to 8 tokens,
+ * the streaming tensor-core kernel from 9 to 128 tokens where K % 256 == 0, the prefill kernel above;
+ * 1-3 = the prefill kernel with one CTA per tile: 128 features x 128 tokens, 128 x 256, 256 x 256;
+ * 4-6 = with CTA pairs: 256 x 256, 512 features x 256 tokens, 256 x 512 - the six tile shapes give the same
+ * result bit for bit; 7 = the streaming kernel wherever it accepts the shape, i.e. from 1 token).
+ * bit 11 = never the streaming kernel (the decode kernel up to 32 tokens, the prefill kernel above). */
 C_EXPORT int cuda_gemm_wq_bf16(int w_type, const void* W, const void* blk_scales, float inv_scale, const void* X,
     void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx,
     unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta, void* stream, unsigned int flags);

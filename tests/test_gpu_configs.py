@@ -116,6 +116,8 @@ def run_one(wt, N, K, M, seed, plan):
     import torch
 
     c = capi()
+    if 9 <= M <= 128:
+        plan = c.PLAN_STREAM    # the streaming tensor-core kernel takes these shapes from 9 to 128 tokens
     W, S, inv = device_weight(wt, N, K, seed)
     X = device_acts(M, K, seed)
     Y = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")

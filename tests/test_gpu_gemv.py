@@ -36,9 +36,13 @@ def test_decode_shapes_match_oracle(wt, M):
     c = capi()
     N, K = 640, 1024
     W, blk, inv, X = O.make_inputs(wt, N, K, M, seed=M, scaled=True)
-    assert c.gemm_wq_bf16_plan(wt, to_dev(W), to_dev(blk) if blk is not None else None, to_dev(X), None, N, M, K) == c.PLAN_DECODE
-    Y = run_linear(wt, W, blk, inv, X, N, M, K)
+    plan = c.gemm_wq_bf16_plan(wt, to_dev(W), to_dev(blk) if blk is not None else None, to_dev(X), None, N, M, K)
+    assert plan == (c.PLAN_DECODE if M <= 8 else c.PLAN_STREAM)
     _, y32 = O.linear_wq_bf16(wt, W, blk, inv, X, N, M, K)
+    # the decode kernel at every token count (it stays the kernel of the fused all-reduce), then the default choice
+    Y = run_linear(wt, W, blk, inv, X, N, M, K, flags=c.FLAG_NO_STREAM)
+    assert_close(O.bf16_bits_to_f32(Y).reshape(M, N), y32, (wt, M, "decode kernel"))
+    Y = run_linear(wt, W, blk, inv, X, N, M, K)
     assert_close(O.bf16_bits_to_f32(Y).reshape(M, N), y32, (wt, M))
 
 

@@ -117,8 +117,8 @@ def test_fp8_decode_kernels_dequantise_bit_exactly(wt, inv, M):
     N, K = 512, 512
     W = fp8_matrix(wt, N, K)
     D = expected_bits(wt, W, None, inv, N, K)
-    assert c_plan(wt, W, None, N, M, K) == capi().PLAN_DECODE
-    run_onehot(wt, W, None, inv, D, N, K, M, all_positions(K, M))
+    assert c_plan(wt, W, None, N, M, K) == (capi().PLAN_DECODE if M <= 8 else capi().PLAN_STREAM)
+    run_onehot(wt, W, None, inv, D, N, K, M, all_positions(K, M), flags=capi().FLAG_NO_STREAM)
 
 
 @pytest.mark.parametrize("M", [1, 8, 16, 32])
@@ -126,8 +126,8 @@ def test_fp4_decode_kernels_dequantise_bit_exactly(M):
     N, K = 508, 512     # 508 = 2 x 254: every non-NaN scale byte twice, with different nibbles
     W, S = fp4_matrix(N, K)
     D = expected_bits(O.FP4_E2M1, W, S, 1.0, N, K)
-    assert c_plan(O.FP4_E2M1, W, S, N, M, K) == capi().PLAN_DECODE
-    run_onehot(O.FP4_E2M1, W, S, 1.0, D, N, K, M, all_positions(K, M))
+    assert c_plan(O.FP4_E2M1, W, S, N, M, K) == (capi().PLAN_DECODE if M <= 8 else capi().PLAN_STREAM)
+    run_onehot(O.FP4_E2M1, W, S, 1.0, D, N, K, M, all_positions(K, M), flags=capi().FLAG_NO_STREAM)
 
 
 @pytest.mark.parametrize("wt", [O.FP8_E5M2, O.FP8_E4M3, O.FP4_E2M1])
@@ -159,7 +159,7 @@ def test_prefill_kernels_dequantise_bit_exactly(wt, variant, M):
         W, S = fp8_matrix(wt, N, K), None
     for inv in ((1.0,) if wt == O.FP4_E2M1 else (1.0, 0.25, 0.37)):
         D = expected_bits(wt, W, S, inv, N, K)
-        assert c_plan(wt, W, S, N, M, K) == c.PLAN_PREFILL
+        assert c_plan(wt, W, S, N, M, K) == (c.PLAN_STREAM if M <= 128 else c.PLAN_PREFILL)    # a tile-shape flag keeps the prefill kernel
         # M tokens cover every k position M / K times over
         positions = [(np.arange(M) * 37 + 11) % K]
         run_onehot(wt, W, S, inv, D, N, K, M, positions, flags=c.flag_prefill_variant(variant))

@@ -79,7 +79,7 @@ def _worker(rank, world, port, q):
                 dX = torch.from_numpy(Xs.view(np.int16)).cuda()
                 part = torch.zeros(M * N, dtype=torch.float32, device="cuda")
                 two = torch.zeros(M * N, dtype=torch.bfloat16, device="cuda")
-                assert capi.gemm_wq_bf16(wt, dW, dB, inv, dX, part, N, M, s.K, flags=capi.FLAG_OUT_F32) == 0
+                assert capi.gemm_wq_bf16(wt, dW, dB, inv, dX, part, N, M, s.K, flags=capi.FLAG_OUT_F32 | capi.FLAG_NO_STREAM) == 0
                 assert ar(part, two, M * N) == 0 and capi.check_error("two") == 0
                 one = torch.full((M * N,), float("nan"), dtype=torch.bfloat16, device="cuda")
                 rc = fused(wt, dW, dB, inv, dX, one, N, M, s.K)
@@ -104,7 +104,7 @@ def _worker(rank, world, port, q):
             dX = torch.from_numpy(Xs.view(np.int16)).cuda()
             part = torch.zeros(M * N, dtype=torch.float32, device="cuda")
             two = torch.zeros(M * N, dtype=torch.bfloat16, device="cuda")
-            assert capi.gemm_wq_bf16(wt, dW, None, inv, dX, part, N, M, s.K, flags=capi.FLAG_OUT_F32) == 0
+            assert capi.gemm_wq_bf16(wt, dW, None, inv, dX, part, N, M, s.K, flags=capi.FLAG_OUT_F32 | capi.FLAG_NO_STREAM) == 0
             assert ar(part, two, M * N) == 0 and capi.check_error("two") == 0
             prepared.append((dW, dX, inv, N, M, s.K, two))
         for rep in range(3):    # an odd number of calls per pass: every pass starts on the other slot set
