@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(256) swiglu_bf16_kernel(const uint16_t* __rest
 // Grid (S, Hkv, B), clusters of S CTAs along x: the S splits of one (sequence, kv head) exchange
 // their softmax statistics and partial outputs through distributed shared memory.
 template <int G, int HD>
-__global__ void __launch_bounds__(kTeam) attn_decode_kernel(const AttnDecodeParams p, unsigned int ts_cap)
+__global__ void __launch_bounds__(kTeam, (G <= 4 ? 2 : 1)) attn_decode_kernel(const AttnDecodeParams p, unsigned int ts_cap)
 {
     extern __shared__ __align__(16) float at_smem[];
     cg::cluster_group cluster = cg::this_cluster();
@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(kTeam) attn_decode_kernel(const AttnDecodePara
     ts = (ts + 31u) & ~31u;
     const unsigned int t0 = min(rank * ts, T), t1 = min(t0 + ts, T);
     const bool owner = pos >= t0 && pos < t1;
-    attn_scores<G, HD>(p, sm, b, kvh, t0, t1, ts_cap, pos, owner, tid);    // (runs the prologue too)
+    attn_scores<G, HD, (G * HD >= 512 ? 4 : 8)>(p, sm, b, kvh, t0, t1, ts_cap, pos, owner, tid);    // (runs the prologue too); fewer rows in flight where two CTAs would no longer fit an SM
     cluster.sync();
     attn_pv<G, HD>(p, sm, b, kvh, t0, t1, ts_cap, owner ? pos : 0xFFFFFFFFu, tid, [&]() {
         if (tid < G)
