@@ -469,7 +469,7 @@ def gpu_arm(args):
                 else:
                     bufs["push_allreduce"] = capi.PushAllReduce(dist, dist.group.WORLD, rank, world, n_max, dev)
                 allreduce = args.ar
-            except Exception as e:  # symmetric memory not available on this box: NCCL does the exchange
+            except Exception as e:  # no symmetric memory on this system: NCCL does the exchange
                 if rank == 0:
                     print(f"peer-memory all-reduce unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr, flush=True)
         ok = torch.tensor([1 if allreduce != "nccl" else 0], device=dev)

@@ -73,15 +73,22 @@ bool DecodeLinears::load(GpuControl* gpu, const BinFile& file, const ModelDims& 
         Linear l;
         l.kind = kind;
         if (!loadWeightShard(file, name, N, K, kind, world, rank, &l.host, err)) { return false; }
+        auto fail = [&](const std::string& what) {
+            if (err) { *err = what + " for '" + name + "'"; }
+            return false;
+        };
         l.w = gpu_->malloc(l.host.weights.size());
-        if (!l.w) { return false; }
-        cudaMemcpy(l.w, l.host.weights.data(), l.host.weights.size(), cudaMemcpyHostToDevice);
+        if (!l.w) { return fail("no device memory"); }
+        if (cudaMemcpy(l.w, l.host.weights.data(), l.host.weights.size(), cudaMemcpyHostToDevice) != cudaSuccess) { return fail("upload failed"); }
         weight_bytes_ += l.host.weights.size();
         if (!l.host.block_scales.empty())
         {
             l.s = gpu_->malloc(l.host.block_scales.size());
-            if (!l.s) { return false; }
-            cudaMemcpy(l.s, l.host.block_scales.data(), l.host.block_scales.size(), cudaMemcpyHostToDevice);
+            if (!l.s) { return fail("no device memory for the block scales"); }
+            if (cudaMemcpy(l.s, l.host.block_scales.data(), l.host.block_scales.size(), cudaMemcpyHostToDevice) != cudaSuccess)
+            {
+                return fail("upload of the block scales failed");
+            }
             weight_bytes_ += l.host.block_scales.size();
         }
         l.host.weights.clear();
@@ -98,9 +105,10 @@ bool DecodeLinears::load(GpuControl* gpu, const BinFile& file, const ModelDims& 
         }
     }
     if (!add("W_lm_head", d.vocab, d.hidden, 'c')) { return false; }
+    bool buffers_ok = true;
     auto mk = [&](const char* name, int width) {
         void* p = gpu_->malloc((size_t)max_tokens * width * 2);
-        cudaMemset(p, 0, (size_t)max_tokens * width * 2);
+        if (!p || cudaMemset(p, 0, (size_t)max_tokens * width * 2) != cudaSuccess) { buffers_ok = false; }
         buf_[name] = (uint16_t*)p;
     };
     mk("x", d.hidden);
@@ -114,10 +122,15 @@ bool DecodeLinears::load(GpuControl* gpu, const BinFile& file, const ModelDims& 
     partial_ = (float*)gpu_->malloc((size_t)max_tokens * d.hidden * 4);
     d_ids_ = (int*)gpu_->malloc((size_t)max_tokens * 4);
     d_vals_ = (float*)gpu_->malloc((size_t)max_tokens * 4);
-    cudaMallocHost((void**)&h_x_, (size_t)max_tokens * d.hidden * 2);
-    cudaMallocHost((void**)&h_ids_, (size_t)max_tokens * 4);
-    cudaMallocHost((void**)&h_vals_, (size_t)max_tokens * 4);
-    return partial_ && d_ids_ && d_vals_ && h_x_ && h_ids_ && h_vals_;
+    const bool pinned_ok = cudaMallocHost((void**)&h_x_, (size_t)max_tokens * d.hidden * 2) == cudaSuccess
+        && cudaMallocHost((void**)&h_ids_, (size_t)max_tokens * 4) == cudaSuccess
+        && cudaMallocHost((void**)&h_vals_, (size_t)max_tokens * 4) == cudaSuccess;
+    if (!(buffers_ok && pinned_ok && partial_ && d_ids_ && d_vals_))
+    {
+        if (err) { *err = "no memory for the step's buffers"; }
+        return false;
+    }
+    return true;
 }
 
 int DecodeLinears::issue(int M, cudaStream_t st)

@@ -162,3 +162,33 @@ def test_quantize_weights_follows_the_reference_rules(host, target):
         assert np.array_equal(q, O.float_to_fp8(w, target, float(maxval / absmax)))
         assert np.float32(L.cccc_host_matrix_quant_scale(m)) == np.float32(absmax / maxval)
     L.cccc_host_matrix_free(m)
+
+
+@pytest.mark.parametrize("wt", WTS[:2])
+@pytest.mark.parametrize("weight_is_a", [1, 0])
+def test_typed_gemm_overloads(host, wt, weight_is_a):
+    """Cublas::gemm(uint8_t* A, bfloat16* B -> bfloat16* C) and its mirror (cccc/cublas_real.h:599-685, 688-752):
+    the same linear as the type-erased dispatcher gives, served by the fused kernel."""
+    import torch
+
+    h, L, g = host
+    c = capi()
+    N, K, M = 384, 512, 6
+    W, _, inv, X = O.make_inputs(wt, N, K, M, seed=21 + wt, scaled=True)
+    dW, dX = to_dev(W), to_dev(X)
+    got = torch.zeros(M * N, dtype=torch.int16, device="cuda")
+    before = L.cccc_host_fused_calls(g)
+    if weight_is_a:
+        # C (N_out x tokens, ldc = N_out) = W^T X
+        L.cccc_host_gemm_typed(g, 1, h.MATRIX_TRANS, h.MATRIX_NO_TRANS, N, M, K, 1.0, dW.data_ptr(), K, dX.data_ptr(), K, 0.0,
+                               got.data_ptr(), N, inv, wt)
+    else:
+        # C (tokens x N_out, ldc = tokens) = X^T W
+        L.cccc_host_gemm_typed(g, 0, h.MATRIX_TRANS, h.MATRIX_NO_TRANS, M, N, K, 1.0, dX.data_ptr(), K, dW.data_ptr(), K, 0.0,
+                               got.data_ptr(), M, inv, wt)
+    L.cccc_host_gpu_sync(g)
+    assert L.cccc_host_fused_calls(g) == before + 1 and c.check_error("typed") == 0
+    _, y32 = O.linear_wq_bf16(wt, W, None, inv, X, N, M, K)
+    out = O.bf16_bits_to_f32(from_dev_u16(got))
+    out = out.reshape(M, N) if weight_is_a else out.reshape(N, M).T
+    assert_close(out, y32, ("typed", wt, weight_is_a))
