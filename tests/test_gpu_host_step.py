@@ -276,7 +276,7 @@ def test_tensor_parallel_in_one_process(host, tmp_path, world, wt, raw):
     if _devices() < world:
         pytest.skip(f"needs {world} GPUs")
     h, L, g = host
-    cfg = small_cfg(True, layers=2, hidden=2048, heads=8, kv=8, ffn=4096, vocab=4096)   # K / world stays a multiple of 256
+    cfg = small_cfg(True, layers=2, hidden=2048, heads=16, kv=8, ffn=4096, vocab=4096)   # K / world stays a multiple of 256 up to 8 ranks
     kw = {}
     if raw:
         rng = np.random.default_rng(12)
