@@ -519,3 +519,57 @@ HOST_EXPORT int cccc_host_tp_steps(const char* path, const int* devices, int wor
     for (int r = 0; r < world; r++) { total += bad[r]; }
     return total;
 }
+
+// ---- CPU-only checks of the host-side pieces ------------------------------------------------------------
+// Writes one quantised tensor under the loaders' keys (BinWriter::addQuantised).
+HOST_EXPORT int cccc_host_bin_write_quantised(const char* path, const char* name, int dtype, int n, int k, const void* weights,
+    unsigned long long weight_bytes, const void* scales, unsigned long long scale_bytes, float quant_scale)
+{
+    WeightShard s;
+    s.dtype = (DataType)dtype;
+    s.n = n;
+    s.k = k;
+    s.quant_scale = quant_scale;
+    s.weights.assign((const uint8_t*)weights, (const uint8_t*)weights + weight_bytes);
+    if (scales && scale_bytes) { s.block_scales.assign((const uint8_t*)scales, (const uint8_t*)scales + scale_bytes); }
+    BinWriter w;
+    w.addQuantised(name, s);
+    return w.save(path) ? 0 : -1;
+}
+
+// The combines of TensorParallel with `world` host threads and no device: rank r passes ids[r], values[r] (arg-max),
+// absmax[r], and its shard of `per` BF16 logits; out_ids / out_best / out_absmax get what each rank received, full
+// (world * world * per floats) the gathered rows as each rank saw them.  `rounds` repetitions exercise the barrier's reuse.
+HOST_EXPORT int cccc_host_tp_combine_selftest(int world, int rounds, const int* ids, const float* values, const float* absmax, const void* shards,
+    int per, int* out_ids, float* out_best, float* out_absmax, float* full)
+{
+    TensorParallel tp(world);
+    std::vector<std::thread> threads;
+    std::vector<int> bad(world, 0);
+    for (int r = 0; r < world; r++)
+    {
+        threads.emplace_back([&, r]() {
+            for (int it = 0; it < rounds; it++)
+            {
+                const int id = tp.combineArgmax(r, ids[r], values[r]);
+                const float best = tp.lastBest(r);
+                const float am = tp.combineAbsmax(r, absmax[r]);
+                std::vector<float> row((size_t)world * per);
+                tp.gatherLogits(r, (const uint16_t*)shards + (size_t)r * per, per, row.data());
+                if (it == 0)
+                {
+                    out_ids[r] = id;
+                    out_best[r] = best;
+                    out_absmax[r] = am;
+                    std::memcpy(full + (size_t)r * world * per, row.data(), row.size() * sizeof(float));
+                }
+                else if (out_ids[r] != id || out_best[r] != best || out_absmax[r] != am) { bad[r]++; }
+                if (!tp.allOk(r, true) || tp.allOk(r, r != 0)) { bad[r]++; }    // all true -> true; rank 0 false -> false for all
+            }
+        });
+    }
+    for (auto& t : threads) { t.join(); }
+    int total = 0;
+    for (int b : bad) { total += b; }
+    return total;
+}

@@ -55,6 +55,9 @@ SYMBOLS = {
     "cccc_host_step_save": (_i, [_vp, C.c_char_p, C.c_char_p, _i]),
     "cccc_host_step_generate": (_i, [_vp, _i, C.POINTER(C.c_int), _i, C.POINTER(C.c_int), _f, _i, _f, _f, C.POINTER(C.c_int), _i, C.c_uint,
                                      _i, C.POINTER(C.c_int), _i, C.POINTER(C.c_int)]),
+    "cccc_host_bin_write_quantised": (_i, [C.c_char_p, C.c_char_p, _i, _i, _i, _vp, C.c_ulonglong, _vp, C.c_ulonglong, _f]),
+    "cccc_host_tp_combine_selftest": (_i, [_i, _i, C.POINTER(C.c_int), C.POINTER(C.c_float), C.POINTER(C.c_float), _vp, _i, C.POINTER(C.c_int),
+                                           C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "cccc_host_tp_steps": (_i, [C.c_char_p, C.POINTER(C.c_int), _i, C.POINTER(C.c_int), _f, _f, C.POINTER(C.c_int), _i, C.POINTER(C.c_int),
                                 C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_char_p, _i]),
     "cccc_host_tp_generate": (_i, [C.c_char_p, C.POINTER(C.c_int), _i, C.POINTER(C.c_int), _f, _f, C.POINTER(C.c_int), _i,

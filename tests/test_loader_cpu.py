@@ -166,3 +166,31 @@ def test_writer_round_trip(tmp_path):
     rc, w, s, qs, dims, err = load(L, f, "w", 4, 256, "c", 2, 1)
     assert rc == 0 and np.array_equal(w[:512], np.frombuffer(blobs[1], np.uint8)[512:])
     L.cccc_host_bin_close(f)
+
+
+@pytest.mark.parametrize("dtype,suffix", [(O.FP8_E5M2, "fp8_e5m2"), (O.FP8_E4M3, "fp8_e4m3"), (O.FP4_E2M1, "fp4_e2m1")])
+def test_quantised_tensors_are_written_under_the_loaders_keys(tmp_path, dtype, suffix):
+    """BinWriter::addQuantised: weight_<dtype>_<name>, scale_<name> (FP8) or blockscale_<name> (FP4), read back by the
+    shard loader bit for bit."""
+    h, L = H()
+    N, K = 16, 512
+    rng = np.random.default_rng(dtype)
+    wbytes = N * K // 2 if dtype == O.FP4_E2M1 else N * K
+    W = rng.integers(0, 256, wbytes).astype(np.uint8)
+    S = rng.integers(0, 120, N * K // 16).astype(np.uint8) if dtype == O.FP4_E2M1 else None
+    path = str(tmp_path / "q.bin")
+    rc = L.cccc_host_bin_write_quantised(path.encode(), b"W_q_0", dtype, N, K, W.ctypes.data, W.size, S.ctypes.data if S is not None else None,
+                                         S.size if S is not None else 0, 0.37)
+    assert rc == 0
+    f = L.cccc_host_bin_open(path.encode())
+    assert L.cccc_host_bin_has(f, f"weight_{suffix}_W_q_0".encode())
+    assert bool(L.cccc_host_bin_has(f, b"scale_W_q_0")) == (dtype != O.FP4_E2M1)
+    assert bool(L.cccc_host_bin_has(f, b"blockscale_W_q_0")) == (dtype == O.FP4_E2M1)
+    rc, w, s, qs, dims, err = load(L, f, "W_q_0", N, K, "c", 1, 0)
+    assert rc == 0 and dims == [dtype, N, K], err
+    assert np.array_equal(w[:wbytes], W)
+    if dtype == O.FP4_E2M1:
+        assert np.array_equal(s[:S.size], S)
+    else:
+        assert np.float32(qs) == np.float32(0.37)
+    L.cccc_host_bin_close(f)

@@ -95,3 +95,40 @@ def test_two_gloo_ranks_match_unsharded(wt, kind):
         p.join(timeout=60)
         assert p.exitcode == 0
     assert sorted(results) == [(0, True), (1, True)]
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_in_process_rank_combines(world):
+    """cccc::TensorParallel (one host thread per rank, no device): every rank gets the largest logit's id with the
+    lowest rank winning a tie and all-NaN shards (id -1) ignored, the largest absmax, and the gathered row of logits in
+    rank order; the barrier is reused over many rounds."""
+    import ctypes as C
+
+    from __graft_entry__ import load_package
+    from oracle import oracle as O
+
+    L = load_package().hostapi.lib()
+    per = 5
+    rng = np.random.default_rng(world)
+    ids = rng.integers(0, 1000, world).astype(np.int32)
+    vals = rng.standard_normal(world).astype(np.float32)
+    vals[world - 1] = vals.max() + 1.0            # the last rank wins ...
+    vals[0] = vals[world - 1]                     # ... but rank 0 ties with it: the lowest rank takes it
+    if world > 2:
+        ids[1] = -1                               # a shard of only NaN never wins
+        vals[1] = 1e30
+    absmax = np.abs(rng.standard_normal(world)).astype(np.float32)
+    shards = O.f32_to_bf16_bits(rng.standard_normal(world * per).astype(np.float32))
+    out_ids = np.zeros(world, np.int32)
+    out_best = np.zeros(world, np.float32)
+    out_abs = np.zeros(world, np.float32)
+    full = np.zeros((world, world * per), np.float32)
+    p = lambda a, t: a.ctypes.data_as(C.POINTER(t))
+    bad = L.cccc_host_tp_combine_selftest(world, 200, p(ids, C.c_int), p(vals, C.c_float), p(absmax, C.c_float), shards.ctypes.data, per,
+                                          p(out_ids, C.c_int), p(out_best, C.c_float), p(out_abs, C.c_float), p(full, C.c_float))
+    assert bad == 0
+    assert np.all(out_ids == ids[0]) and np.all(out_best == vals[0])
+    assert np.all(out_abs == absmax.max())
+    want = O.bf16_bits_to_f32(shards)
+    for r in range(world):
+        assert np.array_equal(full[r], want)
