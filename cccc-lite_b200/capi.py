@@ -259,6 +259,20 @@ class FusedRowLinear:
         self.flag_ptrs = (C.c_ulonglong * world)(*[int(p) for p in hf.buffer_ptrs])
         torch.cuda.synchronize(device)
         dist.barrier(group)
+        # From 9 tokens on the streaming tensor-core kernel is the faster linear; it has no exchange in its epilogue,
+        # so those calls take the two-kernel form (FP32 partial sums, then the one-shot push all-reduce) on areas of
+        # their own.
+        self.push = PushAllReduce(dist, group, rank, world, n_max, device)
+        self.partial = torch.zeros(n_max, dtype=torch.float32, device=device)
+
+    def two_kernels(self, w_type: int, W, blk, inv_scale: float, X, Y, N: int, M: int, K: int, *, alpha: float = 1.0,
+                    stream: int | None = None, flags: int = 0) -> int:
+        """The same result as the fused call (sum over ranks in rank order, one BF16 rounding) as the linear with
+        FP32 output followed by cuda_b200_allreduce_f32_to_bf16."""
+        rc = gemm_wq_bf16(w_type, W, blk, inv_scale, X, self.partial, N, M, K, alpha=alpha, stream=stream, flags=flags | FLAG_OUT_F32)
+        if rc != 0:
+            return rc
+        return self.push(self.partial, Y, M * N, stream=stream, flags=flags & 1)
 
     def __call__(self, w_type: int, W, blk, inv_scale: float, X, Y, N: int, M: int, K: int, *, ldw: int | None = None,
                  ldx: int | None = None, ldy_m: int | None = None, ldy_n: int = 1, alpha: float = 1.0,

@@ -122,8 +122,10 @@ def _worker(rank, world, port, q):
         from tests.test_gpu_decode_model import make_model, oracle_step
 
         cfg = dm.ModelConfig(hidden=1024, n_heads=16, n_kv_heads=8, head_dim=128, ffn=2048, vocab=4096, layers=2, rope_theta=1e4)
-        Tctx, Mb = 32, 2
-        for wt in (O.FP8_E5M2, O.FP4_E2M1):
+        Tctx = 32
+        # two sequences (fused exchange inside the decode kernel), and twelve (from 9 tokens on the row-parallel linears
+        # are the streaming kernel with FP32 output followed by the push all-reduce)
+        for wt, Mb in ((O.FP8_E5M2, 2), (O.FP4_E2M1, 2), (O.FP8_E5M2, 12)):
             w = make_model(wt, cfg, seed=11 + wt)
             cos, sin = O.rope_tables_bf16(Tctx, cfg.head_dim, cfg.rope_theta)
 
@@ -150,7 +152,7 @@ def _worker(rank, world, port, q):
             Kc = [np.zeros((Mb, cfg.n_kv_heads, Tctx, cfg.head_dim), np.uint16) for _ in range(cfg.layers)]
             Vc = [np.zeros((Mb, cfg.n_kv_heads, Tctx, cfg.head_dim), np.uint16) for _ in range(cfg.layers)]
             pos = np.zeros(Mb, np.int32)
-            ids = np.array([3, 1000], np.int32)
+            ids = ((np.arange(Mb) * 997 + 3) % cfg.vocab).astype(np.int32)
             for step in range(3):
                 want = oracle_step(wt, cfg, w, ids, pos, Kc, Vc, cos, sin)
                 model.ids.copy_(torch.from_numpy(ids))
