@@ -113,6 +113,7 @@ __global__ void __launch_bounds__(kTeam, (G <= 4 ? 2 : 1)) attn_decode_kernel(co
     extern __shared__ __align__(16) float at_smem[];
     cg::cluster_group cluster = cg::this_cluster();
     AttnSmem<G, HD> sm(at_smem, ts_cap);
+    uint4* ring = reinterpret_cast<uint4*>(sm.red);    // the reduction buffer is idle while the K and V passes run
     const unsigned int tid = threadIdx.x;
     const unsigned int S = gridDim.x, rank = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     pdl_launch_dependents();
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(kTeam, (G <= 4 ? 2 : 1)) attn_decode_kernel(co
     ts = (ts + 31u) & ~31u;
     const unsigned int t0 = min(rank * ts, T), t1 = min(t0 + ts, T);
     const bool owner = pos >= t0 && pos < t1;
-    attn_scores<G, HD, (G * HD >= 512 ? 4 : 8)>(p, sm, b, kvh, t0, t1, ts_cap, pos, owner, tid);    // (runs the prologue too); fewer rows in flight where two CTAs would no longer fit an SM
+    attn_scores<G, HD, (G * HD >= 512 ? 4 : 8)>(p, sm, b, kvh, t0, t1, ts_cap, pos, owner, tid, ring);    // (runs the prologue too); fewer rows in flight where two CTAs would no longer fit an SM
     cluster.sync();
     attn_pv<G, HD>(p, sm, b, kvh, t0, t1, ts_cap, owner ? pos : 0xFFFFFFFFu, tid, [&]() {
         if (tid < G)
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(kTeam, (G <= 4 ? 2 : 1)) attn_decode_kernel(co
             sm.gl[2 * tid] = gmax;
             sm.gl[2 * tid + 1] = 1.0f / L;
         }
-    });
+    }, ring);
     cluster.sync();
     if (rank == 0)
     {
@@ -164,12 +165,13 @@ static int launch_attn(const AttnDecodeParams& p, int sm_count, int max_smem, cu
     // splits per (sequence, kv head): fill the SMs, at least 64 rows per split, a power of two <= 16
     unsigned int S = 1;
     while (S < 16 && (unsigned long long)p.B * p.Hkv * S * 2 <= (unsigned long long)sm_count + 20 && p.T_max / (S * 2) >= 64) { S *= 2; }
-    while (S < 16 && attn_smem_floats<G, HD>(attn_ts_cap(p.T_max, S)) * sizeof(float) > (size_t)max_smem) { S *= 2; }
+    auto smem_bytes = [](unsigned int ts_cap) { return attn_smem_floats<G, HD>(ts_cap) * sizeof(float); };
+    while (S < 16 && smem_bytes(attn_ts_cap(p.T_max, S)) > (size_t)max_smem) { S *= 2; }
     static std::atomic<int> max_cluster{ 0 };    // largest cluster size this kernel can be scheduled with (0 = not probed)
     for (;;)
     {
         const unsigned int ts_cap = attn_ts_cap(p.T_max, S);
-        const size_t smem = attn_smem_floats<G, HD>(ts_cap) * sizeof(float);
+        const size_t smem = smem_bytes(ts_cap);
         if (smem > (size_t)max_smem) { return -1; }
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess
             || (S > 8 && cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess))

@@ -111,6 +111,21 @@ struct AttnDecodeParams
     float eps, scale;        // RMSNorm epsilon of the q/k norms; 1/sqrt(dk)
 };
 
+constexpr int kAttnRingK = 4;     // passes of 32 rows (8 KB at head_dim 128)
+constexpr int kAttnRingV = 8;     // passes of 16 rows (4 KB at head_dim 128)
+template <int HD>
+__host__ __device__ constexpr size_t attn_ring_bytes()
+{
+    return (size_t)kTeam * 16 * ((kAttnRingK * (HD / 64)) > kAttnRingV ? (kAttnRingK * (HD / 64)) : kAttnRingV);
+}
+
+// floats of the region that serves as the K / V ring during the passes and as the cross-slot reduction buffer after them
+template <int G, int HD>
+__host__ __device__ constexpr size_t attn_red_floats()
+{
+    return (size_t)(kTeam / (HD / 8)) * G * HD > attn_ring_bytes<HD>() / 4 ? (size_t)(kTeam / (HD / 8)) * G * HD : attn_ring_bytes<HD>() / 4;
+}
+
 // Shared memory of one attention team (floats): see attn_smem_floats().
 template <int G, int HD>
 struct AttnSmem
@@ -123,7 +138,7 @@ struct AttnSmem
     float* ml;      // [G][2]    this split's max and sum of exponentials
     float* gl;      // [G][2]    the sequence's max and 1/sum
     float* opart;   // [G][HD]   this split's partial output
-    float* red;     // [kSlots2][G][HD]
+    float* red;     // [kSlots2][G][HD]; the K / V ring (attn_ring_bytes) lives here while the passes run
     float* wq;      // [HD] q-norm weights, [HD] k-norm weights, [HD/2] cos row, [HD/2] sin row
     float* sc;      // [G][ts_cap] scores, then probabilities
     __device__ AttnSmem(float* base, unsigned int ts_cap)
@@ -136,7 +151,7 @@ struct AttnSmem
         gl = ml + 2 * G;
         opart = gl + 2 * G;
         red = opart + G * HD;
-        wq = red + kSlots2 * G * HD;
+        wq = red + attn_red_floats<G, HD>();
         sc = wq + 3 * HD;
         (void)ts_cap;
     }
@@ -145,8 +160,20 @@ template <int G, int HD>
 __host__ __device__ constexpr size_t attn_smem_floats(unsigned int ts_cap)
 {
     return (size_t)G * HD + HD + (size_t)(G + 1) * HD + (size_t)(G + 1) * kTeam + 4 * G + (size_t)G * HD
-        + (size_t)(kTeam / (HD / 8)) * G * HD + 3 * HD + (size_t)G * ts_cap;
+        + attn_red_floats<G, HD>() + 3 * HD + (size_t)G * ts_cap;
 }
+
+// 16-byte asynchronous copy global -> shared that bypasses L1 (cp.async.cg); `valid` false fills zeros without
+// reading.  Each thread later reads back only what it copied itself, so cp.async.wait_group is all it needs.
+__device__ __forceinline__ void cp_async16(uint4* smem_dst, const void* gmem_src, bool valid)
+{
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const uint32_t bytes = valid ? 16u : 0u;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gmem_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ void unpack8(const uint4 v, float (&f)[8])
 {
@@ -254,6 +281,136 @@ __device__ __forceinline__ void attn_prologue(const AttnDecodeParams& p, AttnSme
     }
 }
 
+// The end of a scores pass: the team's maximum per head, then the sum of exp(score - maximum), into sm.ml.
+template <int G, int HD>
+__device__ __forceinline__ void attn_scores_finish(AttnSmem<G, HD>& sm, unsigned int t0, unsigned int t1, unsigned int ts_cap, unsigned int tid,
+    float (&mx)[G])
+{
+    // maximum over the team (all lanes of a row group hold the same value), then the sum of exponentials
+#pragma unroll
+    for (int g = 0; g < G; g++)
+    {
+#pragma unroll
+        for (int o = 8; o < 32; o <<= 1) { mx[g] = fmaxf(mx[g], __shfl_xor_sync(0xFFFFFFFFu, mx[g], o)); }
+        if ((tid & 31u) == 0) { sm.red[g * 8 + (tid >> 5)] = mx[g]; }
+    }
+    team_sync();
+    if (tid < G)
+    {
+        float m = sm.red[tid * 8];
+        for (int w = 1; w < 8; w++) { m = fmaxf(m, sm.red[tid * 8 + w]); }
+        sm.ml[2 * tid] = m;
+    }
+    team_sync();
+    float ls[G];
+    const unsigned int n_rows = t1 > t0 ? t1 - t0 : 0;
+#pragma unroll
+    for (int g = 0; g < G; g++)
+    {
+        ls[g] = 0.f;
+        const float m = sm.ml[2 * g];
+        for (unsigned int i = tid; i < n_rows; i += kTeam) { ls[g] += __expf(sm.sc[g * ts_cap + i] - m); }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) { ls[g] += __shfl_xor_sync(0xFFFFFFFFu, ls[g], o); }
+    }
+    team_sync();    // sm.red is reused
+#pragma unroll
+    for (int g = 0; g < G; g++)
+    {
+        if ((tid & 31u) == 0) { sm.red[g * 8 + (tid >> 5)] = ls[g]; }
+    }
+    team_sync();
+    if (tid < G)
+    {
+        float l = 0.f;
+        for (int w = 0; w < 8; w++) { l += sm.red[tid * 8 + w]; }
+        sm.ml[2 * tid + 1] = l;
+    }
+    team_sync();
+}
+
+// The ring form of attn_scores: K rows travel global -> shared by cp.async into a ring of kAttnRingK passes (32
+// rows each) that belongs to the threads piece by piece (every thread reads back only its own 16-byte pieces, so
+// no barrier is involved), and the copy of pass i + kAttnRingK is issued right after pass i has been consumed:
+// the DRAM latency of a pass overlaps the arithmetic of the passes before it, and no registers hold data in
+// flight.  (With registers as the buffer a pass was requested and then waited for: 32 KB in flight per team only
+// between the request and its use, 0.49 of the HBM rate at 32 sequences x 4096 rows.)
+template <int G, int HD>
+__device__ __forceinline__ void attn_scores_ring(const AttnDecodeParams& p, AttnSmem<G, HD>& sm, unsigned int b, unsigned int kvh,
+    unsigned int t0, unsigned int t1, unsigned int ts_cap, unsigned int pos, bool owner, unsigned int tid, uint4* ring)
+{
+    constexpr int CPL = HD / 64;    // 16-byte pieces per lane
+    constexpr int D = kAttnRingK;
+    const unsigned int sub = tid & 7u, slot = tid >> 3;
+    const uint16_t* Kb = p.k_cache + ((size_t)b * p.Hkv + kvh) * p.T_max * HD;
+    const unsigned int n_pass = t1 > t0 ? (t1 - t0 + 31u) / 32u : 0u;
+    auto issue = [&](unsigned int pass) {
+        if (pass < n_pass)
+        {
+            const unsigned int t = t0 + pass * 32 + slot;
+            const bool valid = t < t1 && !(owner && t == pos);
+            const uint16_t* row = Kb + (size_t)(valid ? t : 0) * HD;
+#pragma unroll
+            for (int c = 0; c < CPL; c++) { cp_async16(ring + ((pass % D) * CPL + c) * kTeam + tid, reinterpret_cast<const uint4*>(row) + sub + 8 * c, valid); }
+        }
+        cp_async_commit();    // a group per pass, empty past the end, so that the wait below always counts the same
+    };
+#pragma unroll
+    for (int d = 0; d < D; d++) { issue(d); }
+    attn_prologue<G, HD>(p, sm, b, kvh, pos, owner, tid);
+    float qf[G][CPL][8];
+#pragma unroll
+    for (int g = 0; g < G; g++)
+#pragma unroll
+        for (int c = 0; c < CPL; c++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) { qf[g][c][e] = sm.qs[g * HD + (sub + 8 * c) * 8 + e]; }
+    float mx[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) { mx[g] = -INFINITY; }
+    for (unsigned int pass = 0; pass < n_pass; pass++)
+    {
+        cp_async_wait<D - 1>();    // the oldest pass in flight has landed
+        const unsigned int t = t0 + pass * 32 + slot;
+        float acc[G];
+#pragma unroll
+        for (int g = 0; g < G; g++) { acc[g] = 0.f; }
+#pragma unroll
+        for (int c = 0; c < CPL; c++)
+        {
+            float kf[8];
+            if (owner && t == pos)
+            {
+                // the row this call appends: taken from shared memory, not re-read from the cache
+#pragma unroll
+                for (int e = 0; e < 8; e++) { kf[e] = sm.kn[(sub + 8 * c) * 8 + e]; }
+            }
+            else { unpack8(ring[((pass % D) * CPL + c) * kTeam + tid], kf); }
+#pragma unroll
+            for (int g = 0; g < G; g++)
+#pragma unroll
+                for (int e = 0; e < 8; e++) { acc[g] = __fmaf_rn(kf[e], qf[g][c][e], acc[g]); }
+        }
+        issue(pass + D);    // the slot just read is free again
+#pragma unroll
+        for (int g = 0; g < G; g++)
+        {
+            acc[g] += __shfl_xor_sync(0xFFFFFFFFu, acc[g], 1);
+            acc[g] += __shfl_xor_sync(0xFFFFFFFFu, acc[g], 2);
+            acc[g] += __shfl_xor_sync(0xFFFFFFFFu, acc[g], 4);
+            if (t < t1)
+            {
+                const float sc = bf16_round(__fmul_rn(p.scale, acc[g]));
+                if (sub == 0) { sm.sc[g * ts_cap + (t - t0)] = sc; }
+                mx[g] = fmaxf(mx[g], sc);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    team_sync();    // the ring shares its memory with sm.red, which the reductions below write
+    attn_scores_finish<G, HD>(sm, t0, t1, ts_cap, tid, mx);
+}
+
 // Prologue and scores of the rows [t0, t1) of one kv head against the G rotated queries:
 // sm.sc[g][t - t0] = bf16(scale * K[t] . q_g) (the reference's BF16 score tensor, MatrixEx.cpp:3056),
 // and this split's maximum and sum of exp(score - maximum) per head in sm.ml.  Eight lanes share a
@@ -262,8 +419,13 @@ __device__ __forceinline__ void attn_prologue(const AttnDecodeParams& p, AttnSme
 // latency of the first batch and the prologue's own round trip overlap.
 template <int G, int HD, int UNROLL = (G <= 4 ? 8 : 4)>
 __device__ __forceinline__ void attn_scores(const AttnDecodeParams& p, AttnSmem<G, HD>& sm, unsigned int b, unsigned int kvh,
-    unsigned int t0, unsigned int t1, unsigned int ts_cap, unsigned int pos, bool owner, unsigned int tid)
+    unsigned int t0, unsigned int t1, unsigned int ts_cap, unsigned int pos, bool owner, unsigned int tid, uint4* ring = nullptr)
 {
+    if (ring != nullptr)
+    {
+        attn_scores_ring<G, HD>(p, sm, b, kvh, t0, t1, ts_cap, pos, owner, tid, ring);
+        return;
+    }
     constexpr int CPL = HD / 64;    // 16-byte pieces per lane
     const unsigned int sub = tid & 7u, slot = tid >> 3;
     const uint16_t* Kb = p.k_cache + ((size_t)b * p.Hkv + kvh) * p.T_max * HD;
@@ -334,47 +496,7 @@ __device__ __forceinline__ void attn_scores(const AttnDecodeParams& p, AttnSmem<
             }
         }
     }
-    // maximum over the team (all lanes of a row group hold the same value), then the sum of exponentials
-#pragma unroll
-    for (int g = 0; g < G; g++)
-    {
-#pragma unroll
-        for (int o = 8; o < 32; o <<= 1) { mx[g] = fmaxf(mx[g], __shfl_xor_sync(0xFFFFFFFFu, mx[g], o)); }
-        if ((tid & 31u) == 0) { sm.red[g * 8 + (tid >> 5)] = mx[g]; }
-    }
-    team_sync();
-    if (tid < G)
-    {
-        float m = sm.red[tid * 8];
-        for (int w = 1; w < 8; w++) { m = fmaxf(m, sm.red[tid * 8 + w]); }
-        sm.ml[2 * tid] = m;
-    }
-    team_sync();
-    float ls[G];
-    const unsigned int n_rows = t1 > t0 ? t1 - t0 : 0;
-#pragma unroll
-    for (int g = 0; g < G; g++)
-    {
-        ls[g] = 0.f;
-        const float m = sm.ml[2 * g];
-        for (unsigned int i = tid; i < n_rows; i += kTeam) { ls[g] += __expf(sm.sc[g * ts_cap + i] - m); }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) { ls[g] += __shfl_xor_sync(0xFFFFFFFFu, ls[g], o); }
-    }
-    team_sync();    // sm.red is reused
-#pragma unroll
-    for (int g = 0; g < G; g++)
-    {
-        if ((tid & 31u) == 0) { sm.red[g * 8 + (tid >> 5)] = ls[g]; }
-    }
-    team_sync();
-    if (tid < G)
-    {
-        float l = 0.f;
-        for (int w = 0; w < 8; w++) { l += sm.red[tid * 8 + w]; }
-        sm.ml[2 * tid + 1] = l;
-    }
-    team_sync();
+    attn_scores_finish<G, HD>(sm, t0, t1, ts_cap, tid, mx);
 }
 
 // Probabilities and P*V for the rows [t0, t1): p = bf16(exp(score - max) / sum) with the
@@ -384,7 +506,7 @@ __device__ __forceinline__ void attn_scores(const AttnDecodeParams& p, AttnSmem<
 // rows has been requested, because V does not depend on it.
 template <int G, int HD, class Stats>
 __device__ __forceinline__ void attn_pv(const AttnDecodeParams& p, AttnSmem<G, HD>& sm, unsigned int b, unsigned int kvh,
-    unsigned int t0, unsigned int t1, unsigned int ts_cap, unsigned int pos_row, unsigned int tid, Stats stats)
+    unsigned int t0, unsigned int t1, unsigned int ts_cap, unsigned int pos_row, unsigned int tid, Stats stats, uint4* ring = nullptr)
 {
     constexpr int LPR = HD / 8;             // lanes per row
     constexpr int SLOTS = kTeam / LPR;      // rows per pass
@@ -392,6 +514,76 @@ __device__ __forceinline__ void attn_pv(const AttnDecodeParams& p, AttnSmem<G, H
     const unsigned int n = t1 > t0 ? t1 - t0 : 0;
     const unsigned int sub = tid % LPR, slot = tid / LPR;
     const uint16_t* Vb = p.v_cache + ((size_t)b * p.Hkv + kvh) * p.T_max * HD;
+    if (ring != nullptr)
+    {
+        // The ring form (see attn_scores_ring): V rows by cp.async, kAttnRingV passes of SLOTS rows in flight, the first
+        // ones requested before the statistics are exchanged.
+        constexpr int D = kAttnRingV;
+        const unsigned int n_pass = (n + SLOTS - 1) / SLOTS;
+        auto issue = [&](unsigned int pass) {
+            if (pass < n_pass)
+            {
+                const unsigned int t = t0 + pass * SLOTS + slot;
+                const bool valid = t < t1;
+                // the row this call appended comes from the projection output, not back from the cache
+                const uint16_t* vrow = t == pos_row ? p.v + (size_t)b * p.ldv + (size_t)kvh * HD : Vb + (size_t)(valid ? t : 0) * HD;
+                cp_async16(ring + (pass % D) * kTeam + tid, reinterpret_cast<const uint4*>(vrow) + sub, valid);
+            }
+            cp_async_commit();
+        };
+#pragma unroll
+        for (int d = 0; d < D; d++) { issue(d); }
+        stats();
+        team_sync();
+#pragma unroll
+        for (int g = 0; g < G; g++)
+        {
+            const float m = sm.gl[2 * g], inv = sm.gl[2 * g + 1];
+            for (unsigned int i = tid; i < n; i += kTeam)
+            {
+                sm.sc[g * ts_cap + i] = bf16_round(__fmul_rn(__expf(sm.sc[g * ts_cap + i] - m), inv));
+            }
+        }
+        team_sync();
+        float acc[G][8];
+#pragma unroll
+        for (int g = 0; g < G; g++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) { acc[g][e] = 0.f; }
+        for (unsigned int pass = 0; pass < n_pass; pass++)
+        {
+            cp_async_wait<D - 1>();
+            const unsigned int t = t0 + pass * SLOTS + slot;
+            if (t < t1)
+            {
+                float vf[8];
+                unpack8(ring[(pass % D) * kTeam + tid], vf);
+#pragma unroll
+                for (int g = 0; g < G; g++)
+                {
+                    const float pr = sm.sc[g * ts_cap + (t - t0)];
+#pragma unroll
+                    for (int e = 0; e < 8; e++) { acc[g][e] = __fmaf_rn(vf[e], pr, acc[g][e]); }
+                }
+            }
+            issue(pass + D);
+        }
+        cp_async_wait<0>();
+        team_sync();    // every thread has read its last ring slot before sm.red (the same memory) is written
+#pragma unroll
+        for (int g = 0; g < G; g++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) { sm.red[(slot * G + g) * HD + sub * 8 + e] = acc[g][e]; }
+        team_sync();
+        for (unsigned int i = tid; i < G * HD; i += kTeam)
+        {
+            float sacc = 0.f;
+            for (int sl = 0; sl < SLOTS; sl++) { sacc += sm.red[sl * G * HD + i]; }
+            sm.opart[i] = sacc;
+        }
+        team_sync();
+        return;
+    }
     uint4 vv[UNROLL];
     auto fetch = [&](unsigned int tb) {
 #pragma unroll
