@@ -128,18 +128,33 @@ __global__ void __launch_bounds__(kTeam, (G <= 4 ? 2 : 1)) attn_decode_kernel(co
     attn_scores<G, HD, (G * HD >= 512 ? 4 : 8)>(p, sm, b, kvh, t0, t1, ts_cap, pos, owner, tid, ring);    // (runs the prologue too); fewer rows in flight where two CTAs would no longer fit an SM
     cluster.sync();
     attn_pv<G, HD>(p, sm, b, kvh, t0, t1, ts_cap, owner ? pos : 0xFFFFFFFFu, tid, [&]() {
-        if (tid < G)
+        // One thread per (head, split) fetches that split's (max, sum) over distributed shared memory in a single
+        // round trip; the S lanes of a head then pass their pairs to the head's first lane, which combines them in
+        // split order (the order a serial loop over the splits would use, so the bits do not depend on S's layout).
+        const unsigned int lanes = G * S;    // <= 128: G <= 8, S <= 16
+        if (tid < ((lanes + 31u) & ~31u))
         {
-            float gmax = -INFINITY;
-            for (unsigned int r = 0; r < S; r++) { gmax = fmaxf(gmax, cluster.map_shared_rank(sm.ml, r)[2 * tid]); }
-            float L = 0.f;
-            for (unsigned int r = 0; r < S; r++)
+            const unsigned int g = tid / S, r = tid % S;
+            float m = -INFINITY, l = 0.f;
+            if (tid < lanes)
             {
                 const float* ml = cluster.map_shared_rank(sm.ml, r);
-                if (ml[2 * tid + 1] > 0.f) { L += ml[2 * tid + 1] * __expf(ml[2 * tid] - gmax); }
+                m = ml[2 * g];
+                l = ml[2 * g + 1];
             }
-            sm.gl[2 * tid] = gmax;
-            sm.gl[2 * tid + 1] = 1.0f / L;
+            float gmax = -INFINITY, L = 0.f;
+            const unsigned int lane = tid & 31u, first = lane - r;    // S divides 32, so a head's lanes share a warp
+            for (unsigned int j = 0; j < S; j++) { gmax = fmaxf(gmax, __shfl_sync(0xFFFFFFFFu, m, first + j)); }
+            for (unsigned int j = 0; j < S; j++)
+            {
+                const float mj = __shfl_sync(0xFFFFFFFFu, m, first + j), lj = __shfl_sync(0xFFFFFFFFu, l, first + j);
+                if (lj > 0.f) { L += lj * __expf(mj - gmax); }
+            }
+            if (tid < lanes && r == 0)
+            {
+                sm.gl[2 * g] = gmax;
+                sm.gl[2 * g + 1] = 1.0f / L;
+            }
         }
     }, ring);
     cluster.sync();

@@ -111,7 +111,7 @@ struct AttnDecodeParams
     float eps, scale;        // RMSNorm epsilon of the q/k norms; 1/sqrt(dk)
 };
 
-constexpr int kAttnRingK = 4;     // passes of 32 rows (8 KB at head_dim 128)
+constexpr int kAttnRingK = 4;     // passes of 32 rows (8 KB at head_dim 128); even: the loop consumes two per turn
 constexpr int kAttnRingV = 8;     // passes of 16 rows (4 KB at head_dim 128)
 template <int HD>
 __host__ __device__ constexpr size_t attn_ring_bytes()
@@ -368,41 +368,56 @@ __device__ __forceinline__ void attn_scores_ring(const AttnDecodeParams& p, Attn
     float mx[G];
 #pragma unroll
     for (int g = 0; g < G; g++) { mx[g] = -INFINITY; }
-    for (unsigned int pass = 0; pass < n_pass; pass++)
+    // Two passes per turn of the loop: their dot-product and shuffle chains are independent and interleave.
+    for (unsigned int pass = 0; pass < n_pass; pass += 2)
     {
-        cp_async_wait<D - 1>();    // the oldest pass in flight has landed
-        const unsigned int t = t0 + pass * 32 + slot;
-        float acc[G];
+        cp_async_wait<D - 2>();    // the two oldest passes in flight have landed
+        float acc[2][G];
 #pragma unroll
-        for (int g = 0; g < G; g++) { acc[g] = 0.f; }
-#pragma unroll
-        for (int c = 0; c < CPL; c++)
+        for (int u = 0; u < 2; u++)
         {
-            float kf[8];
-            if (owner && t == pos)
+            const unsigned int t = t0 + (pass + u) * 32 + slot;
+#pragma unroll
+            for (int g = 0; g < G; g++) { acc[u][g] = 0.f; }
+#pragma unroll
+            for (int c = 0; c < CPL; c++)
             {
-                // the row this call appends: taken from shared memory, not re-read from the cache
+                float kf[8];
+                if (owner && t == pos)
+                {
+                    // the row this call appends: taken from shared memory, not re-read from the cache
 #pragma unroll
-                for (int e = 0; e < 8; e++) { kf[e] = sm.kn[(sub + 8 * c) * 8 + e]; }
+                    for (int e = 0; e < 8; e++) { kf[e] = sm.kn[(sub + 8 * c) * 8 + e]; }
+                }
+                else { unpack8(ring[(((pass + u) % D) * CPL + c) * kTeam + tid], kf); }
+#pragma unroll
+                for (int g = 0; g < G; g++)
+#pragma unroll
+                    for (int e = 0; e < 8; e++) { acc[u][g] = __fmaf_rn(kf[e], qf[g][c][e], acc[u][g]); }
             }
-            else { unpack8(ring[((pass % D) * CPL + c) * kTeam + tid], kf); }
-#pragma unroll
-            for (int g = 0; g < G; g++)
-#pragma unroll
-                for (int e = 0; e < 8; e++) { acc[g] = __fmaf_rn(kf[e], qf[g][c][e], acc[g]); }
         }
-        issue(pass + D);    // the slot just read is free again
+        issue(pass + D);    // the two slots just read are free again
+        issue(pass + D + 1);
 #pragma unroll
         for (int g = 0; g < G; g++)
         {
-            acc[g] += __shfl_xor_sync(0xFFFFFFFFu, acc[g], 1);
-            acc[g] += __shfl_xor_sync(0xFFFFFFFFu, acc[g], 2);
-            acc[g] += __shfl_xor_sync(0xFFFFFFFFu, acc[g], 4);
-            if (t < t1)
+#pragma unroll
+            for (int u = 0; u < 2; u++)
             {
-                const float sc = bf16_round(__fmul_rn(p.scale, acc[g]));
-                if (sub == 0) { sm.sc[g * ts_cap + (t - t0)] = sc; }
-                mx[g] = fmaxf(mx[g], sc);
+                acc[u][g] += __shfl_xor_sync(0xFFFFFFFFu, acc[u][g], 1);
+                acc[u][g] += __shfl_xor_sync(0xFFFFFFFFu, acc[u][g], 2);
+                acc[u][g] += __shfl_xor_sync(0xFFFFFFFFu, acc[u][g], 4);
+            }
+#pragma unroll
+            for (int u = 0; u < 2; u++)
+            {
+                const unsigned int t = t0 + (pass + u) * 32 + slot;
+                if (t < t1)
+                {
+                    const float sc = bf16_round(__fmul_rn(p.scale, acc[u][g]));
+                    if (sub == 0) { sm.sc[g * ts_cap + (t - t0)] = sc; }
+                    mx[g] = fmaxf(mx[g], sc);
+                }
             }
         }
     }
@@ -550,23 +565,28 @@ __device__ __forceinline__ void attn_pv(const AttnDecodeParams& p, AttnSmem<G, H
         for (int g = 0; g < G; g++)
 #pragma unroll
             for (int e = 0; e < 8; e++) { acc[g][e] = 0.f; }
-        for (unsigned int pass = 0; pass < n_pass; pass++)
+        for (unsigned int pass = 0; pass < n_pass; pass += 2)
         {
-            cp_async_wait<D - 1>();
-            const unsigned int t = t0 + pass * SLOTS + slot;
-            if (t < t1)
+            cp_async_wait<D - 2>();
+#pragma unroll
+            for (int u = 0; u < 2; u++)
             {
-                float vf[8];
-                unpack8(ring[(pass % D) * kTeam + tid], vf);
-#pragma unroll
-                for (int g = 0; g < G; g++)
+                const unsigned int t = t0 + (pass + u) * SLOTS + slot;
+                if (t < t1)
                 {
-                    const float pr = sm.sc[g * ts_cap + (t - t0)];
+                    float vf[8];
+                    unpack8(ring[((pass + u) % D) * kTeam + tid], vf);
 #pragma unroll
-                    for (int e = 0; e < 8; e++) { acc[g][e] = __fmaf_rn(vf[e], pr, acc[g][e]); }
+                    for (int g = 0; g < G; g++)
+                    {
+                        const float pr = sm.sc[g * ts_cap + (t - t0)];
+#pragma unroll
+                        for (int e = 0; e < 8; e++) { acc[g][e] = __fmaf_rn(vf[e], pr, acc[g][e]); }
+                    }
                 }
             }
             issue(pass + D);
+            issue(pass + D + 1);
         }
         cp_async_wait<0>();
         team_sync();    // every thread has read its last ring slot before sm.red (the same memory) is written
