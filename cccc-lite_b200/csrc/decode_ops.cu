@@ -125,9 +125,9 @@ __global__ void __launch_bounds__(kTeam, (G <= 4 ? 2 : 1)) attn_decode_kernel(co
     ts = (ts + 31u) & ~31u;
     const unsigned int t0 = min(rank * ts, T), t1 = min(t0 + ts, T);
     const bool owner = pos >= t0 && pos < t1;
-    attn_scores<G, HD, (G * HD >= 512 ? 4 : 8)>(p, sm, b, kvh, t0, t1, ts_cap, pos, owner, tid, ring);    // (runs the prologue too); fewer rows in flight where two CTAs would no longer fit an SM
+    attn_scores<G, HD, 4, true>(p, sm, b, kvh, t0, t1, ts_cap, pos, owner, tid, ring);    // (runs the prologue too)
     cluster.sync();
-    attn_pv<G, HD>(p, sm, b, kvh, t0, t1, ts_cap, owner ? pos : 0xFFFFFFFFu, tid, [&]() {
+    attn_pv<G, HD, true>(p, sm, b, kvh, t0, t1, ts_cap, owner ? pos : 0xFFFFFFFFu, tid, [&]() {
         // One thread per (head, split) fetches that split's (max, sum) over distributed shared memory in a single
         // round trip; the S lanes of a head then pass their pairs to the head's first lane, which combines them in
         // split order (the order a serial loop over the splits would use, so the bits do not depend on S's layout).

@@ -432,15 +432,19 @@ __device__ __forceinline__ void attn_scores_ring(const AttnDecodeParams& p, Attn
 // row (two 16-byte pieces each for HD = 128), 32 rows per pass, UNROLL passes in flight.  The first
 // batch of K rows is requested BEFORE the prologue runs: the cache does not depend on q, so the DRAM
 // latency of the first batch and the prologue's own round trip overlap.
-template <int G, int HD, int UNROLL = (G <= 4 ? 8 : 4)>
+template <int G, int HD, int UNROLL = (G <= 4 ? 8 : 4), bool RING = false>
 __device__ __forceinline__ void attn_scores(const AttnDecodeParams& p, AttnSmem<G, HD>& sm, unsigned int b, unsigned int kvh,
     unsigned int t0, unsigned int t1, unsigned int ts_cap, unsigned int pos, bool owner, unsigned int tid, uint4* ring = nullptr)
 {
-    if (ring != nullptr)
+    // RING is a compile-time choice: a kernel carries only the form it uses (the stand-alone kernel runs its code
+    // once per launch, and what bounds it at one sequence is instruction fetch)
+    if constexpr (RING)
     {
         attn_scores_ring<G, HD>(p, sm, b, kvh, t0, t1, ts_cap, pos, owner, tid, ring);
         return;
     }
+    else
+    {
     constexpr int CPL = HD / 64;    // 16-byte pieces per lane
     const unsigned int sub = tid & 7u, slot = tid >> 3;
     const uint16_t* Kb = p.k_cache + ((size_t)b * p.Hkv + kvh) * p.T_max * HD;
@@ -512,6 +516,7 @@ __device__ __forceinline__ void attn_scores(const AttnDecodeParams& p, AttnSmem<
         }
     }
     attn_scores_finish<G, HD>(sm, t0, t1, ts_cap, tid, mx);
+    }
 }
 
 // Probabilities and P*V for the rows [t0, t1): p = bf16(exp(score - max) / sum) with the
@@ -519,7 +524,7 @@ __device__ __forceinline__ void attn_scores(const AttnDecodeParams& p, AttnSmem<
 // opart[g][d] = sum_t V[t][d] * p[g][t] in FP32.  HD/8 lanes share a row (16 bytes each).
 // `stats` produces the sequence-wide (max, 1/sum) into sm.gl; it runs AFTER the first batch of V
 // rows has been requested, because V does not depend on it.
-template <int G, int HD, class Stats>
+template <int G, int HD, bool RING = false, class Stats>
 __device__ __forceinline__ void attn_pv(const AttnDecodeParams& p, AttnSmem<G, HD>& sm, unsigned int b, unsigned int kvh,
     unsigned int t0, unsigned int t1, unsigned int ts_cap, unsigned int pos_row, unsigned int tid, Stats stats, uint4* ring = nullptr)
 {
@@ -529,7 +534,7 @@ __device__ __forceinline__ void attn_pv(const AttnDecodeParams& p, AttnSmem<G, H
     const unsigned int n = t1 > t0 ? t1 - t0 : 0;
     const unsigned int sub = tid % LPR, slot = tid / LPR;
     const uint16_t* Vb = p.v_cache + ((size_t)b * p.Hkv + kvh) * p.T_max * HD;
-    if (ring != nullptr)
+    if constexpr (RING)
     {
         // The ring form (see attn_scores_ring): V rows by cp.async, kAttnRingV passes of SLOTS rows in flight, the first
         // ones requested before the statistics are exchanged.
@@ -604,6 +609,8 @@ __device__ __forceinline__ void attn_pv(const AttnDecodeParams& p, AttnSmem<G, H
         team_sync();
         return;
     }
+    else
+    {
     uint4 vv[UNROLL];
     auto fetch = [&](unsigned int tb) {
 #pragma unroll
@@ -666,6 +673,7 @@ __device__ __forceinline__ void attn_pv(const AttnDecodeParams& p, AttnSmem<G, H
         sm.opart[i] = s;
     }
     team_sync();
+    }
 }
 
 }    // namespace b200
