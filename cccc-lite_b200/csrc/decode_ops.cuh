@@ -286,12 +286,12 @@ template <int G, int HD>
 __device__ __forceinline__ void attn_scores_finish(AttnSmem<G, HD>& sm, unsigned int t0, unsigned int t1, unsigned int ts_cap, unsigned int tid,
     float (&mx)[G])
 {
-    // maximum over the team (all lanes of a row group hold the same value), then the sum of exponentials
+    // maximum over the team, then the sum of exponentials
 #pragma unroll
     for (int g = 0; g < G; g++)
     {
 #pragma unroll
-        for (int o = 8; o < 32; o <<= 1) { mx[g] = fmaxf(mx[g], __shfl_xor_sync(0xFFFFFFFFu, mx[g], o)); }
+        for (int o = 1; o < 32; o <<= 1) { mx[g] = fmaxf(mx[g], __shfl_xor_sync(0xFFFFFFFFu, mx[g], o)); }
         if ((tid & 31u) == 0) { sm.red[g * 8 + (tid >> 5)] = mx[g]; }
     }
     team_sync();
@@ -398,25 +398,55 @@ __device__ __forceinline__ void attn_scores_ring(const AttnDecodeParams& p, Attn
         }
         issue(pass + D);    // the two slots just read are free again
         issue(pass + D + 1);
+        // The 2 G partial sums of the eight lanes of a row are reduce-scattered: each step halves what a lane
+        // keeps and adds its partner's half (7 shuffles for 8 values where an all-reduce of each takes 24), so
+        // that lane `sub` ends with the finished sum number `sub` (mod the count) and rounds, stores and tracks
+        // the maximum of that one score only.
+        constexpr int NV = 2 * G;
+        float v[NV];
 #pragma unroll
-        for (int g = 0; g < G; g++)
+        for (int i = 0; i < NV; i++) { v[i] = acc[i / G][i % G]; }
+        int idx = 0;    // index of v[0] among the original NV values
+        int cnt = NV;   // compile-time after unrolling
+#pragma unroll
+        for (int step = 4; step >= 1; step >>= 1)
         {
-#pragma unroll
-            for (int u = 0; u < 2; u++)
+            const bool upper = (sub & (unsigned)step) != 0;
+            if (cnt > 1)
             {
-                acc[u][g] += __shfl_xor_sync(0xFFFFFFFFu, acc[u][g], 1);
-                acc[u][g] += __shfl_xor_sync(0xFFFFFFFFu, acc[u][g], 2);
-                acc[u][g] += __shfl_xor_sync(0xFFFFFFFFu, acc[u][g], 4);
+                const int half = cnt / 2;
+#pragma unroll
+                for (int i = 0; i < NV / 2; i++)
+                {
+                    if (i < half)
+                    {
+                        const float send = upper ? v[i] : v[half + i];
+                        const float recv = __shfl_xor_sync(0xFFFFFFFFu, send, step);
+                        v[i] = (upper ? v[half + i] : v[i]) + recv;
+                    }
+                }
+                idx += upper ? half : 0;
+                cnt = half;
             }
+            else { v[0] += __shfl_xor_sync(0xFFFFFFFFu, v[0], step); }
+        }
 #pragma unroll
-            for (int u = 0; u < 2; u++)
+        for (int i = 0; i < NV / 8 + (NV < 8 ? 1 : 0); i++)
+        {
+            if (i < cnt)
             {
+                const int which = idx + i;    // (pass parity, head)
+                const int u = which / G, g = which % G;
                 const unsigned int t = t0 + (pass + u) * 32 + slot;
                 if (t < t1)
                 {
-                    const float sc = bf16_round(__fmul_rn(p.scale, acc[u][g]));
-                    if (sub == 0) { sm.sc[g * ts_cap + (t - t0)] = sc; }
-                    mx[g] = fmaxf(mx[g], sc);
+                    const float sc = bf16_round(__fmul_rn(p.scale, v[i]));
+                    sm.sc[g * ts_cap + (t - t0)] = sc;
+#pragma unroll
+                    for (int gg = 0; gg < G; gg++)
+                    {
+                        if (gg == g) { mx[gg] = fmaxf(mx[gg], sc); }
+                    }
                 }
             }
         }

@@ -64,14 +64,14 @@ float halfToFloat(uint16_t h)
 
 TensorParallel::~TensorParallel()
 {
+    // The areas belong to this object, not to the ranks' GpuControl objects: those live on the ranks' threads and are
+    // gone by the time the last owner of the TensorParallel lets go of it.
     for (int r = 0; r < world_; r++)
     {
-        if (r < (int)gpus_.size() && gpus_[r])
-        {
-            gpus_[r]->setAsCurrent();
-            if (recv_[r]) { gpus_[r]->free(recv_[r]); }
-            if (flag_[r]) { gpus_[r]->free(flag_[r]); }
-        }
+        if (device_[r] < 0) { continue; }
+        cudaSetDevice(device_[r]);
+        if (recv_[r]) { cudaFree(recv_[r]); }
+        if (flag_[r]) { cudaFree(flag_[r]); }
     }
 }
 
@@ -108,14 +108,13 @@ bool TensorParallel::join(int rank, GpuControl* gpu, unsigned int n_max, std::st
     gpu->setAsCurrent();
     n_max = (n_max + 3u) & ~3u;
     const size_t rb = cuda_b200_allreduce_recv_bytes(world_, n_max), fb = cuda_b200_fused_flag_bytes(world_);
-    void* recv = gpu->malloc(rb);
-    void* flag = gpu->malloc(fb);
-    bool ok = recv && flag;
+    void *recv = nullptr, *flag = nullptr;
+    bool ok = cudaMalloc(&recv, rb) == cudaSuccess && cudaMalloc(&flag, fb) == cudaSuccess;
     if (ok) { ok = cudaMemset(recv, 0, rb) == cudaSuccess && cudaMemset(flag, 0, fb) == cudaSuccess; }
+    if (!ok) { cudaGetLastError(); }
     {
         std::lock_guard<std::mutex> lk(m_);
-        if ((int)gpus_.size() < world_) { gpus_.resize(world_, nullptr); }
-        gpus_[rank] = gpu;
+        device_[rank] = gpu->getDeviceID();
         recv_[rank] = recv;
         flag_[rank] = flag;
         n_max_ = n_max;
@@ -127,7 +126,7 @@ bool TensorParallel::join(int rank, GpuControl* gpu, unsigned int n_max, std::st
     for (int r = 0; r < world_ && !failed_; r++)
     {
         if (r == rank) { continue; }
-        const int peer = gpus_[r]->getDeviceID();
+        const int peer = device_[r];
         if (peer == gpu->getDeviceID()) { continue; }
         int can = 0;
         cudaDeviceCanAccessPeer(&can, gpu->getDeviceID(), peer);

@@ -38,7 +38,7 @@ class TensorParallel
 {
 public:
     explicit TensorParallel(int world)
-        : world_(world), recv_(world, nullptr), flag_(world, nullptr), best_(world), id_(world), absmax_(world), last_best_(world)
+        : world_(world), recv_(world, nullptr), flag_(world, nullptr), device_(world, -1), best_(world), id_(world), absmax_(world), last_best_(world)
     {
         ok_.assign(world, 0);
     }
@@ -63,7 +63,7 @@ public:
 private:
     int world_;
     std::vector<void*> recv_, flag_;
-    std::vector<GpuControl*> gpus_;
+    std::vector<int> device_;    // the device of each rank that joined, -1 before
     unsigned int n_max_ = 0;
     std::mutex m_;
     std::condition_variable cv_;
