@@ -25,7 +25,7 @@ struct Workspace
     GemvScratch scratch;
     unsigned int* status() const { return reinterpret_cast<unsigned int*>(base.load(std::memory_order_acquire)); }
 };
-constexpr size_t kPartialBytes = 8u << 20;
+constexpr size_t kPartialBytes = 16u << 20;
 static Workspace g_ws[kMaxDevices];
 static std::mutex g_ws_mutex;
 
@@ -205,7 +205,13 @@ C_EXPORT int cuda_gemm_wq_bf16_plan(int w_type, const void* W, const void* blk_s
     unsigned int ldy_n)
 {
     if (w_type != DT_E4M3 && w_type != DT_E5M2 && w_type != DT_FP4) { return -1; }
-    return plan_for(w_type, W, blk_scales, X, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n);
+    const int plan = plan_for(w_type, W, blk_scales, X, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n);
+    if (plan != PLAN_PLAIN && native_by_default(w_type, M_tokens, (unsigned long long)N_out * K) && al16(W)
+        && (w_type == DT_FP4 ? native_fp4_supported(blk_scales, N_out, M_tokens, K, ldw, ldx) : native_supported(w_type, N_out, M_tokens, K, ldw, ldx)))
+    {
+        return PLAN_NATIVE;    // (an FP8 scale that is no power of two still goes to the kernels that dequantise)
+    }
+    return plan;
 }
 
 C_EXPORT int cuda_check_error(const char* label) { return sync_and_report(label ? label : "cuda"); }

@@ -8,6 +8,8 @@
 #include "tensor_map.cuh"
 #include "prefill_launch.cuh"
 #include "gemm_stream.cuh"
+#include "gemm_native.cuh"
+#include "gemm_native_fp4.cuh"
 
 #include <atomic>
 #include <cmath>
@@ -194,7 +196,8 @@ enum
     PLAN_PLAIN = 0,
     PLAN_DECODE = 1,
     PLAN_PREFILL = 2,
-    PLAN_STREAM = 3
+    PLAN_STREAM = 3,
+    PLAN_NATIVE = 4
 };
 
 // flags bits 8-10 == 7: take the streaming tensor-core kernel whenever it accepts the shape (tests, tuning)
@@ -202,7 +205,37 @@ constexpr unsigned int kVariantStream = 7u;
 // flags bit 11: never take the streaming kernel (the decode kernel up to 32 tokens, the prefill kernel above)
 constexpr unsigned int kFlagNoStream = 0x800u;
 
+// flags bit 12: take the native-operand tensor-core kernel (FP8 weights straight into the UMMA) whenever it accepts
+// the shape; bit 13: never take it
+constexpr unsigned int kFlagNative = 0x1000u;
+constexpr unsigned int kFlagNoNative = 0x2000u;
+// flags bit 14: the native-operand kernel never splits the activations itself (a kernel of its own does, as for many tokens)
+constexpr unsigned int kFlagNativeSplitKernel = 0x4000u;
+
 static inline bool al16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
+
+// Where the native-operand kernels are the default.  Measured on B200 against the kernels that dequantise in registers:
+//   FP8: the decode kernel streams 151936 x 4096 at 0.90-0.92 of the measured copy bandwidth for 1-2 tokens but at
+//        0.78 / 0.72 / 0.69 for 4 / 16 / 32, the native kernel at 0.93-0.86 throughout; on a layer's own linears (16-100 MB)
+//        what one launch costs besides streaming dominates, and there the decode kernel's is smaller;
+//   FP4: the decode kernel's arithmetic holds it to 0.37-0.46 at every size; the native kernel reaches 0.81-0.84 on
+//        128256 x 4096 and wins from about 50 MB of weights (28672 x 4096 at one token: 20.7 us against 26.8 us).
+constexpr unsigned long long kNativeFp8MinBytes = 256ull << 20, kNativeFp4MinBytes = 48ull << 20;
+constexpr unsigned int kNativeFp8MinTokens = 3;
+
+static inline bool native_by_default(int w_type, unsigned int M, unsigned long long weight_elems)
+{
+    if (w_type == DT_FP4) { return M <= (unsigned int)NF_MAX_TOKENS && weight_elems / 2 >= kNativeFp4MinBytes; }
+    return M >= kNativeFp8MinTokens && M <= (unsigned int)NK_MAX_TOKENS && weight_elems >= kNativeFp8MinBytes;
+}
+
+static inline bool want_native(unsigned int flags, int w_type, unsigned int M, unsigned long long weight_elems)
+{
+    if ((flags & kFlagNoNative) != 0 || M > (unsigned int)(w_type == DT_FP4 ? NF_MAX_TOKENS : NK_MAX_TOKENS)) { return false; }
+    const unsigned int variant = (flags >> 8) & 7u;
+    if (variant != 0 || (flags & kFlagNoStream) != 0) { return false; }    // a particular older kernel was asked for
+    return (flags & kFlagNative) != 0 || native_by_default(w_type, M, weight_elems);
+}
 
 static int plan_base(int w_type, const void* W, const void* blk, const void* X, unsigned int N, unsigned int M, unsigned int K, unsigned int ldw,
     unsigned int ldx, unsigned int ldy_m, unsigned int ldy_n)
@@ -281,6 +314,14 @@ static int run_linear_wq(const GemvScratch* ws, int w_type, const void* W, const
     p.out_f32 = (flags & 4u) ? 1u : ((flags & 8u) ? 2u : 0u);
     const bool pdl = (flags & 1u) != 0;
 
+    if (!decode_only && want_native(flags, w_type, M_tokens, (unsigned long long)N_out * K))
+    {
+        const int r = w_type == DT_FP4
+            ? launch_native_fp4(&p, 1, ws->partials, ws->partial_bytes, ws->counters, ws->n_counters, ws->device, ws->sm_count, st, pdl)
+            : launch_native(w_type, &p, 1, ws->partials, ws->partial_bytes, ws->counters, ws->n_counters, ws->device, ws->sm_count, st, pdl,
+                  (flags & kFlagNativeSplitKernel) != 0);
+        if (r != -2) { return r; }
+    }
     int plan = plan_for(w_type, W, blk_scales, X, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n);
     // the exchange lives in the decode kernel; flags bit 11 asks for the kernels that were there before the streaming one
     const unsigned int variant = (flags >> 8) & 7u;
@@ -347,6 +388,44 @@ struct GroupItem
 static int run_linear_wq_group(const GemvScratch* ws, int w_type, unsigned int count, const GroupItem* items, const void* X,
     unsigned int M_tokens, unsigned int K, unsigned int ldx, cudaStream_t st, unsigned int flags)
 {
+    unsigned long long group_elems = 0;
+    for (unsigned int j = 0; j < count; j++) { group_elems += (unsigned long long)items[j].N_out * K; }
+    if (count >= 1 && count <= (unsigned)PF_MAX_GROUP && want_native(flags, w_type, M_tokens, group_elems))
+    {
+        GemvParams ps[PF_MAX_GROUP];
+        memset(ps, 0, sizeof(ps));
+        bool all = true;
+        for (unsigned int j = 0; j < count; j++)
+        {
+            GemvParams& q = ps[j];
+            q.W = (const uint8_t*)items[j].W;
+            q.blk = (w_type == DT_FP4) ? (const uint8_t*)items[j].blk_scales : nullptr;
+            q.X = (const uint16_t*)X;
+            q.Y = (uint16_t*)items[j].Y;
+            q.status = ws->status;
+            q.N = items[j].N_out;
+            q.M = M_tokens;
+            q.K = K;
+            q.ldw = items[j].ldw;
+            q.ldx = ldx;
+            q.ldy_m = items[j].ldy_m;
+            q.ldy_n = items[j].ldy_n;
+            q.w_scale = items[j].inv_scale;
+            q.alpha = items[j].alpha;
+            q.beta = items[j].beta;
+            q.out_f32 = (flags & 4u) ? 1u : ((flags & 8u) ? 2u : 0u);
+            all = all && items[j].N_out != 0;
+        }
+        if (all)
+        {
+            const bool pdl = (flags & 1u) != 0;
+            const int r = w_type == DT_FP4
+                ? launch_native_fp4(ps, count, ws->partials, ws->partial_bytes, ws->counters, ws->n_counters, ws->device, ws->sm_count, st, pdl)
+                : launch_native(w_type, ps, count, ws->partials, ws->partial_bytes, ws->counters, ws->n_counters, ws->device, ws->sm_count, st, pdl,
+                      (flags & kFlagNativeSplitKernel) != 0);
+            if (r != -2) { return r; }
+        }
+    }
     // the streaming tensor-core kernel takes up to three members as one grid
     bool one_stream = count >= 1 && count <= (unsigned)PF_MAX_GROUP;
     bool want_stream = ((flags >> 8) & 7u) == kVariantStream;

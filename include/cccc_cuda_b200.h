@@ -85,7 +85,14 @@ C_EXPORT void cuda_clear_last_error(void);
  * 1-3 = the prefill kernel with one CTA per tile: 128 features x 128 tokens, 128 x 256, 256 x 256;
  * 4-6 = with CTA pairs: 256 x 256, 512 features x 256 tokens, 256 x 512 - the six tile shapes give the same
  * result bit for bit; 7 = the streaming kernel wherever it accepts the shape, i.e. from 1 token).
- * bit 11 = never the streaming kernel (the decode kernel up to 32 tokens, the prefill kernel above). */
+ * bit 11 = never the streaming kernel (the decode kernel up to 32 tokens, the prefill kernel above).
+ * bit 12 = the native-operand kernel wherever it accepts the shape (FP8 up to 32 tokens with a power-of-two
+ * inv_scale and K % 128 == 0; FP4 up to 13 tokens with K % 256 == 0): the quantised weights go from HBM through
+ * shared memory into tcgen05.mma (kind::f8f6f4, kind::mxf4nvf4 with the block scales) unchanged, the BF16
+ * activations as a few narrow rows whose sum they are.  Without the bit it is taken where it is the fastest:
+ * FP8 from 3 tokens and 256 MB of weights (lm_head), FP4 from 48 MB.  (FP4 block scales are read as UNSIGNED E4M3 there,
+ * which is what the reference's converter writes; a token row with an infinity or NaN gives NaN outputs in the FP4 kernel.)  bit 13 = never that kernel.  bit 14 = that
+ * kernel never splits the activations itself (a kernel of its own does, as it always does from 9 tokens). */
 C_EXPORT int cuda_gemm_wq_bf16(int w_type, const void* W, const void* blk_scales, float inv_scale, const void* X,
     void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx,
     unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta, void* stream, unsigned int flags);
@@ -310,7 +317,8 @@ C_EXPORT unsigned int cuda_decode_program_phases(const cuda_decode_program* p);
 C_EXPORT void cuda_decode_program_destroy(cuda_decode_program* p);
 
 /* Tuning/diagnostic: returns which kernel cuda_gemm_wq_bf16 would pick for a shape
- * (0 = plain kernel, 1 = decode GEMV (M<=32), 2 = prefill tcgen05 GEMM) without launching. */
+ * (0 = plain kernel, 1 = decode GEMV (M<=32), 2 = prefill tcgen05 GEMM, 3 = streaming tcgen05 kernel,
+ * 4 = native-operand tcgen05 kernel) without launching. */
 C_EXPORT int cuda_gemm_wq_bf16_plan(int w_type, const void* W, const void* blk_scales, const void* X,
     const void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx,
     unsigned int ldy_m, unsigned int ldy_n);
