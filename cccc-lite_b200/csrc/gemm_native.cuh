@@ -207,6 +207,47 @@ static __global__ void __launch_bounds__(256) split_activations_kernel(const uin
     *reinterpret_cast<uint2*>(p0 + 2 * (size_t)K) = make_uint2(o2[0], o2[1]);
 }
 
+// The parts of a tile that was cut across CTAs c_first .. c_last, added in that (k) order into v.  CTA c_first left its
+// part in its second slot, the others in their first.  The loads of eight parts and four tokens are issued together, so
+// that the CTA that arrived last waits for memory once per batch, not once per part; absent parts add an exact 0.
+template <int TOK>
+__device__ __forceinline__ void nk_sum_parts(const float* __restrict__ partials, unsigned int M, unsigned int c_first, unsigned int c_last, unsigned int f,
+    float (&v)[TOK])
+{
+    constexpr int TB = TOK < 4 ? TOK : 4, PB = 8;
+#pragma unroll
+    for (int t = 0; t < TOK; t++) { v[t] = 0.f; }
+#pragma unroll
+    for (int t0 = 0; t0 < TOK; t0 += TB)
+    {
+        if ((unsigned int)t0 >= M) { break; }
+        for (unsigned int c0 = c_first; c0 <= c_last; c0 += PB)
+        {
+            float tmp[PB][TB];
+#pragma unroll
+            for (int i = 0; i < PB; i++)
+            {
+                const unsigned int c = c0 + i;
+                const float* part = partials + (size_t)(2 * c + (c == c_first ? 1u : 0u)) * M * NK_BM;
+#pragma unroll
+                for (int j = 0; j < TB; j++)
+                {
+                    tmp[i][j] = (c <= c_last && t0 + j < TOK && (unsigned int)(t0 + j) < M) ? __ldcg(part + (t0 + j) * NK_BM + f) : 0.f;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < PB; i++)
+            {
+#pragma unroll
+                for (int j = 0; j < TB; j++)
+                {
+                    if (t0 + j < TOK) { v[t0 + j] += tmp[i][j]; }
+                }
+            }
+        }
+    }
+}
+
 // ---- the linear -------------------------------------------------------------------------------------------
 // BNP = UMMA N = 3 * tokens rounded up to a multiple of 16 (the rows past 3 * M are zero: the TMA's fill, or written so).
 // FUSED: no split kernel ran.  Four more warps read the BF16 activations themselves - first every token's whole row
@@ -247,6 +288,23 @@ __global__ void __launch_bounds__(FUSED ? NK_THREADS + 128 : NK_THREADS, 2) gemm
     const unsigned int u0 = (unsigned int)((U * blockIdx.x) / G), u1 = (unsigned int)((U * (blockIdx.x + 1ull)) / G);
     const unsigned int n_units = u1 - u0;
 
+    // which member of the group a tile belongs to
+    auto member_of = [&](unsigned int tile) -> unsigned int {
+        unsigned int si = 0;
+        if (p.n_seg > 1 && tile >= p.seg[1].tile0) { si = 1; }
+        if (p.n_seg > 2 && tile >= p.seg[2].tile0) { si = 2; }
+        return si;
+    };
+    const uint64_t pol = l2_policy_evict_first();
+    auto issue_weights = [&](unsigned int i) {
+        const unsigned int u = u0 + i, tile = u / p.nkb, kb = u % p.nkb, s = i % STAGES;
+        const unsigned int si = member_of(tile);
+        mbar_expect_tx(full + s, NK_W_BYTES);
+        tma_load_2d_hint(stages + s * STAGE_BYTES, &tmW.w[si], (int)(kb * NK_BK), (int)((tile - p.seg[si].tile0) * NK_BM), full + s, pol);
+        if (FUSED) { mbar_arrive(full + s); }
+    };
+    const unsigned int pre = n_units < (unsigned int)STAGES ? n_units : (unsigned int)STAGES;
+
     if (threadIdx.x == 0)
     {
         for (int s = 0; s < STAGES; s++)
@@ -261,6 +319,9 @@ __global__ void __launch_bounds__(FUSED ? NK_THREADS + 128 : NK_THREADS, 2) gemm
         *abort_flag = 0;
         *last_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // The weights depend on nothing - not on the previous kernel, not on the rest of this CTA: the first ring of
+        // stages is asked for before the CTA has even met (this thread is the TMA lane).
+        for (unsigned int i = 0; i < pre; i++) { issue_weights(i); }
     }
     if (warp == 1) { tmem_alloc(tmem_base_slot, TMEM_COLS); }
     tc_fence_before();
@@ -269,36 +330,17 @@ __global__ void __launch_bounds__(FUSED ? NK_THREADS + 128 : NK_THREADS, 2) gemm
     const uint32_t tmem_base = *tmem_base_slot;
     pdl_launch_dependents();
 
-    // which member of the group a tile belongs to
-    auto member_of = [&](unsigned int tile) -> unsigned int {
-        unsigned int si = 0;
-        if (p.n_seg > 1 && tile >= p.seg[1].tile0) { si = 1; }
-        if (p.n_seg > 2 && tile >= p.seg[2].tile0) { si = 2; }
-        return si;
-    };
-
     if (warp == 0)
     {
         // =========================== TMA lane ===========================
         if (lane == 0)
         {
-            const uint64_t pol = l2_policy_evict_first();
-            auto issue_weights = [&](unsigned int i) {
-                const unsigned int u = u0 + i, tile = u / p.nkb, kb = u % p.nkb, s = i % STAGES;
-                const unsigned int si = member_of(tile);
-                mbar_expect_tx(full + s, NK_W_BYTES);
-                tma_load_2d_hint(stages + s * STAGE_BYTES, &tmW.w[si], (int)(kb * NK_BK), (int)((tile - p.seg[si].tile0) * NK_BM), full + s, pol);
-                if (FUSED) { mbar_arrive(full + s); }
-            };
             auto issue_acts = [&](unsigned int i) {
                 const unsigned int u = u0 + i, kb = u % p.nkb, s = i % STAGES;
                 mbar_expect_tx(full + s, X_BYTES);
                 tma_load_2d(stages + s * STAGE_BYTES + NK_W_BYTES, &tmX, (int)(kb * NK_BK), 0, full + s);
                 mbar_arrive(full + s);
             };
-            // the weights do not depend on the previous kernel: the first ring of stages is asked for before waiting
-            const unsigned int pre = n_units < (unsigned int)STAGES ? n_units : (unsigned int)STAGES;
-            for (unsigned int i = 0; i < pre; i++) { issue_weights(i); }
             if (!FUSED)
             {
                 pdl_wait();
@@ -548,17 +590,7 @@ __global__ void __launch_bounds__(FUSED ? NK_THREADS + 128 : NK_THREADS, 2) gemm
                 if (write_out)
                 {
                     __threadfence();
-#pragma unroll
-                    for (int t = 0; t < TOK; t++) { v[t] = 0.f; }
-                    for (unsigned int c = c_first; c <= c_last; c++)
-                    {
-                        const float* part = p.partials + (size_t)(2 * c + (c == c_first ? 1u : 0u)) * p.M * NK_BM;
-#pragma unroll
-                        for (int t = 0; t < TOK; t++)
-                        {
-                            if ((unsigned int)t < p.M) { v[t] += __ldcg(part + t * NK_BM + f); }
-                        }
-                    }
+                    nk_sum_parts<TOK>(p.partials, p.M, c_first, c_last, f, v);
                 }
                 bar_sync_named(1, 128);    // everybody has read last_flag before the next tile's writes it
             }

@@ -1,4 +1,4 @@
-// FP4 (E2M1, one E4M3 scale per 16 weights) linear for 1 .. 13 tokens with the weights AND their block scales fed to
+// FP4 (E2M1, one E4M3 scale per 16 weights) linear for 1 .. 32 tokens with the weights AND their block scales fed to
 // the tensor cores as they lie in memory: tcgen05.mma kind::mxf4nvf4 with block-16 scales multiplies
 // (e2m1 * ue4m3) by (e2m1 * ue4m3) exactly and accumulates in FP32 - the reference's FP4 format IS that operand
 // format.  No thread touches a weight; four warps only carry each stage's 2 KB of scale bytes from shared memory
@@ -26,13 +26,21 @@ constexpr int NF_BK = 256;                  // k per block: one 128-byte swizzle
 constexpr int NF_THREADS = 32 * 10;         // TMA warp, MMA warp, four scale warps, four epilogue warps
 constexpr int NF_W_BYTES = NK_BM * 128;     // one weight stage
 constexpr int NF_SFA_BYTES = NK_BM * 16;    // its block scales: 16 per row
-constexpr int NF_MAX_TOKENS = 13;           // 7 * 13 = 91 of the 96 rows of B
-constexpr int NF_ACC_COLS = 96;             // accumulator columns reserved ahead of the scale columns
-constexpr int NF_MAX_STAGES = 5;            // 16 scale columns of A and of B per stage: 96 + 2 * 80 = 256 columns
+constexpr int NF_MAX_TOKENS = 32;           // 7 * 32 = 224 rows of B
+constexpr int NF_NARROW_TOKENS = 13;        // up to here (7 * 13 = 91 of 96 rows) two CTAs share an SM
+// Two shapes.  Narrow (N <= 96): two CTAs per SM, 256 TMEM columns each: 96 for the accumulators, then 16 scale columns
+// of A and 16 of B per stage, at most 5 stages.  Wide (N = 224, 14 .. 32 tokens): one CTA per SM with all 512 columns:
+// 224 + 4 stages x (16 + 32).
+__host__ __device__ constexpr bool nf_wide(int bnp) { return bnp > 96; }
+__host__ __device__ constexpr int nf_acc_cols(int bnp) { return nf_wide(bnp) ? 224 : 96; }
+__host__ __device__ constexpr int nf_sfb_words(int bnp) { return nf_wide(bnp) ? 8 : 4; }    // 32-row groups of B whose scales a 64-k step reads
+__host__ __device__ constexpr int nf_max_stages(int bnp) { return nf_wide(bnp) ? 4 : 5; }
 __host__ __device__ constexpr int nf_stage_bytes(int bnp) { return (NF_W_BYTES + bnp * 128 + NF_SFA_BYTES + bnp * 16 + 1023) & ~1023; }
 __host__ __device__ constexpr int nf_stages(int bnp)
 {
-    return (113 * 1024 - 2048) / nf_stage_bytes(bnp) > NF_MAX_STAGES ? NF_MAX_STAGES : (113 * 1024 - 2048) / nf_stage_bytes(bnp);
+    return ((nf_wide(bnp) ? 227 : 113) * 1024 - 2048) / nf_stage_bytes(bnp) > nf_max_stages(bnp)
+        ? nf_max_stages(bnp)
+        : ((nf_wide(bnp) ? 227 : 113) * 1024 - 2048) / nf_stage_bytes(bnp);
 }
 __host__ __device__ constexpr int nf_smem_bytes(int bnp) { return NK_HEADER_BYTES + nf_stages(bnp) * nf_stage_bytes(bnp) + 1024; }
 
@@ -154,16 +162,18 @@ struct NativeFp4Params
 // ---- the linear -------------------------------------------------------------------------------------------
 // BNP = UMMA N = 7 * tokens rounded up to a multiple of 16.
 template <int BNP>
-__global__ void __launch_bounds__(NF_THREADS, 2) gemm_wq_native_fp4_kernel(const __grid_constant__ NativeFp4Maps tm, const NativeParams p)
+__global__ void __launch_bounds__(NF_THREADS, nf_wide(BNP) ? 1 : 2) gemm_wq_native_fp4_kernel(const __grid_constant__ NativeFp4Maps tm, const NativeParams p)
 {
     constexpr int STAGES = nf_stages(BNP);
     constexpr int STAGE_BYTES = nf_stage_bytes(BNP);
     constexpr int B_BYTES = BNP * 128, SFB_BYTES = BNP * 16;
-    constexpr int TMEM_COLS = 256;
+    constexpr int TMEM_COLS = nf_wide(BNP) ? 512 : 256;
+    constexpr int ACC_COLS = nf_acc_cols(BNP), MAX_STAGES = nf_max_stages(BNP), SFB_WORDS = nf_sfb_words(BNP);
     constexpr int TOK = BNP / NF_PIECES;
-    constexpr int ACCS = NF_ACC_COLS / BNP >= 4 ? 4 : (NF_ACC_COLS / BNP >= 2 ? 2 : 1);    // independent accumulators, see nk_accs
-    constexpr int SFA_COL = NF_ACC_COLS, SFB_COL = NF_ACC_COLS + 16 * NF_MAX_STAGES;
-    static_assert(STAGES >= 2 && STAGES <= NF_MAX_STAGES && BNP <= NF_ACC_COLS && BNP % 16 == 0, "shape");
+    constexpr int ACCS = ACC_COLS / BNP >= 4 ? 4 : (ACC_COLS / BNP >= 2 ? 2 : 1);    // independent accumulators, see nk_accs
+    constexpr int SFA_COL = ACC_COLS, SFB_COL = ACC_COLS + 16 * MAX_STAGES, SFB_STAGE_COLS = 4 * SFB_WORDS;
+    static_assert(STAGES >= 2 && STAGES <= MAX_STAGES && BNP <= ACC_COLS && BNP % 16 == 0, "shape");
+    static_assert(SFB_COL + SFB_STAGE_COLS * MAX_STAGES <= TMEM_COLS && 32 * SFB_WORDS >= BNP, "tensor memory");
     extern __shared__ unsigned char nf_smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(nf_smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
@@ -183,6 +193,24 @@ __global__ void __launch_bounds__(NF_THREADS, 2) gemm_wq_native_fp4_kernel(const
     const unsigned int u0 = (unsigned int)((U * blockIdx.x) / G), u1 = (unsigned int)((U * (blockIdx.x + 1ull)) / G);
     const unsigned int n_units = u1 - u0;
 
+    auto member_of = [&](unsigned int tile) -> unsigned int {
+        unsigned int si = 0;
+        if (p.n_seg > 1 && tile >= p.seg[1].tile0) { si = 1; }
+        if (p.n_seg > 2 && tile >= p.seg[2].tile0) { si = 2; }
+        return si;
+    };
+    const uint64_t pol = l2_policy_evict_first();
+    auto issue_weights = [&](unsigned int i) {
+        const unsigned int u = u0 + i, tile = u / p.nkb, kb = u % p.nkb, s = i % STAGES;
+        const unsigned int si = member_of(tile);
+        const int row0 = (int)((tile - p.seg[si].tile0) * NK_BM);
+        unsigned char* st = stages + s * STAGE_BYTES;
+        mbar_expect_tx(full + s, NF_W_BYTES + NF_SFA_BYTES);
+        tma_load_2d_hint(st, &tm.w[si], (int)(kb * 128), row0, full + s, pol);
+        tma_load_2d_hint(st + NF_W_BYTES + B_BYTES, &tm.s[si], (int)(kb * 16), row0, full + s, pol);
+    };
+    const unsigned int pre = n_units < (unsigned int)STAGES ? n_units : (unsigned int)STAGES;
+
     if (threadIdx.x == 0)
     {
         for (int s = 0; s < STAGES; s++)
@@ -196,6 +224,8 @@ __global__ void __launch_bounds__(NF_THREADS, 2) gemm_wq_native_fp4_kernel(const
         *abort_flag = 0;
         *last_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // the weights and their scales depend on nothing: the first ring of stages is asked for before the CTA has met
+        for (unsigned int i = 0; i < pre; i++) { issue_weights(i); }
     }
     if (warp == 1) { tmem_alloc(tmem_base_slot, TMEM_COLS); }
     tc_fence_before();
@@ -204,28 +234,11 @@ __global__ void __launch_bounds__(NF_THREADS, 2) gemm_wq_native_fp4_kernel(const
     const uint32_t tmem_base = *tmem_base_slot;
     pdl_launch_dependents();
 
-    auto member_of = [&](unsigned int tile) -> unsigned int {
-        unsigned int si = 0;
-        if (p.n_seg > 1 && tile >= p.seg[1].tile0) { si = 1; }
-        if (p.n_seg > 2 && tile >= p.seg[2].tile0) { si = 2; }
-        return si;
-    };
-
     if (warp == 0)
     {
         // =========================== TMA lane ===========================
         if (lane == 0)
         {
-            const uint64_t pol = l2_policy_evict_first();
-            auto issue_weights = [&](unsigned int i) {
-                const unsigned int u = u0 + i, tile = u / p.nkb, kb = u % p.nkb, s = i % STAGES;
-                const unsigned int si = member_of(tile);
-                const int row0 = (int)((tile - p.seg[si].tile0) * NK_BM);
-                unsigned char* st = stages + s * STAGE_BYTES;
-                mbar_expect_tx(full + s, NF_W_BYTES + NF_SFA_BYTES);
-                tma_load_2d_hint(st, &tm.w[si], (int)(kb * 128), row0, full + s, pol);
-                tma_load_2d_hint(st + NF_W_BYTES + B_BYTES, &tm.s[si], (int)(kb * 16), row0, full + s, pol);
-            };
             auto issue_acts = [&](unsigned int i) {
                 const unsigned int u = u0 + i, kb = u % p.nkb, s = i % STAGES;
                 unsigned char* st = stages + s * STAGE_BYTES;
@@ -234,8 +247,6 @@ __global__ void __launch_bounds__(NF_THREADS, 2) gemm_wq_native_fp4_kernel(const
                 tma_load_2d(st + NF_W_BYTES + B_BYTES + NF_SFA_BYTES, &tm.xs, (int)(kb * 16), 0, full + s);
                 mbar_arrive(full + s);
             };
-            const unsigned int pre = n_units < (unsigned int)STAGES ? n_units : (unsigned int)STAGES;
-            for (unsigned int i = 0; i < pre; i++) { issue_weights(i); }
             pdl_wait();
             for (unsigned int i = 0; i < pre; i++) { issue_acts(i); }
             bool ok = true;
@@ -300,7 +311,7 @@ __global__ void __launch_bounds__(NF_THREADS, 2) gemm_wq_native_fp4_kernel(const
                 {
                     // 64 k = 32 bytes further along the swizzle row; its scales are the next four columns
                     umma_nvf4(tmem_base + (m % ACCS) * BNP, umma_desc_kmajor_sw128(a_addr + m * 32), umma_desc_kmajor_sw128(b_addr + m * 32), idesc,
-                        tmem_base + SFA_COL + s * 16 + m * 4, tmem_base + SFB_COL + s * 16 + m * 4, (first && m < ACCS) ? 0u : 1u);
+                        tmem_base + SFA_COL + s * 16 + m * 4, tmem_base + SFB_COL + s * SFB_STAGE_COLS + m * SFB_WORDS, (first && m < ACCS) ? 0u : 1u);
                 }
                 umma_commit(empty + s);
                 if (last) { umma_commit(acc_full); }
@@ -330,7 +341,7 @@ __global__ void __launch_bounds__(NF_THREADS, 2) gemm_wq_native_fp4_kernel(const
                 break;
             }
             const uint32_t sfa = smem_u32(stages + s * STAGE_BYTES + NF_W_BYTES + B_BYTES), sfb = sfa + NF_SFA_BYTES;
-            uint32_t ra[16], rb[16];
+            uint32_t ra[16], rb[SFB_STAGE_COLS];
 #pragma unroll
             for (int q = 0; q < 4; q++)
             {
@@ -339,15 +350,20 @@ __global__ void __launch_bounds__(NF_THREADS, 2) gemm_wq_native_fp4_kernel(const
                 ra[4 + q] = a.y;
                 ra[8 + q] = a.z;
                 ra[12 + q] = a.w;
+            }
+#pragma unroll
+            for (int q = 0; q < SFB_WORDS; q++)
+            {
                 uint4 b = make_uint4(0, 0, 0, 0);
                 if (q * 32 + (int)lane < BNP) { b = sk_lds128(sfb + (q * 32 + lane) * 16); }
                 rb[q] = b.x;
-                rb[4 + q] = b.y;
-                rb[8 + q] = b.z;
-                rb[12 + q] = b.w;
+                rb[SFB_WORDS + q] = b.y;
+                rb[2 * SFB_WORDS + q] = b.z;
+                rb[3 * SFB_WORDS + q] = b.w;
             }
             tmem_st_32x16(tmem_base + lane_field + SFA_COL + s * 16, ra);
-            tmem_st_32x16(tmem_base + lane_field + SFB_COL + s * 16, rb);
+#pragma unroll
+            for (int c = 0; c < SFB_STAGE_COLS; c += 16) { tmem_st_32x16(tmem_base + lane_field + SFB_COL + s * SFB_STAGE_COLS + c, rb + c); }
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
@@ -380,27 +396,37 @@ __global__ void __launch_bounds__(NF_THREADS, 2) gemm_wq_native_fp4_kernel(const
             tc_fence_after();
             float v[TOK];
             {
-                float acc[BNP];
+                // at most 112 columns (16 tokens) in registers at a time
+                constexpr int CH = BNP > 112 ? 112 : BNP, TPC = CH / NF_PIECES;
+                static_assert(BNP % CH == 0 && (BNP / CH) * TPC >= TOK, "chunks");
 #pragma unroll
-                for (int a = 0; a < ACCS; a++)
+                for (int h = 0; h < BNP / CH; h++)
                 {
+                    float acc[CH];
 #pragma unroll
-                    for (int c = 0; c < BNP; c += 16)
+                    for (int a = 0; a < ACCS; a++)
                     {
-                        uint32_t r[16];
-                        tmem_ld_32x16(tmem_base + ((quarter * 32u) << 16) + a * BNP + c, r);
-                        tmem_ld_wait();
 #pragma unroll
-                        for (int q = 0; q < 16; q++) { acc[c + q] = a == 0 ? __uint_as_float(r[q]) : acc[c + q] + __uint_as_float(r[q]); }
+                        for (int c = 0; c < CH; c += 16)
+                        {
+                            uint32_t r[16];
+                            tmem_ld_32x16(tmem_base + ((quarter * 32u) << 16) + a * BNP + h * CH + c, r);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int q = 0; q < 16; q++) { acc[c + q] = a == 0 ? __uint_as_float(r[q]) : acc[c + q] + __uint_as_float(r[q]); }
+                        }
                     }
-                }
 #pragma unroll
-                for (int t = 0; t < TOK; t++)
-                {
-                    float sum = acc[NF_PIECES * t];
+                    for (int t = 0; t < TPC; t++)
+                    {
+                        if (h * TPC + t < TOK)
+                        {
+                            float sum = acc[NF_PIECES * t];
 #pragma unroll
-                    for (int j = 1; j < NF_PIECES; j++) { sum += acc[NF_PIECES * t + j]; }
-                    v[t] = sum;
+                            for (int j = 1; j < NF_PIECES; j++) { sum += acc[NF_PIECES * t + j]; }
+                            v[h * TPC + t] = sum;
+                        }
+                    }
                 }
             }
             tc_fence_before();
@@ -436,17 +462,7 @@ __global__ void __launch_bounds__(NF_THREADS, 2) gemm_wq_native_fp4_kernel(const
                 if (write_out)
                 {
                     __threadfence();
-#pragma unroll
-                    for (int t = 0; t < TOK; t++) { v[t] = 0.f; }
-                    for (unsigned int c = c_first; c <= c_last; c++)
-                    {
-                        const float* part = p.partials + (size_t)(2 * c + (c == c_first ? 1u : 0u)) * p.M * NK_BM;
-#pragma unroll
-                        for (int t = 0; t < TOK; t++)
-                        {
-                            if ((unsigned int)t < p.M) { v[t] += __ldcg(part + t * NK_BM + f); }
-                        }
-                    }
+                    nk_sum_parts<TOK>(p.partials, p.M, c_first, c_last, f, v);
                 }
                 bar_sync_named(1, 128);
             }
@@ -494,7 +510,8 @@ static int launch_native_fp4_bn(const void* X, unsigned int ldx, NativeParams& n
 {
     const unsigned long long U = (unsigned long long)np.tiles * np.nkb;
     if (U == 0 || U > 0x7FFFFFFFull) { return -2; }
-    const unsigned int grid = (unsigned int)(U < 2ull * (unsigned)sm_count ? U : 2ull * (unsigned)sm_count);
+    const unsigned long long slots = (nf_wide(BNP) ? 1ull : 2ull) * (unsigned)sm_count;
+    const unsigned int grid = (unsigned int)(U < slots ? U : slots);
     // BNP rows, those past 7 M zeroed by the split kernel: a TMA box with rows out of bounds is slow (measured: 88 us
     // instead of 56 us for 128256 x 4096 at one token, where 26 of a box's 32 rows were out of bounds)
     const size_t rows = (size_t)BNP;
@@ -601,7 +618,8 @@ static int launch_native_fp4(const GemvParams* items, unsigned int count, float*
     if (np.M <= 4) { return NF_LAUNCH(32); }
     if (np.M <= 6) { return NF_LAUNCH(48); }
     if (np.M <= 9) { return NF_LAUNCH(64); }
-    return NF_LAUNCH(96);
+    if (np.M <= (unsigned int)NF_NARROW_TOKENS) { return NF_LAUNCH(96); }
+    return NF_LAUNCH(224);
 #undef NF_LAUNCH
 }
 
