@@ -87,7 +87,7 @@ C_EXPORT void cuda_clear_last_error(void);
  * result bit for bit; 7 = the streaming kernel wherever it accepts the shape, i.e. from 1 token).
  * bit 11 = never the streaming kernel (the decode kernel up to 32 tokens, the prefill kernel above).
  * bit 12 = the native-operand kernel wherever it accepts the shape (FP8 up to 32 tokens with a power-of-two
- * inv_scale and K % 128 == 0; FP4 up to 13 tokens with K % 256 == 0): the quantised weights go from HBM through
+ * inv_scale and K % 128 == 0; FP4 up to 32 tokens with K % 256 == 0): the quantised weights go from HBM through
  * shared memory into tcgen05.mma (kind::f8f6f4, kind::mxf4nvf4 with the block scales) unchanged, the BF16
  * activations as a few narrow rows whose sum they are.  Without the bit it is taken where it is the fastest:
  * FP8 from 3 tokens and 256 MB of weights (lm_head), FP4 from 48 MB.  (FP4 block scales are read as UNSIGNED E4M3 there,

@@ -119,7 +119,7 @@ def run_one(wt, N, K, M, seed, plan):
     if 9 <= M <= 128:
         plan = c.PLAN_STREAM    # the streaming tensor-core kernel takes these shapes from 9 to 128 tokens
     # the native-operand kernels where they are the fastest: FP8 from 3 tokens and 256 MB of weights, FP4 from 48 MB
-    if (wt == O.FP4_E2M1 and M <= 13 and N * K // 2 >= 48 << 20) or (wt != O.FP4_E2M1 and 3 <= M <= 32 and N * K >= 256 << 20):
+    if (wt == O.FP4_E2M1 and M <= 32 and N * K // 2 >= 48 << 20) or (wt != O.FP4_E2M1 and 3 <= M <= 32 and N * K >= 256 << 20):
         plan = c.PLAN_NATIVE
     W, S, inv = device_weight(wt, N, K, seed)
     X = device_acts(M, K, seed)
@@ -197,9 +197,9 @@ def test_grouped_calls_of_the_benchmark(wt, members, M):
                           alpha=1.0 + 0.25 * j))
     before = c.launch_count()
     assert c.gemm_wq_bf16_group(wt, c.make_group(items, K), X, M, K) == 0 and c.check_error("group") == 0
-    # one launch for the group; the native-operand FP4 kernel (the group's weights are above 48 MB, up to 13 tokens)
+    # one launch for the group; the native-operand FP4 kernel (the group's weights are above 48 MB, up to 32 tokens)
     # has the split of the activations as a launch of its own before it
-    native_fp4 = wt == O.FP4_E2M1 and M <= 13 and sum(it["N"] for it in items) * K // 2 >= 48 << 20
+    native_fp4 = wt == O.FP4_E2M1 and M <= 32 and sum(it["N"] for it in items) * K // 2 >= 48 << 20
     assert c.launch_count() - before == (2 if native_fp4 else 1)
     toks = None if M <= 32 else np.unique(np.concatenate([np.arange(0, M, 131), [M - 1]]))
     for it in items:

@@ -1,6 +1,6 @@
 """The native-operand kernels: the quantised weight bytes go from HBM through TMA into shared memory and from there
 into the tensor cores unchanged - FP8 (1 .. 32 tokens) into tcgen05.mma kind::f8f6f4, FP4 with its E4M3 block scales
-(1 .. 13 tokens) into kind::mxf4nvf4 - and each BF16 activation row as three E5M2 rows (FP8) or seven E2M1 rows with
+(1 .. 32 tokens) into kind::mxf4nvf4 - and each BF16 activation row as three E5M2 rows (FP8) or seven E2M1 rows with
 power-of-two block scales (FP4) whose sum it is.  Up to 8 tokens the FP8 kernel splits the activations itself (one
 launch); otherwise a small kernel does (two launches; flags bit 14 asks for that form everywhere).
 Forced through flags bit 12, so that every shape the kernels accept is checked, not only those the dispatcher gives them.
@@ -62,7 +62,8 @@ def test_native_kernel_matches_oracle(wt, form, N, K, M):
 
 
 @pytest.mark.parametrize("N,K,M", [(128, 256, 1), (256, 512, 2), (384, 1024, 3), (200, 768, 5), (1000, 4096, 6), (512, 2048, 8),
-                                   (4096, 4096, 9), (128, 14336, 13), (6144, 4096, 1), (300, 1024, 7)])
+                                   (4096, 4096, 9), (128, 14336, 13), (6144, 4096, 1), (300, 1024, 7), (1000, 2048, 14),
+                                   (640, 4096, 20), (2500, 1024, 32), (4096, 4096, 27)])
 def test_native_fp4_kernel_matches_oracle(N, K, M):
     wt = O.FP4_E2M1
     W, blk, inv, X = O.make_inputs(wt, N, K, M, seed=N + M, scaled=False)
@@ -88,7 +89,7 @@ def unsigned_scales(S):
     return (S & 0x7F).astype(np.uint8)
 
 
-@pytest.mark.parametrize("M", [1, 5, 9, 13])
+@pytest.mark.parametrize("M", [1, 5, 9, 13, 14, 32])
 def test_native_fp4_products_are_exact(M):
     N, K = 508, 512
     W, S = fp4_matrix(N, K)
@@ -97,8 +98,9 @@ def test_native_fp4_products_are_exact(M):
     run_onehot(O.FP4_E2M1, W, S, 1.0, D, N, K, M, all_positions(K, M)[:40], flags=NATIVE)
 
 
-def test_native_fp4_tiles_cut_across_ctas_are_exact():
-    N, K, M = 200, 16384, 3
+@pytest.mark.parametrize("M", [3, 30])
+def test_native_fp4_tiles_cut_across_ctas_are_exact(M):
+    N, K = 200, 16384
     W, S = fp4_matrix(N, K)
     S = unsigned_scales(S)
     D = expected_bits(O.FP4_E2M1, W, S, 1.0, N, K)
@@ -205,8 +207,7 @@ def test_a_scale_that_is_no_power_of_two_goes_to_the_dequantising_kernels():
 @pytest.mark.parametrize("wt", WTS + [O.FP4_E2M1])
 @pytest.mark.parametrize("M", [2, 12, 30])
 def test_native_group_is_one_linear_launch(wt, M):
-    if wt == O.FP4_E2M1 and M > 13:
-        pytest.skip("the FP4 kernel takes up to 13 tokens")
+
     from tests.test_gpu_group import build
 
     c = capi()
@@ -250,5 +251,5 @@ def test_the_dispatcher_takes_the_native_kernels_where_they_are_the_fastest():
     assert plan(O.FP8_E5M2, 151936, 4) == c.PLAN_NATIVE and plan(O.FP8_E5M2, 151936, 32) == c.PLAN_NATIVE
     assert plan(O.FP8_E5M2, 151936, 1) == c.PLAN_DECODE and plan(O.FP8_E5M2, 12288, 4) == c.PLAN_DECODE
     assert plan(O.FP8_E5M2, 151936, 33) == c.PLAN_STREAM
-    assert plan(O.FP4_E2M1, 28672, 1) == c.PLAN_NATIVE and plan(O.FP4_E2M1, 28672, 13) == c.PLAN_NATIVE
-    assert plan(O.FP4_E2M1, 4096, 1) == c.PLAN_DECODE and plan(O.FP4_E2M1, 28672, 14) == c.PLAN_STREAM
+    assert plan(O.FP4_E2M1, 28672, 1) == c.PLAN_NATIVE and plan(O.FP4_E2M1, 28672, 32) == c.PLAN_NATIVE
+    assert plan(O.FP4_E2M1, 4096, 1) == c.PLAN_DECODE and plan(O.FP4_E2M1, 28672, 33) == c.PLAN_STREAM
