@@ -208,42 +208,32 @@ static __global__ void __launch_bounds__(256) split_activations_kernel(const uin
 }
 
 // The parts of a tile that was cut across CTAs c_first .. c_last, added in that (k) order into v.  CTA c_first left its
-// part in its second slot, the others in their first.  The loads of eight parts and four tokens are issued together, so
-// that the CTA that arrived last waits for memory once per batch, not once per part; absent parts add an exact 0.
+// part in its second slot, the others in their first.  About 32 loads are issued together - every token of as many
+// parts as that allows - so that the CTA that arrived last waits for memory once per batch, not once per value;
+// absent parts add an exact 0.
 template <int TOK>
 __device__ __forceinline__ void nk_sum_parts(const float* __restrict__ partials, unsigned int M, unsigned int c_first, unsigned int c_last, unsigned int f,
     float (&v)[TOK])
 {
-    constexpr int TB = TOK < 4 ? TOK : 4, PB = 8;
+    constexpr int PB = TOK >= 32 ? 1 : (32 / TOK > 8 ? 8 : 32 / TOK);
 #pragma unroll
     for (int t = 0; t < TOK; t++) { v[t] = 0.f; }
-#pragma unroll
-    for (int t0 = 0; t0 < TOK; t0 += TB)
+    for (unsigned int c0 = c_first; c0 <= c_last; c0 += PB)
     {
-        if ((unsigned int)t0 >= M) { break; }
-        for (unsigned int c0 = c_first; c0 <= c_last; c0 += PB)
+        float tmp[PB][TOK];
+#pragma unroll
+        for (int i = 0; i < PB; i++)
         {
-            float tmp[PB][TB];
+            const unsigned int c = c0 + i;
+            const float* part = partials + (size_t)(2 * c + (c == c_first ? 1u : 0u)) * M * NK_BM;
 #pragma unroll
-            for (int i = 0; i < PB; i++)
-            {
-                const unsigned int c = c0 + i;
-                const float* part = partials + (size_t)(2 * c + (c == c_first ? 1u : 0u)) * M * NK_BM;
+            for (int t = 0; t < TOK; t++) { tmp[i][t] = (c <= c_last && (unsigned int)t < M) ? __ldcg(part + t * NK_BM + f) : 0.f; }
+        }
 #pragma unroll
-                for (int j = 0; j < TB; j++)
-                {
-                    tmp[i][j] = (c <= c_last && t0 + j < TOK && (unsigned int)(t0 + j) < M) ? __ldcg(part + (t0 + j) * NK_BM + f) : 0.f;
-                }
-            }
+        for (int i = 0; i < PB; i++)
+        {
 #pragma unroll
-            for (int i = 0; i < PB; i++)
-            {
-#pragma unroll
-                for (int j = 0; j < TB; j++)
-                {
-                    if (t0 + j < TOK) { v[t0 + j] += tmp[i][j]; }
-                }
-            }
+            for (int t = 0; t < TOK; t++) { v[t] += tmp[i][t]; }
         }
     }
 }
@@ -256,7 +246,9 @@ __device__ __forceinline__ void nk_sum_parts(const float* __restrict__ partials,
 // less on the critical path between the previous kernel's activations and this one's outputs; taken for few tokens,
 // where every CTA re-reading the rows costs little.
 template <int WT, int BNP, bool FUSED>
-__global__ void __launch_bounds__(FUSED ? NK_THREADS + 128 : NK_THREADS, 2) gemm_wq_native_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ StreamWMaps tmW, const NativeParams p)
+// (The bounds name 32 threads more than are launched: two CTAs then leave registers for a 256-thread block of the
+// kernel that comes next on the stream - the split of the next linear's activations - to start beside them.)
+__global__ void __launch_bounds__((FUSED ? NK_THREADS + 128 : NK_THREADS) + 32, 2) gemm_wq_native_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ StreamWMaps tmW, const NativeParams p)
 {
     constexpr int STAGES = nk_stages(BNP);
     constexpr int STAGE_BYTES = nk_stage_bytes(BNP);

@@ -162,7 +162,8 @@ struct NativeFp4Params
 // ---- the linear -------------------------------------------------------------------------------------------
 // BNP = UMMA N = 7 * tokens rounded up to a multiple of 16.
 template <int BNP>
-__global__ void __launch_bounds__(NF_THREADS, nf_wide(BNP) ? 1 : 2) gemm_wq_native_fp4_kernel(const __grid_constant__ NativeFp4Maps tm, const NativeParams p)
+// (the narrow shape's bounds name 32 threads more than are launched, see gemm_wq_native_kernel)
+__global__ void __launch_bounds__(nf_wide(BNP) ? NF_THREADS : NF_THREADS + 32, nf_wide(BNP) ? 1 : 2) gemm_wq_native_fp4_kernel(const __grid_constant__ NativeFp4Maps tm, const NativeParams p)
 {
     constexpr int STAGES = nf_stages(BNP);
     constexpr int STAGE_BYTES = nf_stage_bytes(BNP);
