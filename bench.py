@@ -244,8 +244,9 @@ def plan_step(capi, lin, bufs, M, world, grouped):
 def run_step(torch, dist, capi, wt, calls, bufs, M, world, flags):
     """One token's linears.  alpha keeps activation magnitudes steady through the random layers.
     With more than one rank, row-parallel linears (o, down) write FP32 partial sums, which are
-    all-reduced and rounded to BF16 once; the logits are all-gathered."""
-    n_launch = 0
+    all-reduced and rounded to BF16 once; the logits are all-gathered.  Returns the number of kernels the library
+    launched (its own counter: a call is one kernel, or two where the activations are split by a kernel of their own)."""
+    launched_before = capi.launch_count()
     for c in calls:
         fused = bufs.get("fused_row_linear") if c["row_parallel"] else None
         if fused is not None:
@@ -254,7 +255,6 @@ def run_step(torch, dist, capi, wt, calls, bufs, M, world, flags):
             rc = fused(wt, it["W"], it["S"], it["inv"], c["src"], c["dst"], it["N"], M, c["K"], alpha=it["alpha"], flags=flags)
             if rc != 0:
                 raise RuntimeError(f"fused linear {c['name']} failed: {rc}")
-            n_launch += 1
             continue
         if len(c["items"]) == 1:
             it = c["items"][0]
@@ -264,19 +264,17 @@ def run_step(torch, dist, capi, wt, calls, bufs, M, world, flags):
             rc = capi.gemm_wq_bf16_group(wt, c["group"], c["src"], M, c["K"], flags=flags)
         if rc != 0:
             raise RuntimeError(f"linear {c['name']} failed: {rc}")
-        n_launch += 1
         if c["row_parallel"]:
             ar = bufs.get("push_allreduce")
             if ar is not None:
                 if ar(bufs["partial"], c["dst"], bufs["partial"].numel(), flags=flags & 1) != 0:
                     raise RuntimeError("cuda_b200_allreduce_f32_to_bf16 failed")
-                n_launch += 1
             else:
                 dist.all_reduce(bufs["partial"])
                 c["dst"].copy_(bufs["partial"])
     if world > 1:
         dist.all_gather_into_tensor(bufs["logits_all"], bufs["logits"])
-    return n_launch
+    return capi.launch_count() - launched_before
 
 
 def build_chain_program(capi, wt, calls, M):
@@ -397,7 +395,9 @@ def time_decode_step(torch, dist, capi, model, dims, M, wtype, flags, reps, dev,
                     model.step_program(M)
             g = Direct()
         else:
-            n = model.step(M, flags)
+            launched_before = capi.launch_count()
+            model.step(M, flags)
+            n = capi.launch_count() - launched_before
             stream.synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):

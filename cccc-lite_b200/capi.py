@@ -19,7 +19,7 @@ FLAG_NO_STREAM = 0x800   # flags bit 11 of cuda_gemm_wq_bf16: the decode / prefi
 FLAG_STREAM = 7 << 8     # flags bits 8-10 = 7: the streaming kernel wherever it accepts the shape
 FLAG_NATIVE = 0x1000     # flags bit 12: FP8 weights straight into the tensor cores (1..32 tokens) wherever the kernel accepts the shape
 FLAG_NO_NATIVE = 0x2000  # flags bit 13: never that kernel
-FLAG_NATIVE_SPLIT_KERNEL = 0x4000  # flags bit 14: that kernel never splits the activations itself
+FLAG_NATIVE_FUSED = 0x4000  # flags bit 14: the FP8 native kernel splits the activations itself (up to 8 tokens)
 FLAG_PDL = 1
 FLAG_CHECKED = 2  # cuda_gemm_wq_bf16_static only
 FLAG_OUT_F32 = 4  # Y is float32 (partial sums of a row-parallel shard)

@@ -206,7 +206,13 @@ C_EXPORT int cuda_gemm_wq_bf16_plan(int w_type, const void* W, const void* blk_s
 {
     if (w_type != DT_E4M3 && w_type != DT_E5M2 && w_type != DT_FP4) { return -1; }
     const int plan = plan_for(w_type, W, blk_scales, X, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n);
-    if (plan != PLAN_PLAIN && native_by_default(w_type, M_tokens, (unsigned long long)N_out * K) && al16(W)
+    int sm_count = 148, dev = 0;    // without a device (the query reads no memory and runs on CPU-only hosts too): a B200's
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    {
+        cudaGetLastError();
+        sm_count = 148;
+    }
+    if (plan != PLAN_PLAIN && native_by_default(w_type, M_tokens, (unsigned long long)N_out * K, (N_out + NK_BM - 1) / NK_BM, sm_count) && al16(W)
         && (w_type == DT_FP4 ? native_fp4_supported(blk_scales, N_out, M_tokens, K, ldw, ldx) : native_supported(w_type, N_out, M_tokens, K, ldw, ldx)))
     {
         return PLAN_NATIVE;    // (an FP8 scale that is no power of two still goes to the kernels that dequantise)

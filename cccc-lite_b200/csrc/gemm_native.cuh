@@ -618,6 +618,19 @@ __global__ void __launch_bounds__((FUSED ? NK_THREADS + 128 : NK_THREADS) + 32, 
 }
 
 // ---- host side -----------------------------------------------------------------------------------------
+// CTAs of a launch.  With more feature tiles than CTA slots: one CTA per slot, the units dealt out evenly (tiles are cut
+// wherever a range ends; on such launches the exchange is a small share).  With fewer: every tile is cut into the same
+// number of parts, as many as the slots allow (one part = the whole tile and no exchange between half the slots and all
+// of them), so that no CTA works on two tiles and each meets the exchange once.  CTAs share HBM, not SMs: 192 whole-tile
+// CTAs on 148 SMs finish together.
+static inline unsigned int nk_grid(unsigned int tiles, unsigned int nkb, unsigned long long slots)
+{
+    if (tiles > slots) { return (unsigned int)slots; }
+    unsigned long long parts = slots / tiles;
+    if (parts > nkb) { parts = nkb; }
+    return (unsigned int)(tiles * parts);
+}
+
 inline bool native_supported(int w_type, unsigned int N, unsigned int M, unsigned int K, unsigned int ldw, unsigned int ldx)
 {
     if (w_type != DT_E4M3 && w_type != DT_E5M2) { return false; }
@@ -632,7 +645,7 @@ static int launch_native_bn(const void* X, unsigned int ldx, NativeParams& np, u
 {
     const unsigned long long U = (unsigned long long)np.tiles * np.nkb;
     if (U == 0 || U > 0x7FFFFFFFull) { return -2; }
-    const unsigned int grid = (unsigned int)(U < 2ull * (unsigned)sm_count ? U : 2ull * (unsigned)sm_count);
+    const unsigned int grid = nk_grid(np.tiles, np.nkb, 2ull * (unsigned)sm_count);
     // scratch memory: (the tokens' 2^-s and their pieces, when a kernel of its own writes them,) then two partial tiles per CTA
     const size_t piece_bytes = FUSED ? 0 : ((((size_t)BNP * np.K) + 1023) & ~(size_t)1023) + NK_SCALE_BYTES;
     const size_t part_bytes = (size_t)2 * grid * np.M * NK_BM * sizeof(float);

@@ -512,7 +512,7 @@ static int launch_native_fp4_bn(const void* X, unsigned int ldx, NativeParams& n
     const unsigned long long U = (unsigned long long)np.tiles * np.nkb;
     if (U == 0 || U > 0x7FFFFFFFull) { return -2; }
     const unsigned long long slots = (nf_wide(BNP) ? 1ull : 2ull) * (unsigned)sm_count;
-    const unsigned int grid = (unsigned int)(U < slots ? U : slots);
+    const unsigned int grid = nk_grid(np.tiles, np.nkb, slots);
     // BNP rows, those past 7 M zeroed by the split kernel: a TMA box with rows out of bounds is slow (measured: 88 us
     // instead of 56 us for 128256 x 4096 at one token, where 26 of a box's 32 rows were out of bounds)
     const size_t rows = (size_t)BNP;

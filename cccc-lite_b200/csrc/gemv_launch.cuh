@@ -209,32 +209,44 @@ constexpr unsigned int kFlagNoStream = 0x800u;
 // the shape; bit 13: never take it
 constexpr unsigned int kFlagNative = 0x1000u;
 constexpr unsigned int kFlagNoNative = 0x2000u;
-// flags bit 14: the native-operand kernel never splits the activations itself (a kernel of its own does, as for many tokens)
-constexpr unsigned int kFlagNativeSplitKernel = 0x4000u;
+// flags bit 14: the native-operand FP8 kernel splits the activations itself (up to 8 tokens) instead of a kernel of its
+// own doing it: the shortest path from activations to outputs for one linear alone
+constexpr unsigned int kFlagNativeFused = 0x4000u;
 
 static inline bool al16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
 
-// Where the native-operand kernels are the default.  Measured on B200 against the kernels that dequantise in registers:
-//   FP8: the decode kernel streams 151936 x 4096 at 0.90-0.92 of the measured copy bandwidth for 1-2 tokens but at
-//        0.78 / 0.72 / 0.69 for 4 / 16 / 32, the native kernel at 0.93-0.86 throughout; on a layer's own linears (16-100 MB)
-//        what one launch costs besides streaming dominates, and there the decode kernel's is smaller;
-//   FP4: the decode kernel's arithmetic holds it to 0.37-0.46 at every size; the native kernel reaches 0.81-0.84 on
-//        128256 x 4096 and wins from about 50 MB of weights (28672 x 4096 at one token: 20.7 us against 26.8 us).
+// Where the native-operand kernels are the default.  Measured on B200 against the kernels that dequantise in registers
+// (one linear in a CUDA graph of distinct weight copies, PDL):
+//   * streaming, they reach 0.93-0.86 (FP8, 1-32 tokens, 151936 x 4096) and 0.81-0.84 (FP4, 128256 x 4096) of the
+//     measured copy bandwidth, where the decode / streaming kernels reach 0.90 / 0.78 / 0.69 (FP8 at 1 / 4 / 32) and
+//     0.45 (FP4: the dequantising arithmetic is the bound);
+//   * one launch costs them more besides streaming (the activations' split, and the exchange of partial tiles when a
+//     128-feature tile has to be cut across CTAs): 4096 x 4096 FP8 at one token 8.0 us against 5.4 us;
+//   * no tile is cut when the launch has between one and two feature tiles per SM (every CTA takes one whole tile):
+//     24576 x 4096 FP8 at 1 / 4 / 16 / 32 tokens 20.8 / 20.9 / 22.0 / 25.5 us against 22.1 / 24.5 / 26.1 / 28.3 us,
+//     28672 x 4096 FP4 at 1 / 8 tokens 16.9 / 17.9 us against 26.8 / 28.5 us.
+// Hence: launches of whole tiles (gate+up as a group) and lm_head-sized ones; FP4 always, FP8 from 3 tokens (at 1-2 the
+// decode kernel is as fast on lm_head, and inside a whole decode step the two launches of the native form cost a
+// batch-1 step 50 us where the chain of linears alone gains 12 us).
 constexpr unsigned long long kNativeFp8MinBytes = 256ull << 20, kNativeFp4MinBytes = 48ull << 20;
 constexpr unsigned int kNativeFp8MinTokens = 3;
 
-static inline bool native_by_default(int w_type, unsigned int M, unsigned long long weight_elems)
+static inline bool native_by_default(int w_type, unsigned int M, unsigned long long weight_elems, unsigned int feature_tiles, int sm_count)
 {
-    if (w_type == DT_FP4) { return M <= (unsigned int)NF_MAX_TOKENS && weight_elems / 2 >= kNativeFp4MinBytes; }
-    return M >= kNativeFp8MinTokens && M <= (unsigned int)NK_MAX_TOKENS && weight_elems >= kNativeFp8MinBytes;
+    if (M > (unsigned int)(w_type == DT_FP4 ? NF_MAX_TOKENS : NK_MAX_TOKENS)) { return false; }
+    if (w_type != DT_FP4 && M < kNativeFp8MinTokens) { return false; }
+    const bool wide_fp4 = w_type == DT_FP4 && M > (unsigned int)NF_NARROW_TOKENS;    // one CTA per SM
+    if (!wide_fp4 && feature_tiles > (unsigned int)sm_count && feature_tiles <= 2u * (unsigned int)sm_count) { return true; }
+    return w_type == DT_FP4 ? weight_elems / 2 >= kNativeFp4MinBytes : weight_elems >= kNativeFp8MinBytes;
 }
 
-static inline bool want_native(unsigned int flags, int w_type, unsigned int M, unsigned long long weight_elems)
+static inline bool want_native(unsigned int flags, int w_type, unsigned int M, unsigned long long weight_elems, unsigned int feature_tiles,
+    int sm_count)
 {
     if ((flags & kFlagNoNative) != 0 || M > (unsigned int)(w_type == DT_FP4 ? NF_MAX_TOKENS : NK_MAX_TOKENS)) { return false; }
     const unsigned int variant = (flags >> 8) & 7u;
     if (variant != 0 || (flags & kFlagNoStream) != 0) { return false; }    // a particular older kernel was asked for
-    return (flags & kFlagNative) != 0 || native_by_default(w_type, M, weight_elems);
+    return (flags & kFlagNative) != 0 || native_by_default(w_type, M, weight_elems, feature_tiles, sm_count);
 }
 
 static int plan_base(int w_type, const void* W, const void* blk, const void* X, unsigned int N, unsigned int M, unsigned int K, unsigned int ldw,
@@ -314,12 +326,12 @@ static int run_linear_wq(const GemvScratch* ws, int w_type, const void* W, const
     p.out_f32 = (flags & 4u) ? 1u : ((flags & 8u) ? 2u : 0u);
     const bool pdl = (flags & 1u) != 0;
 
-    if (!decode_only && want_native(flags, w_type, M_tokens, (unsigned long long)N_out * K))
+    if (!decode_only && want_native(flags, w_type, M_tokens, (unsigned long long)N_out * K, (N_out + NK_BM - 1) / NK_BM, ws->sm_count))
     {
         const int r = w_type == DT_FP4
             ? launch_native_fp4(&p, 1, ws->partials, ws->partial_bytes, ws->counters, ws->n_counters, ws->device, ws->sm_count, st, pdl)
             : launch_native(w_type, &p, 1, ws->partials, ws->partial_bytes, ws->counters, ws->n_counters, ws->device, ws->sm_count, st, pdl,
-                  (flags & kFlagNativeSplitKernel) != 0);
+                  (flags & kFlagNativeFused) == 0);
         if (r != -2) { return r; }
     }
     int plan = plan_for(w_type, W, blk_scales, X, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n);
@@ -389,8 +401,13 @@ static int run_linear_wq_group(const GemvScratch* ws, int w_type, unsigned int c
     unsigned int M_tokens, unsigned int K, unsigned int ldx, cudaStream_t st, unsigned int flags)
 {
     unsigned long long group_elems = 0;
-    for (unsigned int j = 0; j < count; j++) { group_elems += (unsigned long long)items[j].N_out * K; }
-    if (count >= 1 && count <= (unsigned)PF_MAX_GROUP && want_native(flags, w_type, M_tokens, group_elems))
+    unsigned int group_tiles = 0;
+    for (unsigned int j = 0; j < count; j++)
+    {
+        group_elems += (unsigned long long)items[j].N_out * K;
+        group_tiles += (items[j].N_out + NK_BM - 1) / NK_BM;
+    }
+    if (count >= 1 && count <= (unsigned)PF_MAX_GROUP && want_native(flags, w_type, M_tokens, group_elems, group_tiles, ws->sm_count))
     {
         GemvParams ps[PF_MAX_GROUP];
         memset(ps, 0, sizeof(ps));
@@ -422,7 +439,7 @@ static int run_linear_wq_group(const GemvScratch* ws, int w_type, unsigned int c
             const int r = w_type == DT_FP4
                 ? launch_native_fp4(ps, count, ws->partials, ws->partial_bytes, ws->counters, ws->n_counters, ws->device, ws->sm_count, st, pdl)
                 : launch_native(w_type, ps, count, ws->partials, ws->partial_bytes, ws->counters, ws->n_counters, ws->device, ws->sm_count, st, pdl,
-                      (flags & kFlagNativeSplitKernel) != 0);
+                      (flags & kFlagNativeFused) == 0);
             if (r != -2) { return r; }
         }
     }

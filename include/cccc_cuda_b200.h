@@ -90,9 +90,11 @@ C_EXPORT void cuda_clear_last_error(void);
  * inv_scale and K % 128 == 0; FP4 up to 32 tokens with K % 256 == 0): the quantised weights go from HBM through
  * shared memory into tcgen05.mma (kind::f8f6f4, kind::mxf4nvf4 with the block scales) unchanged, the BF16
  * activations as a few narrow rows whose sum they are.  Without the bit it is taken where it is the fastest:
- * FP8 from 3 tokens and 256 MB of weights (lm_head), FP4 from 48 MB.  (FP4 block scales are read as UNSIGNED E4M3 there,
- * which is what the reference's converter writes; a token row with an infinity or NaN gives NaN outputs in the FP4 kernel.)  bit 13 = never that kernel.  bit 14 = that
- * kernel never splits the activations itself (a kernel of its own does, as it always does from 9 tokens). */
+ * launches with between one and two 128-feature tiles per SM (gate+up as a group: every CTA streams one whole tile,
+ * nothing is exchanged) and lm_head-sized ones (FP8 256 MB, FP4 48 MB of weights); FP8 only from 3 tokens.  (FP4 block scales are
+ * read as UNSIGNED E4M3 there, which is what the reference's converter writes; a token row with an infinity or NaN
+ * gives NaN outputs in the FP4 kernel.)  bit 13 = never that kernel.  bit 14 = the FP8 form of that kernel that splits
+ * the activations itself (up to 8 tokens) instead of a kernel of its own doing it before. */
 C_EXPORT int cuda_gemm_wq_bf16(int w_type, const void* W, const void* blk_scales, float inv_scale, const void* X,
     void* Y, unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx,
     unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta, void* stream, unsigned int flags);

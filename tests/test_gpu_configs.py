@@ -112,14 +112,33 @@ def subset(N, count, seed):
     return np.unique(np.concatenate([np.arange(edge), np.arange(N - edge, N), rng.integers(0, N, count)]))
 
 
+def native_by_default(wt, M, Ns, K):
+    """The dispatcher's rule for the native-operand kernels: launches of whole tiles (between one and two 128-feature
+    tiles per SM) and lm_head-sized ones (FP8 256 MB, FP4 48 MB of weights), up to 32 tokens, FP8 only from 3."""
+    import torch
+
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    tiles = sum((n + 127) // 128 for n in Ns)
+    elems = sum(Ns) * K
+    if M > 32 or (wt != O.FP4_E2M1 and M < 3):
+        return False
+    if sms < tiles <= 2 * sms and not (wt == O.FP4_E2M1 and M > 13):
+        return True
+    return elems // 2 >= 48 << 20 if wt == O.FP4_E2M1 else elems >= 256 << 20
+
+
+def is_pow2(x):
+    m, _ = np.frexp(x)
+    return m == 0.5
+
+
 def run_one(wt, N, K, M, seed, plan):
     import torch
 
     c = capi()
     if 9 <= M <= 128:
         plan = c.PLAN_STREAM    # the streaming tensor-core kernel takes these shapes from 9 to 128 tokens
-    # the native-operand kernels where they are the fastest: FP8 from 3 tokens and 256 MB of weights, FP4 from 48 MB
-    if (wt == O.FP4_E2M1 and M <= 32 and N * K // 2 >= 48 << 20) or (wt != O.FP4_E2M1 and 3 <= M <= 32 and N * K >= 256 << 20):
+    if native_by_default(wt, M, [N], K):
         plan = c.PLAN_NATIVE
     W, S, inv = device_weight(wt, N, K, seed)
     X = device_acts(M, K, seed)
@@ -197,10 +216,10 @@ def test_grouped_calls_of_the_benchmark(wt, members, M):
                           alpha=1.0 + 0.25 * j))
     before = c.launch_count()
     assert c.gemm_wq_bf16_group(wt, c.make_group(items, K), X, M, K) == 0 and c.check_error("group") == 0
-    # one launch for the group; the native-operand FP4 kernel (the group's weights are above 48 MB, up to 32 tokens)
-    # has the split of the activations as a launch of its own before it
-    native_fp4 = wt == O.FP4_E2M1 and M <= 32 and sum(it["N"] for it in items) * K // 2 >= 48 << 20
-    assert c.launch_count() - before == (2 if native_fp4 else 1)
+    # one launch for the group; before a native-operand kernel the split of the activations is a launch of its own
+    # (an FP8 scale that is no power of two keeps the kernels that dequantise)
+    native = native_by_default(wt, M, [it["N"] for it in items], K) and (wt == O.FP4_E2M1 or all(is_pow2(it["inv"]) for it in items))
+    assert c.launch_count() - before == (2 if native else 1)
     toks = None if M <= 32 else np.unique(np.concatenate([np.arange(0, M, 131), [M - 1]]))
     for it in items:
         check_against_oracle_subset(wt, it["W"], it["S"], it["inv"], X, it["Y"], it["N"], M, K, subset(it["N"], 150, M), toks,

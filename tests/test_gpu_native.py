@@ -1,8 +1,8 @@
 """The native-operand kernels: the quantised weight bytes go from HBM through TMA into shared memory and from there
 into the tensor cores unchanged - FP8 (1 .. 32 tokens) into tcgen05.mma kind::f8f6f4, FP4 with its E4M3 block scales
 (1 .. 32 tokens) into kind::mxf4nvf4 - and each BF16 activation row as three E5M2 rows (FP8) or seven E2M1 rows with
-power-of-two block scales (FP4) whose sum it is.  Up to 8 tokens the FP8 kernel splits the activations itself (one
-launch); otherwise a small kernel does (two launches; flags bit 14 asks for that form everywhere).
+power-of-two block scales (FP4) whose sum it is.  A small kernel writes those rows (two launches); with flags bit 14
+the FP8 kernel does it itself up to 8 tokens (one launch).
 Forced through flags bit 12, so that every shape the kernels accept is checked, not only those the dispatcher gives them.
 Against the CPU oracle at the GEMM bar (max relative error 1e-2 with the 1e-2 * rms floor, cosine >= 0.9999),
 bit for bit on one-hot activations (where the output IS the dequantised weight), and bit for bit between runs
@@ -18,13 +18,13 @@ pytestmark = pytest.mark.gpu
 
 WTS = [O.FP8_E5M2, O.FP8_E4M3]
 NATIVE = 0x1000
-SPLIT_KERNEL = 0x4000
-FORMS = [0, SPLIT_KERNEL]
+FUSED = 0x4000
+FORMS = [0, FUSED]
 
 
 def launches_of(wt, M, flags):
-    """The FP8 kernel splits the activations itself up to 8 tokens unless told otherwise."""
-    return 1 if (wt != O.FP4_E2M1 and M <= 8 and not (flags & SPLIT_KERNEL)) else 2
+    """The split of the activations is a launch of its own unless the FP8 kernel was asked to do it itself (up to 8 tokens)."""
+    return 1 if (wt != O.FP4_E2M1 and M <= 8 and (flags & FUSED)) else 2
 
 
 def run(wt, W, inv, X, N, M, K, Y0=None, blk=None, **kw):
@@ -54,7 +54,7 @@ def run(wt, W, inv, X, N, M, K, Y0=None, blk=None, **kw):
                                    (4096, 4096, 16), (128, 12288, 17), (2500, 1024, 32), (6144, 4096, 1), (100, 28672, 3)])
 def test_native_kernel_matches_oracle(wt, form, N, K, M):
     if form and M > 8:
-        pytest.skip("from 9 tokens there is only the form with the split kernel")
+        pytest.skip("the kernel splits the activations itself only up to 8 tokens")
     W, _, inv, X = O.make_inputs(wt, N, K, M, seed=N + M, scaled=False)
     Y = run(wt, W, inv, X, N, M, K, flags=form)
     _, y32 = O.linear_wq_bf16(wt, W, None, inv, X, N, M, K)
@@ -178,7 +178,7 @@ def test_native_alpha_beta_strides_and_output_modes(wt):
 
 @pytest.mark.parametrize("wt", WTS)
 @pytest.mark.parametrize("inv", [1.0, 0.25])
-@pytest.mark.parametrize("M,form", [(1, 0), (1, SPLIT_KERNEL), (5, 0), (8, SPLIT_KERNEL), (16, 0), (32, 0)])
+@pytest.mark.parametrize("M,form", [(1, 0), (1, FUSED), (5, FUSED), (8, 0), (16, 0), (32, 0)])
 def test_native_products_are_exact(wt, inv, M, form):
     N, K = 512, 512
     W = fp8_matrix(wt, N, K)
@@ -235,15 +235,17 @@ def test_same_bits_every_run_and_for_every_batch_size():
     for M in (1, 4, 9, 16):
         b = run(wt, W, inv, X[: M * K], N, M, K).reshape(M, N)
         assert np.array_equal(a[:M], b), M
-    b = run(wt, W, inv, X[: 4 * K], N, 4, K, flags=SPLIT_KERNEL).reshape(4, N)
+    b = run(wt, W, inv, X[: 4 * K], N, 4, K, flags=FUSED).reshape(4, N)
     assert np.array_equal(a[:4], b)    # whichever kernel splits the activations
 
 
 def test_the_dispatcher_takes_the_native_kernels_where_they_are_the_fastest():
-    """FP8 from 3 tokens and 256 MB of weights (lm_head), FP4 from 48 MB; never with the older kernels asked for."""
+    """Launches of whole tiles (between one and two 128-feature tiles per SM: gate+up) and lm_head-sized ones (FP8 256 MB,
+    FP4 48 MB of weights); FP8 only from 3 tokens."""
     import torch
 
     c = capi()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
     X = torch.zeros(32 * 4096, dtype=torch.int16, device="cuda")
     W = torch.zeros(16, dtype=torch.uint8, device="cuda")    # the plan query reads no memory
     Y = torch.zeros(16, dtype=torch.int16, device="cuda")
@@ -251,5 +253,9 @@ def test_the_dispatcher_takes_the_native_kernels_where_they_are_the_fastest():
     assert plan(O.FP8_E5M2, 151936, 4) == c.PLAN_NATIVE and plan(O.FP8_E5M2, 151936, 32) == c.PLAN_NATIVE
     assert plan(O.FP8_E5M2, 151936, 1) == c.PLAN_DECODE and plan(O.FP8_E5M2, 12288, 4) == c.PLAN_DECODE
     assert plan(O.FP8_E5M2, 151936, 33) == c.PLAN_STREAM
+    whole = 128 * (sms + sms // 2)    # one and a half tiles per SM
+    assert plan(O.FP8_E5M2, whole, 3) == c.PLAN_NATIVE and plan(O.FP8_E5M2, whole, 32) == c.PLAN_NATIVE
+    assert plan(O.FP8_E5M2, whole, 2) == c.PLAN_DECODE and plan(O.FP8_E5M2, 128 * sms, 4) == c.PLAN_DECODE
+    assert plan(O.FP8_E5M2, 128 * (2 * sms + 1), 4) == c.PLAN_DECODE and plan(O.FP4_E2M1, whole, 1) == c.PLAN_NATIVE
     assert plan(O.FP4_E2M1, 28672, 1) == c.PLAN_NATIVE and plan(O.FP4_E2M1, 28672, 32) == c.PLAN_NATIVE
     assert plan(O.FP4_E2M1, 4096, 1) == c.PLAN_DECODE and plan(O.FP4_E2M1, 28672, 33) == c.PLAN_STREAM
