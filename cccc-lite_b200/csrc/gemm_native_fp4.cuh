@@ -154,11 +154,6 @@ static __global__ void __launch_bounds__(256) split_activations_fp4_kernel(const
     }
 }
 
-struct NativeFp4Params
-{
-    NativeParams base;
-};
-
 // ---- the linear -------------------------------------------------------------------------------------------
 // BNP = UMMA N = 7 * tokens rounded up to a multiple of 16.
 template <int BNP>
@@ -330,13 +325,11 @@ __global__ void __launch_bounds__(nf_wide(BNP) ? NF_THREADS : NF_THREADS + 32, n
         // sixteen-byte scale rows l, 32 + l, 64 + l, 96 + l.
         const unsigned int quarter = warp & 3u;
         const uint32_t lane_field = (quarter * 32u) << 16;
-        bool ok = true;
         for (unsigned int i = 0; i < n_units; i++)
         {
             const unsigned int s = i % STAGES;
             if (*abort_flag != 0 || !mbar_wait_bounded(full + s, (i / STAGES) & 1u))
             {
-                ok = false;
                 atomicMax(p.status, (unsigned int)ST_TIMEOUT_FULL);
                 *abort_flag = 1;
                 break;
@@ -370,7 +363,6 @@ __global__ void __launch_bounds__(nf_wide(BNP) ? NF_THREADS : NF_THREADS + 32, n
             __syncwarp();
             if (lane == 0) { mbar_arrive(sf_full + s); }
         }
-        (void)ok;
     }
     else
     {
