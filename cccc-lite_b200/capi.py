@@ -65,6 +65,8 @@ class WqLinear(C.Structure):
 
 
 SYMBOLS["cuda_gemm_wq_bf16_group"] = (_i, [_i, _u, C.POINTER(WqLinear), _vp, _u, _u, _u, _vp, _u])
+SYMBOLS["cuda_gemm_w8a8_bf16"] = (_i, [_vp, _f, _vp, _f, _vp, _u, _u, _u, _u, _u, _u, _u, _f, _f, _vp, _u])
+SYMBOLS["cuda_bf16_to_fp8e4m3_dynamic"] = (_i, [_vp, _vp, _u, _vp, _vp])
 
 
 
@@ -156,6 +158,22 @@ def gemm_wq_bf16(w_type: int, W, blk, inv_scale: float, X, Y, N: int, M: int, K:
     return lib().cuda_gemm_wq_bf16(w_type, _ptr(W), _ptr(blk), inv_scale, _ptr(X), _ptr(Y), N, M, K,
                                    K if ldw is None else ldw, K if ldx is None else ldx,
                                    N if ldy_m is None else ldy_m, ldy_n, alpha, beta, stream, flags)
+
+
+def gemm_w8a8_bf16(W, w_inv_scale: float, X, act_scale: float, Y, N: int, M: int, K: int, *, ldw: int | None = None,
+                   ldx: int | None = None, ldy_m: int | None = None, ldy_n: int = 1, alpha: float = 1.0, beta: float = 0.0,
+                   stream: int | None = None, flags: int = 0) -> int:
+    """W8A8 linear: E4M3 weights, BF16 activations quantised to E4M3 inside the call (act_scale > 0 static, 0 dynamic)."""
+    if stream is None:
+        import torch
+
+        stream = torch.cuda.current_stream().cuda_stream
+    return lib().cuda_gemm_w8a8_bf16(_ptr(W), w_inv_scale, _ptr(X), act_scale, _ptr(Y), N, M, K, K if ldw is None else ldw,
+                                     K if ldx is None else ldx, N if ldy_m is None else ldy_m, ldy_n, alpha, beta, stream, flags)
+
+
+def bf16_to_fp8e4m3_dynamic(src, dst, n: int, absmax_tmp, inv_scale_out) -> int:
+    return lib().cuda_bf16_to_fp8e4m3_dynamic(_ptr(src), _ptr(dst), n, _ptr(absmax_tmp), _ptr(inv_scale_out))
 
 
 def gemm_wq_bf16_static(w_type: int, W, blk, inv_scale: float, X, Y, N: int, M: int, K: int, *, ldw: int | None = None,

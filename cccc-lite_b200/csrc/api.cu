@@ -1,6 +1,7 @@
 // C-ABI of the fused quantized-weight linear and the library's host bookkeeping.
 #include "common.cuh"
 #include "gemv_launch.cuh"
+#include "gemm_w8a8.cuh"
 #include "../../include/cccc_cuda_b200.h"
 
 #include <atomic>
@@ -140,6 +141,36 @@ C_EXPORT int cuda_gemm_wq_bf16(int w_type, const void* W, const void* blk_scales
     }
     return run_linear_wq(&ws->scratch, w_type, W, blk_scales, inv_scale, X, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n, alpha,
         beta, (cudaStream_t)stream, flags);
+}
+
+C_EXPORT int cuda_gemm_w8a8_bf16(const void* W, float w_inv_scale, const void* X, float act_scale, void* Y, unsigned int N_out,
+    unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta,
+    void* stream, unsigned int flags)
+{
+    if (N_out == 0 || M_tokens == 0) { return 0; }
+    if (!W || !X || !Y) { return -1; }
+    Workspace* ws = workspace();
+    if (!ws)
+    {
+        fprintf(stderr, "gemm_w8a8_bf16 kernel launch failed: no workspace on this device\n");
+        return 1;
+    }
+    return launch_w8a8(&ws->scratch, W, w_inv_scale, X, act_scale, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n, alpha, beta,
+        (cudaStream_t)stream, flags);
+}
+
+C_EXPORT int cuda_bf16_to_fp8e4m3_dynamic(const void* src, void* dst_fp8, unsigned int n, void* d_absmax_tmp, void* d_inv_scale_out)
+{
+    if (n == 0) { return 0; }
+    if (!src || !dst_fp8 || !d_absmax_tmp || !d_inv_scale_out) { return -1; }
+    if (cudaMemsetAsync(d_absmax_tmp, 0, sizeof(float), 0) != cudaSuccess) { return report_launch("bf162fp8e4m3_dynamic") ? 1 : 0; }
+    unsigned int gx = (n + 255u) / 256u;
+    count_launch();
+    absmax_bf16_rows_kernel<<<dim3(gx > 1024u ? 1024u : gx, 1), 256>>>((const uint16_t*)src, n, n, 1, (float*)d_absmax_tmp);
+    count_launch();
+    quantise_activations_kernel<<<dim3(gx, 1), 256>>>((const uint16_t*)src, n, n, 1, (uint8_t*)dst_fp8, n, (const float*)d_absmax_tmp, 0.f, 0.f,
+        (float*)d_inv_scale_out, 1, false);
+    return report_launch("bf162fp8e4m3_dynamic");
 }
 
 C_EXPORT int cuda_gemm_wq_bf16_group(int w_type, unsigned int count, const cuda_wq_linear* linears, const void* X,

@@ -74,11 +74,11 @@ __device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t a_desc, uint64
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// Instruction descriptor, kind::f8f6f4: D = F32 (bits 4-5 = 1), A format at bits 7-9 (0 E4M3, 1 E5M2), B = E5M2
-// (bits 10-12 = 1), both K-major, N >> 3 at bits 17-22, M >> 4 at bits 24-28.
-__device__ __forceinline__ uint32_t umma_idesc_f8(bool a_e5m2, uint32_t m, uint32_t n)
+// Instruction descriptor, kind::f8f6f4: D = F32 (bits 4-5 = 1), A format at bits 7-9 and B format at bits 10-12
+// (0 E4M3, 1 E5M2), both K-major, N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+__device__ __forceinline__ uint32_t umma_idesc_f8(bool a_e5m2, bool b_e5m2, uint32_t m, uint32_t n)
 {
-    return (1u << 4) | ((a_e5m2 ? 1u : 0u) << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+    return (1u << 4) | ((a_e5m2 ? 1u : 0u) << 7) | ((b_e5m2 ? 1u : 0u) << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 __device__ __forceinline__ void tma_load_2d_hint(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar, uint64_t policy)
 {
@@ -245,7 +245,9 @@ __device__ __forceinline__ void nk_sum_parts(const float* __restrict__ partials,
 // needs - and write the three E5M2 rows into the stage's B tile in the layout the TMA would have produced.  One kernel
 // less on the critical path between the previous kernel's activations and this one's outputs; taken for few tokens,
 // where every CTA re-reading the rows costs little.
-template <int WT, int BNP, bool FUSED>
+// PIECES = 3: BF16 activations as three E5M2 rows per token (W8A16).  PIECES = 1: the activations ARE FP8 (E4M3, one row
+// per token, quantised with one scale for the whole tensor): the W8A8 linear of gemm_w8a8.cuh.
+template <int WT, int BNP, bool FUSED, int PIECES = 3>
 // (The bounds name 32 threads more than are launched: two CTAs then leave registers for a 256-thread block of the
 // kernel that comes next on the stream - the split of the next linear's activations - to start beside them.)
 __global__ void __launch_bounds__((FUSED ? NK_THREADS + 128 : NK_THREADS) + 32, 2) gemm_wq_native_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ StreamWMaps tmW, const NativeParams p)
@@ -254,7 +256,8 @@ __global__ void __launch_bounds__((FUSED ? NK_THREADS + 128 : NK_THREADS) + 32, 
     constexpr int STAGE_BYTES = nk_stage_bytes(BNP);
     constexpr int X_BYTES = nk_x_bytes(BNP);
     constexpr int TMEM_COLS = nk_tmem_cols(BNP);
-    constexpr int TOK = BNP / 3;    // tokens one accumulator holds
+    constexpr int TOK = BNP / PIECES;    // tokens one accumulator holds
+    static_assert(PIECES == 3 || (PIECES == 1 && !FUSED), "pieces");
     constexpr int ACCS = nk_accs(BNP);
     static_assert(STAGES >= 2 && STAGES <= 8, "ring depth");
     static_assert(ACCS * BNP <= TMEM_COLS && (NK_BK / 32) % ACCS == 0, "accumulators");
@@ -370,7 +373,7 @@ __global__ void __launch_bounds__((FUSED ? NK_THREADS + 128 : NK_THREADS) + 32, 
     else if (warp == 1)
     {
         // =========================== MMA warp ===========================
-        const uint32_t idesc = umma_idesc_f8(WT == DT_E5M2, NK_BM, BNP);
+        const uint32_t idesc = umma_idesc_f8(WT == DT_E5M2, PIECES == 3, NK_BM, BNP);
         unsigned int runs_done = 0;    // accumulations this CTA has handed to the epilogue
         bool ok = true;
         for (unsigned int i = 0; i < n_units && ok; i++)
@@ -545,7 +548,7 @@ __global__ void __launch_bounds__((FUSED ? NK_THREADS + 128 : NK_THREADS) + 32, 
                     }
                 }
 #pragma unroll
-                for (int t = 0; t < TOK; t++) { v[t] = (acc[3 * t] + acc[3 * t + 1]) + acc[3 * t + 2]; }
+                for (int t = 0; t < TOK; t++) { v[t] = PIECES == 3 ? (acc[PIECES * t] + acc[PIECES * t + PIECES / 2]) + acc[PIECES * t + PIECES - 1] : acc[t]; }
             }
             // the accumulator is in registers: the MMA warp may start the next tile
             tc_fence_before();

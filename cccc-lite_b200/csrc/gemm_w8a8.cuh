@@ -1,0 +1,172 @@
+// W8A8: E4M3 weights times E4M3 ACTIVATIONS (one scale for the whole activation tensor) with FP32 accumulation, the mode
+// the reference selects with act_data_type = FP8_E4M3 (cccc/cublas_real.h:619-666: quantise the BF16 activations, static
+// scale or dynamic absmax, then a cublasLt FP8 x FP8 matmul with both scales).  Here the quantised activations are one
+// E4M3 row per token of the native-operand FP8 kernel (gemm_native.cuh, PIECES = 1): both operands go into
+// tcgen05.mma kind::f8f6f4 as they are.
+#pragma once
+
+#include "gemm_native.cuh"
+
+namespace b200
+{
+
+constexpr int W8A8_MAX_TOKENS = 32;
+
+static inline int w8a8_launch_failed()
+{
+    report_launch("gemm_w8a8_bf16");
+    return 1;
+}
+
+// Largest |x| over a [rows][cols] BF16 tensor (leading dimension ld) into *absmax (zero before), as the reference's
+// absmax_bf16_kernel computes it (cccc-cuda/cuda_functions.cu:2611-2637): fmaxf over |x|, which skips NaN and keeps an
+// infinity.  Non-negative floats order as their bits, so the device-wide step is an integer atomicMax.
+static __global__ void __launch_bounds__(256) absmax_bf16_rows_kernel(const uint16_t* __restrict__ X, unsigned int ld, unsigned int cols,
+    unsigned int rows, float* __restrict__ absmax)
+{
+    __shared__ unsigned int warp_max[8];
+    const unsigned int tid = threadIdx.x;
+    unsigned int m = 0;
+    for (unsigned int r = blockIdx.y; r < rows; r += gridDim.y)
+    {
+        const uint16_t* x = X + (size_t)r * ld;
+        for (unsigned int i = blockIdx.x * 256 + tid; i < cols; i += gridDim.x * 256)
+        {
+            const unsigned int b = x[i] & 0x7FFFu;
+            if (b <= 0x7F80u) { m = max(m, b); }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o)); }
+    if ((tid & 31u) == 0) { warp_max[tid >> 5] = m; }
+    __syncthreads();
+    if (tid == 0)
+    {
+#pragma unroll
+        for (int w = 1; w < 8; w++) { m = max(m, warp_max[w]); }
+        atomicMax(reinterpret_cast<unsigned int*>(absmax), m << 16);
+    }
+}
+
+// BF16 -> E4M3 with the reference's encoder (float_to_e4m3, cuda_functions.cu:2551-2580).  Dynamic (fwd_static == 0):
+// scale = 448 / absmax, multiplier back = absmax / 448 (1 and 1 for an all-zero tensor), cuda_functions.cu:2640-2657;
+// static: fwd_static = 1 / act_scale, multiplier back = inv_static = act_scale (cublas_real.h:627-632).
+// Grid (column chunks, rows + padding rows): rows past `rows` are written as zeros.  inv_out[r] receives the multiplier
+// back for each of the first n_inv rows (the linear reads one per token); pass n_inv = 1 for a single word.
+static __global__ void __launch_bounds__(256) quantise_activations_kernel(const uint16_t* __restrict__ X, unsigned int ld, unsigned int cols,
+    unsigned int rows, uint8_t* __restrict__ Q, unsigned int ldq, const float* __restrict__ absmax, float fwd_static, float inv_static,
+    float* __restrict__ inv_out, unsigned int n_inv, bool pdl)
+{
+    if (pdl)
+    {
+        pdl_launch_dependents();
+        pdl_wait();
+    }
+    float fwd = fwd_static, inv = inv_static;
+    if (fwd_static == 0.f)
+    {
+        const float a = *absmax;
+        fwd = (a > 0.f) ? (448.0f / a) : 1.0f;
+        inv = (a > 0.f) ? (a / 448.0f) : 1.0f;
+    }
+    const unsigned int r = blockIdx.y, i = blockIdx.x * 256 + threadIdx.x;
+    if (blockIdx.x == 0 && threadIdx.x == 0 && r < n_inv) { inv_out[r] = inv; }
+    if (i >= cols) { return; }
+    Q[(size_t)r * ldq + i] = r < rows ? float_to_e4m3(bf16_bits_to_float(X[(size_t)r * ld + i]), fwd) : (uint8_t)0;
+}
+
+// The linear.  Returns the C-ABI code, -1 for what this path does not serve (more than 32 tokens, K % 128 != 0,
+// unaligned operands, a workspace that is too small).
+static int launch_w8a8(const GemvScratch* ws, const void* W, float w_inv_scale, const void* X, float act_scale, void* Y, unsigned int N_out,
+    unsigned int M, unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta,
+    cudaStream_t stream, unsigned int flags)
+{
+    if (M == 0 || M > (unsigned int)W8A8_MAX_TOKENS || !native_supported(DT_E4M3, N_out, M, K, ldw, ldx) || !sk_al16(W) || act_scale < 0.f) { return -1; }
+    const unsigned int bnp = M <= 16 ? 16u : 32u;
+    NativeParams np;
+    memset(&np, 0, sizeof(np));
+    np.n_seg = 1;
+    np.status = ws->status;
+    np.M = M;
+    np.K = K;
+    np.out_f32 = (flags & 4u) ? 1u : ((flags & 8u) ? 2u : 0u);
+    np.counters = ws->counters;
+    np.nkb = K / NK_BK;
+    np.tiles = (N_out + NK_BM - 1) / NK_BM;
+    PrefillSeg& g = np.seg[0];
+    g.W = (const uint8_t*)W;
+    g.Y = (uint16_t*)Y;
+    g.N = N_out;
+    g.ldw = ldw;
+    g.ldy_m = ldy_m;
+    g.ldy_n = ldy_n;
+    g.alpha = alpha;
+    g.beta = beta;
+    g.w_scale = 1.0f;
+    g.post_scale = w_inv_scale;    // both scales multiply the FP32 sums, as cublasLt's scale pointers do
+    const unsigned int grid = nk_grid(np.tiles, np.nkb, 2ull * (unsigned)ws->sm_count);
+    // scratch: [0, 1024): the multipliers back (one per token) and, at float 255, the absmax word; then the E4M3 rows; then partial tiles
+    unsigned char* sc = reinterpret_cast<unsigned char*>(ws->partials);
+    const size_t q_bytes = (((size_t)bnp * K) + 1023) & ~(size_t)1023;
+    const size_t part_bytes = (size_t)2 * grid * M * NK_BM * sizeof(float);
+    if (!sc || NK_SCALE_BYTES + q_bytes + part_bytes > ws->partial_bytes || grid > ws->n_counters || ((uintptr_t)sc & 255u) != 0) { return -1; }
+    float* inv = reinterpret_cast<float*>(sc);
+    float* absmax = inv + 255;
+    uint8_t* Q = sc + NK_SCALE_BYTES;
+    np.inv_scale = inv;
+    np.partials = reinterpret_cast<float*>(Q + q_bytes);
+    CUtensorMap tmX;
+    StreamWMaps tmW;
+    memset(&tmW, 0, sizeof(tmW));
+    bool ok = make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Q, K, bnp, K, NK_BK, bnp, true);
+    for (int j = 0; j < PF_MAX_GROUP && ok; j++) { ok = make_map_2d(&tmW.w[j], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, K, N_out, ldw, NK_BK, NK_BM, true); }
+    if (!ok) { return -1; }
+    const bool pdl = (flags & 1u) != 0;
+    const bool dynamic = act_scale == 0.f;
+    if (dynamic)
+    {
+        if (cudaMemsetAsync(absmax, 0, sizeof(float), stream) != cudaSuccess) { return w8a8_launch_failed(); }
+        unsigned int gx = (K + 255) / 256;
+        if (gx > 64) { gx = 64; }
+        count_launch();
+        absmax_bf16_rows_kernel<<<dim3(gx, M), 256, 0, stream>>>((const uint16_t*)X, ldx, K, M, absmax);
+    }
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.gridDim = dim3((K + 255) / 256, bnp);
+    cfg.blockDim = dim3(256);
+    const bool q_pdl = pdl && !dynamic;    // behind the absmax kernel the quantiser is plainly ordered
+    cfg.numAttrs = q_pdl ? 1 : 0;
+    count_launch();
+    if (cudaLaunchKernelEx(&cfg, quantise_activations_kernel, (const uint16_t*)X, ldx, K, M, Q, K, (const float*)absmax,
+            dynamic ? 0.f : 1.0f / act_scale, dynamic ? 0.f : act_scale, inv, M, q_pdl)
+        != cudaSuccess)
+    {
+        return w8a8_launch_failed();
+    }
+    auto launch_linear = [&](auto kernel, int smem) -> int {
+        static std::atomic<bool> attr_set[2][64];
+        const int which = smem == nk_smem_bytes(16) ? 0 : 1;
+        if (!attr_set[which][ws->device].load(std::memory_order_acquire))
+        {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) { return w8a8_launch_failed(); }
+            attr_set[which][ws->device].store(true, std::memory_order_release);
+        }
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(NK_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.numAttrs = 1;    // its weight prefetch does not depend on the quantiser before it
+        count_launch();
+        if (cudaLaunchKernelEx(&cfg, kernel, tmX, tmW, np) != cudaSuccess) { return w8a8_launch_failed(); }
+        return 0;
+    };
+    return bnp == 16 ? launch_linear(gemm_wq_native_kernel<DT_E4M3, 16, false, 1>, nk_smem_bytes(16))
+                     : launch_linear(gemm_wq_native_kernel<DT_E4M3, 32, false, 1>, nk_smem_bytes(32));
+}
+
+}    // namespace b200

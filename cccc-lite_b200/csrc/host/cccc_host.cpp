@@ -86,7 +86,6 @@ void Cublas::gemm(MatrixTransType TransA, MatrixTransType TransB, int M, int N, 
     int lda, float invScaleA, const void* B, DataType typeB, int ldb, float invScaleB, float beta, void* C, DataType typeC,
     int ldc, float act_scale, const uint8_t* blk_scA, const uint8_t* blk_scB)
 {
-    (void)act_scale;
     const bool aQ = isQuantized(typeA), bQ = isQuantized(typeB);
     const cublasOperation_t opA = TransA == MATRIX_NO_TRANS ? CUBLAS_OP_N : CUBLAS_OP_T;
     const cublasOperation_t opB = TransB == MATRIX_NO_TRANS ? CUBLAS_OP_N : CUBLAS_OP_T;
@@ -105,6 +104,21 @@ void Cublas::gemm(MatrixTransType TransA, MatrixTransType TransB, int M, int N, 
         {
             LOG_ERR("Cublas::gemm: quantised weights need BF16 activations and output here (got %d, %d)\n", (int)typeX, (int)typeC);
             return;
+        }
+        // W8A8 (cublas_real.h:619-666, :692-739): E4M3 weights with the activation type set to FP8_E4M3.  The decode case
+        // (up to 32 tokens) is one call; anything it does not serve continues as W8A16, which is also where the
+        // reference ends up when its cublasLt call fails.
+        if (typeW == FP8_E4M3 && act_data_type_ == FP8_E4M3 && TransA == MATRIX_TRANS && TransB == MATRIX_NO_TRANS)
+        {
+            const int r = aQ ? cuda_gemm_w8a8_bf16(A, inv, B, act_scale, C, (unsigned)M, (unsigned)N, (unsigned)K, (unsigned)lda, (unsigned)ldb,
+                                   (unsigned)ldc, 1u, alpha, beta, stream_, 0)
+                             : cuda_gemm_w8a8_bf16(B, inv, A, act_scale, C, (unsigned)N, (unsigned)M, (unsigned)K, (unsigned)ldb, (unsigned)lda, 1u,
+                                   (unsigned)ldc, alpha, beta, stream_, 0);
+            if (r == 0)
+            {
+                fused_calls_++;
+                return;
+            }
         }
         // Fused path: the weight's K runs contiguously when it is op(A) = A^T (weight as A) or
         // op(B) = B (weight as B), and the activations' K is contiguous for the other operand.

@@ -89,6 +89,9 @@ public:
     // Largest |x| of n floats on the device, as Matrix::quantizeWeights finds it (cublasIsamax, cccc/Matrix.cpp:340-343).
     float absmax(const float* x, size_t n);
 
+    // W8A16 (BFLOAT16, the default) or W8A8 (FP8_E4M3): cccc/cublas_real.h:1228-1233
+    void setActDataType(DataType dt) { act_data_type_ = dt; }
+    DataType getActDataType() const { return act_data_type_; }
     int fusedCalls() const { return fused_calls_; }
     int fallbackCalls() const { return fallback_calls_; }
     float getLastFp8OutScale() const { return 1.0f; }
@@ -100,6 +103,7 @@ private:
     void* ws_ = nullptr;
     size_t ws_cap_ = 0;
     int fused_calls_ = 0, fallback_calls_ = 0;
+    DataType act_data_type_ = BFLOAT16;
 };
 
 // One per device.  The reference creates no stream (everything runs on the legacy default stream

@@ -22,6 +22,8 @@ HOST_EXPORT void cccc_host_gpu_destroy(void* g) { delete (GpuControl*)g; }
 HOST_EXPORT void cccc_host_gpu_sync(void* g) { ((GpuControl*)g)->synchronize(); }
 HOST_EXPORT int cccc_host_fused_calls(void* g) { return ((GpuControl*)g)->cublas_->fusedCalls(); }
 HOST_EXPORT int cccc_host_fallback_calls(void* g) { return ((GpuControl*)g)->cublas_->fallbackCalls(); }
+// W8A16 (BFLOAT16) or W8A8 (FP8_E4M3) for the quantised linears that follow: Cublas::setActDataType
+HOST_EXPORT void cccc_host_set_act_type(void* g, int dt) { ((GpuControl*)g)->cublas_->setActDataType((DataType)dt); }
 
 // Views over caller-owned device memory; dims are cccc's (width, height, channel, number).
 HOST_EXPORT void* cccc_host_matrix_view(void* g, void* data, int w, int h, int c, int n, int dt, float quant_scale, void* blk)

@@ -25,6 +25,7 @@ SYMBOLS = {
     "cccc_host_matrix_quant_scale": (_f, [_vp]),
     "cccc_host_matrix_dtype": (_i, [_vp]),
     "cccc_host_matrix_quantize": (None, [_vp, _i]),
+    "cccc_host_set_act_type": (None, [_vp, _i]),
     "cccc_host_mul": (None, [_vp, _vp, _vp, _f, _f, _i, _i]),
     "cccc_host_mul_batched": (None, [_vp, _vp, _vp, _i, _i, _f, _f]),
     "cccc_host_gemm": (None, [_vp, _i, _i, _i, _i, _i, _f, _vp, _i, _i, _f, _vp, _i, _i, _f, _f, _vp, _i, _i, _vp, _vp]),

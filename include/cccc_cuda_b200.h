@@ -120,6 +120,25 @@ typedef struct cuda_wq_linear
 C_EXPORT int cuda_gemm_wq_bf16_group(int w_type, unsigned int count, const cuda_wq_linear* linears, const void* X,
     unsigned int M_tokens, unsigned int K, unsigned int ldx, void* stream, unsigned int flags);
 
+/* W8A8: E4M3 weights times E4M3 activations with FP32 accumulation - the mode the reference's dispatcher takes when
+ * its activation type is FP8_E4M3 (cccc/cublas_real.h:619-666 and 692-739: quantise the BF16 activations, then a cublasLt
+ * FP8 x FP8 matmul with both scale pointers).  X is BF16 as there; this call quantises it itself:
+ *   act_scale > 0: static, q = e4m3(x / act_scale) and the multiplier back is act_scale (cublas_real.h:627-632);
+ *   act_scale == 0: dynamic, one absmax over the whole [M_tokens, K] tensor, q = e4m3(x * 448 / absmax), multiplier back
+ *                   absmax / 448 (cccc-cuda/cuda_functions.cu:2611-2669);
+ * and Y = alpha * w_inv_scale * multiplier * (W . q) + beta * Y (BF16, or float32 with flags bit 2; bit 3 and bit 0 as
+ * cuda_gemm_wq_bf16).  Both operands go into tcgen05.mma kind::f8f6f4 unchanged.  Serves the decode case: up to 32
+ * tokens, K % 128 == 0, ldw % 16 == 0, ldx % 8 == 0, 16-byte aligned W and X; anything else returns -1 (the caller keeps
+ * its own path).  Shares the device's workspace with cuda_gemm_wq_bf16: same ordering rule. */
+C_EXPORT int cuda_gemm_w8a8_bf16(const void* W, float w_inv_scale, const void* X, float act_scale, void* Y, unsigned int N_out,
+    unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m, unsigned int ldy_n, float alpha,
+    float beta, void* stream, unsigned int flags);
+
+/* Replaces cuda_bf16_to_fp8e4m3_dynamic (cccc-cuda/cuda_functions.h, cuda_functions.cu:2659-2669), same arguments and bits:
+ * absmax of n BF16 values into *d_absmax_tmp, dst = e4m3(src * 448 / absmax), *d_inv_scale_out = absmax / 448 (1 for an
+ * all-zero tensor).  On the legacy default stream like the reference's. */
+C_EXPORT int cuda_bf16_to_fp8e4m3_dynamic(const void* src, void* dst_fp8, unsigned int n, void* d_absmax_tmp, void* d_inv_scale_out);
+
 /* No counterpart in the reference.  The same linear as cuda_gemm_wq_bf16 for callers that cannot
  * allocate when they issue it: hosts that plan every byte of device memory up front (or have already
  * committed all of it) and hand the library no allocator, and latency-critical loops that may not take

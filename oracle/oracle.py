@@ -182,6 +182,34 @@ def linear_wq_bf16(w_type: int, W: np.ndarray, blk: np.ndarray | None, inv_scale
     return Y, y32
 
 
+def quantise_activations_e4m3(X: np.ndarray, act_scale: float = 0.0):
+    """BF16 bits -> (E4M3 bytes of the same shape, multiplier back) by the reference's W8A8 rules: act_scale > 0 is the
+    static form (q = e4m3(x * (1 / act_scale)), multiplier act_scale, cccc/cublas_real.h:627-632); 0 the dynamic one
+    (absmax by fmaxf, which skips NaN; q = e4m3(x * (448 / absmax)), multiplier absmax / 448; 1 and 1 for an all-zero
+    tensor: cccc-cuda/cuda_functions.cu:2611-2657).  All arithmetic in float32 as there."""
+    x = bf16_bits_to_f32(np.ascontiguousarray(X, np.uint16))
+    if act_scale > 0.0:
+        fwd, inv = np.float32(1.0) / np.float32(act_scale), np.float32(act_scale)
+    else:
+        mag = np.abs(x)
+        a = np.float32(np.max(np.where(np.isnan(mag), np.float32(0.0), mag))) if mag.size else np.float32(0.0)
+        fwd = np.float32(448.0) / a if a > 0 else np.float32(1.0)
+        inv = a / np.float32(448.0) if a > 0 else np.float32(1.0)
+    return float_to_fp8(x.reshape(-1), FP8_E4M3, float(fwd)).reshape(np.shape(X)), float(inv)
+
+
+def linear_w8a8(W: np.ndarray, w_inv_scale: float, X: np.ndarray, N: int, M: int, K: int, *, act_scale: float = 0.0,
+                alpha: float = 1.0):
+    """The W8A8 linear (cccc/cublas_real.h:619-666): E4M3 weights [N, K] times the E4M3-quantised activations [M, K],
+    both scales applied to the sums.  Returns (float64-accumulated float32 result [M, N], the quantised activations,
+    the activations' multiplier back)."""
+    q, inv = quantise_activations_e4m3(np.ascontiguousarray(X, np.uint16).reshape(M, K), act_scale)
+    wf = fp8_to_float(np.ascontiguousarray(W, np.uint8).reshape(-1), FP8_E4M3, 1.0).reshape(N, K).astype(np.float64)
+    xf = fp8_to_float(q.reshape(-1), FP8_E4M3, 1.0).reshape(M, K).astype(np.float64)
+    y = (xf @ wf.T) * (float(alpha) * float(np.float32(w_inv_scale)) * float(np.float32(inv)))
+    return y.astype(np.float32), q, inv
+
+
 def cpu_path_dequant_sgemm(w_type: int, W: np.ndarray, blk: np.ndarray | None, inv_scale: float, Xf: np.ndarray,
                            N: int, M: int, K: int, wf: np.ndarray | None = None):
     """The reference's CPU form of the path (dequantise to float, then sgemm).  Returns

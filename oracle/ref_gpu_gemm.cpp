@@ -38,6 +38,27 @@ extern "C" __attribute__((visibility("default"))) int ref_cublas_gemm(int transA
     return cudaDeviceSynchronize() == cudaSuccess ? 0 : 1;
 }
 
+// The reference's switch between W8A16 (BFLOAT16 activations, the default) and W8A8 (FP8_E4M3 activations):
+// cccc::Cublas::setActDataType (cccc/cublas_real.h:1233).
+extern "C" __attribute__((visibility("default"))) int ref_cublas_set_act_type(int type)
+{
+    if (ref_cublas_init()) { return 1; }
+    g_blas->setActDataType((cccc::DataType)type);
+    return 0;
+}
+
+// The typed overload the reference's W8A8 lives in (cccc/cublas_real.h:599-684: E4M3 weight as A, BF16 activations as B,
+// quantised to E4M3 inside when the activation type is FP8_E4M3).  The type-erased dispatcher above never reaches it
+// for BF16 activations (cublas_real.h:940-964 always dequantises), so it is called directly.
+extern "C" __attribute__((visibility("default"))) int ref_cublas_gemm_w8_typed(int transA, int transB, int M, int N, int K, float alpha,
+    const void* A, int lda, const void* B, int ldb, float beta, void* C, int ldc, float inv_scale, int weight_type, float act_scale)
+{
+    if (ref_cublas_init()) { return 1; }
+    g_blas->gemm((cccc::MatrixTransType)transA, (cccc::MatrixTransType)transB, M, N, K, alpha, (const uint8_t*)A, lda,
+        (const cccc::bfloat16*)B, ldb, beta, (cccc::bfloat16*)C, ldc, inv_scale, (cccc::DataType)weight_type, act_scale);
+    return cudaDeviceSynchronize() == cudaSuccess ? 0 : 1;
+}
+
 extern "C" __attribute__((visibility("default"))) void ref_cublas_destroy(void)
 {
     delete g_blas;

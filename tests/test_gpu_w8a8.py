@@ -1,0 +1,205 @@
+"""W8A8: E4M3 weights times E4M3-quantised activations (the reference's mode with act_data_type = FP8_E4M3,
+cccc/cublas_real.h:619-666).  The activation quantiser bit for bit against the reference's own kernels (compiled from
+its cuda_functions.cu) and against the CPU oracle; the linear (tcgen05.mma kind::f8f6f4 on both operands as they are)
+against the oracle at the GEMM bar (max relative error 1e-2 with the 1e-2 * rms floor, cosine >= 0.9999) and against
+the reference's own dispatcher running its cublasLt FP8 x FP8 matmul on the same device buffers."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests._util import assert_close, capi, from_dev_u16, ref_cuda_lib, ref_gemm_lib, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def acts(rng, M, K, spread=0.0):
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    if spread:
+        x *= np.exp2(rng.integers(-spread, spread, (M, K))).astype(np.float32)
+    return O.f32_to_bf16_bits(x)
+
+
+@pytest.mark.parametrize("n", [1, 255, 4096, 100_003])
+def test_dynamic_quantiser_matches_the_reference_s_kernels_and_the_oracle(n):
+    import torch
+
+    c = capi()
+    rng = np.random.default_rng(n)
+    X = acts(rng, 1, n, spread=6).reshape(-1)
+    if n > 300:
+        X[7] = 0x7FC0    # a NaN: fmaxf skips it in the absmax and the encoder writes 0x7F
+    dX = to_dev(X)
+    q = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    tmp = torch.full((1,), 7.0, dtype=torch.float32, device="cuda")
+    inv = torch.zeros(1, dtype=torch.float32, device="cuda")
+    assert c.bf16_to_fp8e4m3_dynamic(dX, q, n, tmp, inv) == 0 and c.check_error("quant") == 0
+    want_q, want_inv = O.quantise_activations_e4m3(X)
+    assert np.array_equal(q.cpu().numpy(), want_q)
+    assert np.float32(inv.item()) == np.float32(want_inv)
+    R = ref_cuda_lib()
+    if R is not None:
+        R.cuda_bf16_to_fp8e4m3_dynamic.restype = C.c_int
+        R.cuda_bf16_to_fp8e4m3_dynamic.argtypes = [C.c_void_p, C.c_void_p, C.c_uint, C.c_void_p, C.c_void_p]
+        q2 = torch.zeros(n, dtype=torch.uint8, device="cuda")
+        inv2 = torch.zeros(1, dtype=torch.float32, device="cuda")
+        assert R.cuda_bf16_to_fp8e4m3_dynamic(dX.data_ptr(), q2.data_ptr(), n, tmp.data_ptr(), inv2.data_ptr()) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(q, q2) and inv.item() == inv2.item()
+
+
+def test_dynamic_quantiser_on_zeros():
+    import torch
+
+    c = capi()
+    n = 512
+    dX = torch.zeros(n, dtype=torch.int16, device="cuda")
+    q = torch.full((n,), 9, dtype=torch.uint8, device="cuda")
+    tmp = torch.zeros(1, dtype=torch.float32, device="cuda")
+    inv = torch.zeros(1, dtype=torch.float32, device="cuda")
+    assert c.bf16_to_fp8e4m3_dynamic(dX, q, n, tmp, inv) == 0 and c.check_error("quant") == 0
+    assert int(q.max()) == 0 and inv.item() == 1.0
+
+
+def run(W, w_inv, X, act_scale, N, M, K, Y0=None, **kw):
+    import torch
+
+    c = capi()
+    dW, dX = to_dev(W), to_dev(X)
+    f32 = bool(kw.get("flags", 0) & 4)
+    ldy_m, ldy_n = kw.get("ldy_m", N), kw.get("ldy_n", 1)
+    size = (M - 1) * ldy_m + (N - 1) * ldy_n + 1
+    dY = to_dev(Y0) if Y0 is not None else torch.zeros(size, dtype=torch.float32 if f32 else torch.int16, device="cuda")
+    before = c.launch_count()
+    assert c.gemm_w8a8_bf16(dW, w_inv, dX, act_scale, dY, N, M, K, **kw) == 0 and c.check_error("w8a8") == 0
+    assert c.launch_count() - before == (2 if act_scale > 0 else 3)    # (absmax,) quantiser, linear
+    return dY.cpu().numpy() if f32 else from_dev_u16(dY)
+
+
+@pytest.mark.parametrize("act_scale", [0.0, 0.0123])
+@pytest.mark.parametrize("N,K,M", [(128, 128, 1), (256, 512, 2), (1000, 4096, 5), (4096, 4096, 16), (512, 2048, 17),
+                                   (2500, 1024, 32), (6144, 4096, 1), (100, 28672, 3), (24576, 4096, 4)])
+def test_w8a8_linear_matches_oracle(act_scale, N, K, M):
+    W, _, w_inv, X = O.make_inputs(O.FP8_E4M3, N, K, M, seed=N + M, scaled=True)
+    Y = run(W, w_inv, X, act_scale, N, M, K)
+    y32, _, _ = O.linear_w8a8(W, w_inv, X, N, M, K, act_scale=act_scale)
+    assert_close(O.bf16_bits_to_f32(Y).reshape(M, N), y32, (N, K, M, act_scale))
+
+
+def test_w8a8_float32_output_is_the_exact_sum():
+    """FP8 x FP8 products are exact in FP32 and so are the sums of a few thousand of them at these magnitudes: the
+    float32 output against the oracle's float64 sums."""
+    N, K, M = 1024, 4096, 8
+    W, _, w_inv, X = O.make_inputs(O.FP8_E4M3, N, K, M, seed=3, scaled=True)
+    Yf = run(W, w_inv, X, 0.0, N, M, K, flags=4).reshape(M, N)
+    y32, _, _ = O.linear_w8a8(W, w_inv, X, N, M, K)
+    rms = np.sqrt(np.mean(np.square(y32), axis=1, keepdims=True))
+    assert np.max(np.abs(Yf - y32) / np.maximum(np.abs(y32), rms)) < 1e-5
+
+
+def test_w8a8_alpha_beta_and_strides():
+    N, K, M = 200, 512, 20
+    ldw, ldx = K + 256, K + 8
+    rng = np.random.default_rng(3)
+    Wd, _, w_inv, Xd = O.make_inputs(O.FP8_E4M3, N, ldw, M, seed=13, scaled=True)
+    W = Wd.reshape(N, ldw)[:, :K].copy()
+    X = np.zeros((M, ldx), np.uint16)
+    X[:, :K] = Xd.reshape(M, ldw)[:, :K]
+    Y0 = O.f32_to_bf16_bits(rng.standard_normal((N, M + 3)).astype(np.float32))
+    Y = run(Wd, w_inv, X, 0.0, N, M, K, Y0=Y0.copy(), ldw=ldw, ldx=ldx, alpha=0.25, beta=1.5, ldy_m=1, ldy_n=M + 3)
+    y32, _, _ = O.linear_w8a8(W, w_inv, X[:, :K].copy(), N, M, K, alpha=0.25)
+    got = O.bf16_bits_to_f32(Y[:N * (M + 3)]).reshape(N, M + 3)
+    want = y32.T + 1.5 * O.bf16_bits_to_f32(Y0)[:, :M]
+    assert_close(got[:, :M].T.copy(), want.T.copy(), "alpha beta strides")
+    assert np.array_equal(got[:, M:], O.bf16_bits_to_f32(Y0)[:, M:])
+
+
+def test_w8a8_refuses_what_it_does_not_serve():
+    import torch
+
+    c = capi()
+    W = torch.zeros(256 * 256, dtype=torch.uint8, device="cuda")
+    X = torch.zeros(64 * 256, dtype=torch.int16, device="cuda")
+    Y = torch.zeros(64 * 256, dtype=torch.int16, device="cuda")
+    assert c.gemm_w8a8_bf16(W, 1.0, X, 0.0, Y, 256, 33, 256) == -1       # more than 32 tokens
+    assert c.gemm_w8a8_bf16(W, 1.0, X, 0.0, Y, 256, 4, 192) == -1        # K % 128
+    assert c.gemm_w8a8_bf16(W, 1.0, X, -1.0, Y, 256, 4, 256) == -1       # a negative activation scale
+    assert c.gemm_w8a8_bf16(W, 1.0, X, 0.0, Y, 0, 4, 256) == 0           # nothing to do
+
+
+@pytest.mark.parametrize("act_scale", [0.0, 0.02])
+@pytest.mark.parametrize("M", [1, 8, 32])
+def test_w8a8_against_the_reference_s_own_dispatcher(act_scale, M):
+    """cccc::Cublas::gemm's typed overload with the activation type set to FP8_E4M3 (cublasLt FP8 x FP8, both scale
+    pointers) on the same device buffers."""
+    import torch
+
+    R = ref_gemm_lib()
+    if R is None:
+        pytest.skip("oracle/_ref/libref_gpu_gemm.so not built")
+    R.ref_cublas_set_act_type.restype = C.c_int
+    R.ref_cublas_set_act_type.argtypes = [C.c_int]
+    c = capi()
+    N, K = 4096, 4096
+    W, _, w_inv, X = O.make_inputs(O.FP8_E4M3, N, K, M, seed=31 + M, scaled=True)
+    dW, dX = to_dev(W), to_dev(X)
+    ours = torch.zeros(M * N, dtype=torch.int16, device="cuda")
+    ref = torch.zeros(M * N, dtype=torch.int16, device="cuda")
+    assert c.gemm_w8a8_bf16(dW, w_inv, dX, act_scale, ours, N, M, K) == 0 and c.check_error("t") == 0
+    R.ref_cublas_gemm_w8_typed.restype = C.c_int
+    R.ref_cublas_gemm_w8_typed.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_int, C.c_void_p, C.c_int,
+                                           C.c_float, C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_float]
+    assert R.ref_cublas_set_act_type(O.FP8_E4M3) == 0
+    try:
+        # cccc's call: C(N x M, ldc N) = A^T (weight, lda K) * B (activations, ldb K), through the typed overload
+        rc = R.ref_cublas_gemm_w8_typed(1, 0, N, M, K, 1.0, dW.data_ptr(), K, dX.data_ptr(), K, 0.0, ref.data_ptr(), N, w_inv,
+                                        O.FP8_E4M3, act_scale)
+    finally:
+        R.ref_cublas_set_act_type(3)    # BFLOAT16 again: the library object is shared with other tests
+    assert rc == 0
+    a = O.bf16_bits_to_f32(from_dev_u16(ours)).reshape(M, N)
+    b = O.bf16_bits_to_f32(from_dev_u16(ref)).reshape(M, N)
+    y32, _, _ = O.linear_w8a8(W, w_inv, X, N, M, K, act_scale=act_scale)
+    assert_close(b, y32, "the reference's W8A8 against the oracle")
+    assert_close(a, b, "ours against the reference's W8A8")
+
+
+def test_the_host_dispatcher_takes_w8a8_when_its_activation_type_says_so():
+    """Matrix::mulBatched -> Cublas::gemm with setActDataType(FP8_E4M3), as cccc's MainProcess sets it for
+    weight_data_type = fp8_e4m3 (cccc/MainProcess.cpp:398-409): the W8A8 linear; back to BFLOAT16: W8A16 again."""
+    import torch
+
+    from __graft_entry__ import load_package
+
+    h = load_package().hostapi
+    L = h.lib()
+    g = L.cccc_host_gpu_create(0)
+    assert g
+    try:
+        N, K, M = 512, 1024, 4
+        W, _, inv, X = O.make_inputs(O.FP8_E4M3, N, K, M, seed=9, scaled=True)
+        dW, dX = to_dev(W), to_dev(X)
+        mW = L.cccc_host_matrix_view(g, dW.data_ptr(), K, N, 1, 1, O.FP8_E4M3, inv, None)
+        mX = L.cccc_host_matrix_view(g, dX.data_ptr(), K, M, 1, 1, O.BFLOAT16, 1.0, None)
+        outs = []
+        for act in (O.FP8_E4M3, O.BFLOAT16):
+            dY = torch.zeros(M * N, dtype=torch.int16, device="cuda")
+            mY = L.cccc_host_matrix_view(g, dY.data_ptr(), N, M, 1, 1, O.BFLOAT16, 1.0, None)
+            L.cccc_host_set_act_type(g, act)
+            before = L.cccc_host_fused_calls(g)
+            L.cccc_host_mul_batched(mW, mX, mY, h.MATRIX_TRANS, h.MATRIX_NO_TRANS, 1.0, 0.0)
+            L.cccc_host_gpu_sync(g)
+            assert L.cccc_host_fused_calls(g) == before + 1 and capi().check_error("host") == 0
+            outs.append(O.bf16_bits_to_f32(from_dev_u16(dY)).reshape(M, N))
+            L.cccc_host_matrix_free(mY)
+        y8, _, _ = O.linear_w8a8(W, inv, X, N, M, K)
+        _, y16 = O.linear_wq_bf16(O.FP8_E4M3, W, None, inv, X, N, M, K)
+        assert_close(outs[0], y8, "host W8A8")
+        assert_close(outs[1], y16, "host W8A16")
+        assert not np.array_equal(outs[0], outs[1])    # the activations' quantisation is visible
+        for m in (mW, mX):
+            L.cccc_host_matrix_free(m)
+    finally:
+        L.cccc_host_set_act_type(g, O.BFLOAT16)
+        L.cccc_host_gpu_destroy(g)
