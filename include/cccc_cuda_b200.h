@@ -134,6 +134,20 @@ C_EXPORT int cuda_gemm_w8a8_bf16(const void* W, float w_inv_scale, const void* X
     unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m, unsigned int ldy_n, float alpha,
     float beta, void* stream, unsigned int flags);
 
+/* The elementwise ops of the W8A8 mode on E4M3 tensors; they replace the entry points of the same names
+ * (cccc-cuda/cuda_functions.h:181-192, cuda_functions.cu:2446-2544) with the same arguments and bits: values widened to
+ * float, combined, narrowed with the round-to-nearest-even saturating conversion.  On the legacy default stream.
+ *   add:        R = a A + b B + r R            silu:  R = x * sigmoid(x)            elementmul: R = a A B + r R
+ *   addbias:    R = a bias[idx] + b R  (X already copied into R; idx = (i % (size_mc * size_b)) / size_mc, or i % size_b
+ *               when size_mc <= 1); _bf16bias takes a BF16 bias. */
+C_EXPORT int cuda_add_fp8e4m3(const void* A, const void* B, void* R, unsigned int n, float a, float b, float r);
+C_EXPORT int cuda_addbias_fp8e4m3(const void* X, const void* bias, void* R, unsigned int n, unsigned int size_mc, unsigned int size_b,
+    float a, float b);
+C_EXPORT int cuda_addbias_fp8e4m3_bf16bias(const void* X, const void* bias, void* R, unsigned int n, unsigned int size_mc,
+    unsigned int size_b, float a, float b);
+C_EXPORT int cuda_silu_fp8e4m3(const void* A, void* R, unsigned int n);
+C_EXPORT int cuda_elementmul_fp8e4m3(const void* A, const void* B, void* R, unsigned int n, float a, float r);
+
 /* Replaces cuda_bf16_to_fp8e4m3_dynamic (cccc-cuda/cuda_functions.h, cuda_functions.cu:2659-2669), same arguments and bits:
  * absmax of n BF16 values into *d_absmax_tmp, dst = e4m3(src * 448 / absmax), *d_inv_scale_out = absmax / 448 (1 for an
  * all-zero tensor).  On the legacy default stream like the reference's. */

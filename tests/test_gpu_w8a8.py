@@ -203,3 +203,50 @@ def test_the_host_dispatcher_takes_w8a8_when_its_activation_type_says_so():
     finally:
         L.cccc_host_set_act_type(g, O.BFLOAT16)
         L.cccc_host_gpu_destroy(g)
+
+
+@pytest.mark.parametrize("n", [1000, 4096, 65536 + 16])
+def test_fp8_elementwise_ops_match_the_reference_s_kernels(n):
+    """add, silu, elementmul, addbias (E4M3 and BF16 bias) on E4M3 tensors: the same bytes as the reference's kernels
+    (cccc-cuda/cuda_functions.cu:2446-2544), NaN bytes and saturation included; n = 1000 takes the one-byte path,
+    the others sixteen bytes per thread."""
+    import torch
+
+    R = ref_cuda_lib()
+    if R is None:
+        pytest.skip("oracle/_ref/libcccc-cuda-ref.so not built")
+    L = capi().lib()
+    g = torch.Generator(device="cuda").manual_seed(n)
+    A = torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda", generator=g)
+    B = torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda", generator=g)
+    R0 = torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda", generator=g)
+    bias8 = torch.randint(0, 0x78, (64,), dtype=torch.uint8, device="cuda", generator=g)
+    bias16 = torch.randn(64, device="cuda", generator=g).to(torch.bfloat16)
+    sigs = {"cuda_add_fp8e4m3": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint, C.c_float, C.c_float, C.c_float],
+            "cuda_silu_fp8e4m3": [C.c_void_p, C.c_void_p, C.c_uint],
+            "cuda_elementmul_fp8e4m3": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint, C.c_float, C.c_float],
+            "cuda_addbias_fp8e4m3": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint, C.c_uint, C.c_uint, C.c_float, C.c_float],
+            "cuda_addbias_fp8e4m3_bf16bias": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint, C.c_uint, C.c_uint, C.c_float, C.c_float]}
+    for name, args in sigs.items():
+        getattr(R, name).restype = C.c_int
+        getattr(R, name).argtypes = args
+
+    def both(name, build_args):
+        outs = []
+        for lib_ in (L, R):
+            r = R0.clone()
+            assert getattr(lib_, name)(*build_args(r)) == 0
+            torch.cuda.synchronize()
+            outs.append(r)
+        assert torch.equal(outs[0], outs[1]), name
+        return outs[0]
+
+    for a, b, r in ((1.0, 1.0, 0.0), (0.5, -2.0, 1.0), (100.0, 100.0, 0.25)):
+        both("cuda_add_fp8e4m3", lambda out: (A.data_ptr(), B.data_ptr(), out.data_ptr(), n, a, b, r))
+    both("cuda_silu_fp8e4m3", lambda out: (A.data_ptr(), out.data_ptr(), n))
+    for a, r in ((1.0, 0.0), (0.125, 1.0)):
+        both("cuda_elementmul_fp8e4m3", lambda out: (A.data_ptr(), B.data_ptr(), out.data_ptr(), n, a, r))
+    for size_mc, size_b in ((1, 64), (8, 50)):
+        both("cuda_addbias_fp8e4m3", lambda out: (None, bias8.data_ptr(), out.data_ptr(), n, size_mc, size_b, 1.0, 1.0))
+        both("cuda_addbias_fp8e4m3_bf16bias", lambda out: (None, bias16.data_ptr(), out.data_ptr(), n, size_mc, size_b, 0.5, 2.0))
+    assert capi().check_error("fp8 ops") == 0
