@@ -72,6 +72,8 @@ SYMBOLS["cuda_addbias_fp8e4m3"] = (_i, [_vp, _vp, _vp, _u, _u, _u, _f, _f])
 SYMBOLS["cuda_addbias_fp8e4m3_bf16bias"] = (_i, [_vp, _vp, _vp, _u, _u, _u, _f, _f])
 SYMBOLS["cuda_silu_fp8e4m3"] = (_i, [_vp, _vp, _u])
 SYMBOLS["cuda_elementmul_fp8e4m3"] = (_i, [_vp, _vp, _vp, _u, _f, _f])
+SYMBOLS["cuda_embed_fwd_fp8_to_fp8"] = (_i, [_vp, _vp, _vp, _i, _i, _i, _f])
+SYMBOLS["cuda_embed_fwd_bf16_to_fp8"] = (_i, [_vp, _vp, _vp, _i, _i, _i])
 
 
 

@@ -79,9 +79,59 @@ __global__ void __launch_bounds__(256) fp8_addbias_kernel(const Bias* __restrict
     R[i] = e4m3_narrow(a * fbias + fr);
 }
 
+// Embedding rows into an E4M3 activation tensor.  ids are FLOATS holding token numbers, as these two entry points of the
+// reference take them ([B][T]); one thread per four consecutive dimensions of a row when D % 4 == 0, else per element.
+// MODE 0: E4M3 table at inv_scale_w re-encoded at scale 1 with the hardware conversion (cuda_functions.cu:1615-1640);
+// MODE 1: BF16 table encoded with the reference's truncating E4M3 encoder at scale 1 (cuda_functions.cu:1642-1667).
+template <int MODE, int VEC>
+__global__ void __launch_bounds__(256) embed_to_fp8_kernel(const float* __restrict__ ids, const void* __restrict__ W, unsigned char* __restrict__ Y,
+    int D, long long total, float inv_scale_w)
+{
+    const long long idx = ((long long)blockIdx.x * 256 + threadIdx.x) * VEC;
+    if (idx >= total) { return; }
+    const int d = (int)(idx % D);
+    const long long row = idx / D;    // = t + b * T
+    const long long src = d + (long long)(int)ids[row] * D;
+    unsigned int out = 0;
+#pragma unroll
+    for (int e = 0; e < VEC; e++)
+    {
+        unsigned char q;
+        if (MODE == 0) { q = e4m3_narrow(e4m3_widen(reinterpret_cast<const unsigned char*>(W)[src + e]) * inv_scale_w); }
+        else { q = float_to_e4m3(bf16_bits_to_float(reinterpret_cast<const uint16_t*>(W)[src + e]), 1.0f); }
+        out |= (unsigned int)q << (8 * e);
+    }
+    if (VEC == 4) { *reinterpret_cast<unsigned int*>(Y + idx) = out; }
+    else { Y[idx] = (unsigned char)out; }
+}
+
+template <int MODE>
+static int launch_embed_to_fp8(const char* label, const void* ids, const void* W, void* Y, int D, int T, int B, float inv_scale_w)
+{
+    if (D <= 0 || T <= 0 || B <= 0) { return 0; }
+    if (!ids || !W || !Y) { return -1; }
+    const long long total = (long long)D * T * B;
+    const bool vec = (D % 4) == 0 && ((uintptr_t)Y & 3u) == 0;
+    const long long threads = vec ? total / 4 : total;
+    count_launch();
+    if (vec) { embed_to_fp8_kernel<MODE, 4><<<(unsigned int)((threads + 255) / 256), 256>>>((const float*)ids, W, (unsigned char*)Y, D, total, inv_scale_w); }
+    else { embed_to_fp8_kernel<MODE, 1><<<(unsigned int)((threads + 255) / 256), 256>>>((const float*)ids, W, (unsigned char*)Y, D, total, inv_scale_w); }
+    return report_launch(label);
+}
+
 }    // namespace b200
 
 using namespace b200;
+
+/* Replace cuda_embed_fwd_fp8_to_fp8 and cuda_embed_fwd_bf16_to_fp8 (cccc-cuda/cuda_functions.cu:1615-1667). */
+C_EXPORT int cuda_embed_fwd_fp8_to_fp8(const void* ids, const void* W, void* Y, int D, int T, int B, float inv_scale_w)
+{
+    return launch_embed_to_fp8<0>("embed_fwd_fp8_to_fp8", ids, W, Y, D, T, B, inv_scale_w);
+}
+C_EXPORT int cuda_embed_fwd_bf16_to_fp8(const void* ids, const void* W, void* Y, int D, int T, int B)
+{
+    return launch_embed_to_fp8<1>("embed_fwd_bf16_to_fp8", ids, W, Y, D, T, B, 1.0f);
+}
 
 /* Replaces cuda_add_fp8e4m3 (cccc-cuda/cuda_functions.cu:2446-2463): R = a A + b B + r R on E4M3 tensors. */
 C_EXPORT int cuda_add_fp8e4m3(const void* A, const void* B, void* R, unsigned int n, float a, float b, float r)

@@ -147,6 +147,11 @@ C_EXPORT int cuda_addbias_fp8e4m3_bf16bias(const void* X, const void* bias, void
     unsigned int size_b, float a, float b);
 C_EXPORT int cuda_silu_fp8e4m3(const void* A, void* R, unsigned int n);
 C_EXPORT int cuda_elementmul_fp8e4m3(const void* A, const void* B, void* R, unsigned int n, float a, float r);
+/* Embedding rows into an E4M3 activation tensor (cccc-cuda/cuda_functions.h:193-196, cuda_functions.cu:1615-1667), same
+ * arguments and bits: ids are floats holding token numbers, [B][T]; W is [vocab][D]; Y is [B][T][D].  fp8_to_fp8
+ * re-encodes an E4M3 table at inv_scale_w to scale 1; bf16_to_fp8 encodes a BF16 table at scale 1. */
+C_EXPORT int cuda_embed_fwd_fp8_to_fp8(const void* ids, const void* W, void* Y, int D, int T, int B, float inv_scale_w);
+C_EXPORT int cuda_embed_fwd_bf16_to_fp8(const void* ids, const void* W, void* Y, int D, int T, int B);
 
 /* Replaces cuda_bf16_to_fp8e4m3_dynamic (cccc-cuda/cuda_functions.h, cuda_functions.cu:2659-2669), same arguments and bits:
  * absmax of n BF16 values into *d_absmax_tmp, dst = e4m3(src * 448 / absmax), *d_inv_scale_out = absmax / 448 (1 for an

@@ -250,3 +250,36 @@ def test_fp8_elementwise_ops_match_the_reference_s_kernels(n):
         both("cuda_addbias_fp8e4m3", lambda out: (None, bias8.data_ptr(), out.data_ptr(), n, size_mc, size_b, 1.0, 1.0))
         both("cuda_addbias_fp8e4m3_bf16bias", lambda out: (None, bias16.data_ptr(), out.data_ptr(), n, size_mc, size_b, 0.5, 2.0))
     assert capi().check_error("fp8 ops") == 0
+
+
+@pytest.mark.parametrize("D", [64, 100])
+def test_fp8_embedding_variants_match_the_reference_s_kernels(D):
+    """cuda_embed_fwd_fp8_to_fp8 (E4M3 table re-encoded to scale 1) and cuda_embed_fwd_bf16_to_fp8 (BF16 table encoded
+    at scale 1), ids as floats: the same bytes as the reference's kernels (cccc-cuda/cuda_functions.cu:1615-1667);
+    D = 100 takes the one-byte path."""
+    import torch
+
+    R = ref_cuda_lib()
+    if R is None:
+        pytest.skip("oracle/_ref/libcccc-cuda-ref.so not built")
+    L = capi().lib()
+    T, B, vocab = 7, 3, 50
+    g = torch.Generator(device="cuda").manual_seed(D)
+    ids = torch.randint(0, vocab, (B, T), device="cuda", generator=g).to(torch.float32)
+    W8 = torch.randint(0, 256, (vocab, D), dtype=torch.uint8, device="cuda", generator=g)
+    W16 = (torch.randn(vocab, D, device="cuda", generator=g) * 100).to(torch.bfloat16)
+    for lib_ in (R,):
+        lib_.cuda_embed_fwd_fp8_to_fp8.restype = C.c_int
+        lib_.cuda_embed_fwd_fp8_to_fp8.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float]
+        lib_.cuda_embed_fwd_bf16_to_fp8.restype = C.c_int
+        lib_.cuda_embed_fwd_bf16_to_fp8.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+    outs = []
+    for lib_ in (L, R):
+        y8 = torch.full((B, T, D), 0x55, dtype=torch.uint8, device="cuda")
+        y16 = torch.full((B, T, D), 0x55, dtype=torch.uint8, device="cuda")
+        assert lib_.cuda_embed_fwd_fp8_to_fp8(ids.data_ptr(), W8.data_ptr(), y8.data_ptr(), D, T, B, 0.37) == 0
+        assert lib_.cuda_embed_fwd_bf16_to_fp8(ids.data_ptr(), W16.data_ptr(), y16.data_ptr(), D, T, B) == 0
+        torch.cuda.synchronize()
+        outs.append((y8, y16))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert capi().check_error("fp8 embed") == 0
