@@ -67,6 +67,7 @@ class WqLinear(C.Structure):
 SYMBOLS["cuda_gemm_wq_bf16_group"] = (_i, [_i, _u, C.POINTER(WqLinear), _vp, _u, _u, _u, _vp, _u])
 SYMBOLS["cuda_gemm_w8a8_bf16"] = (_i, [_vp, _f, _vp, _f, _vp, _u, _u, _u, _u, _u, _u, _u, _f, _f, _vp, _u])
 SYMBOLS["cuda_bf16_to_fp8e4m3_dynamic"] = (_i, [_vp, _vp, _u, _vp, _vp])
+SYMBOLS["cuda_gemm_fp8_fp8"] = (_i, [_vp, _f, _vp, _f, _vp, _i, _u, _u, _u, _u, _u, _u, _u, _f, _f, _vp, _u])
 SYMBOLS["cuda_add_fp8e4m3"] = (_i, [_vp, _vp, _vp, _u, _f, _f, _f])
 SYMBOLS["cuda_addbias_fp8e4m3"] = (_i, [_vp, _vp, _vp, _u, _u, _u, _f, _f])
 SYMBOLS["cuda_addbias_fp8e4m3_bf16bias"] = (_i, [_vp, _vp, _vp, _u, _u, _u, _f, _f])

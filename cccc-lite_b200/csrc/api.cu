@@ -159,6 +159,23 @@ C_EXPORT int cuda_gemm_w8a8_bf16(const void* W, float w_inv_scale, const void* X
         (cudaStream_t)stream, flags);
 }
 
+C_EXPORT int cuda_gemm_fp8_fp8(const void* W, float w_inv_scale, const void* X_fp8, float x_inv_scale, void* Y, int y_type, unsigned int N_out,
+    unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta,
+    void* stream, unsigned int flags)
+{
+    if (y_type != DT_BF16 && y_type != DT_E4M3) { return -1; }
+    if (N_out == 0 || M_tokens == 0) { return 0; }
+    if (!W || !X_fp8 || !Y) { return -1; }
+    Workspace* ws = workspace();
+    if (!ws)
+    {
+        fprintf(stderr, "gemm_fp8_fp8 kernel launch failed: no workspace on this device\n");
+        return 1;
+    }
+    return launch_w8a8(&ws->scratch, W, w_inv_scale, X_fp8, x_inv_scale, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n, alpha, beta,
+        (cudaStream_t)stream, flags & 1u, true, y_type == DT_E4M3);
+}
+
 C_EXPORT int cuda_bf16_to_fp8e4m3_dynamic(const void* src, void* dst_fp8, unsigned int n, void* d_absmax_tmp, void* d_inv_scale_out)
 {
     if (n == 0) { return 0; }
@@ -169,7 +186,7 @@ C_EXPORT int cuda_bf16_to_fp8e4m3_dynamic(const void* src, void* dst_fp8, unsign
     absmax_bf16_rows_kernel<<<dim3(gx > 1024u ? 1024u : gx, 1), 256>>>((const uint16_t*)src, n, n, 1, (float*)d_absmax_tmp);
     count_launch();
     quantise_activations_kernel<<<dim3(gx, 1), 256>>>((const uint16_t*)src, n, n, 1, (uint8_t*)dst_fp8, n, (const float*)d_absmax_tmp, 0.f, 0.f,
-        (float*)d_inv_scale_out, 1, false);
+        (float*)d_inv_scale_out, 1, false, false);
     return report_launch("bf162fp8e4m3_dynamic");
 }
 

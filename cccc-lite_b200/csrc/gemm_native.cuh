@@ -54,7 +54,7 @@ struct NativeParams
     unsigned int n_seg;
     unsigned int* status;
     unsigned int M, K;
-    unsigned int out_f32;            // 0 BF16, 1 FP32, 2 BF16 with the product rounded before beta * Y
+    unsigned int out_f32;            // 0 BF16, 1 FP32, 2 BF16 with the product rounded before beta * Y, 3 E4M3 (PIECES = 1 only)
     unsigned int tiles;              // feature tiles of all members
     unsigned int nkb;                // 128-k blocks of one tile
     const float* inv_scale;          // [M]: 2^-s of each token
@@ -602,6 +602,12 @@ __global__ void __launch_bounds__((FUSED ? NK_THREADS + 128 : NK_THREADS) + 32, 
                         float* y = reinterpret_cast<float*>(g.Y) + yi;
                         if (g.beta != 0.f) { o += g.beta * *y; }
                         *y = o;
+                    }
+                    else if (PIECES == 1 && p.out_f32 == 3u)
+                    {
+                        // E4M3 output of the W8A8 mode: the BF16 result re-encoded at scale 1 with the reference's encoder,
+                        // beta ignored (cccc/cublas_real.h:787-834)
+                        reinterpret_cast<uint8_t*>(g.Y)[yi] = float_to_e4m3(__bfloat162float(__float2bfloat16_rn(o)), 1.0f);
                     }
                     else
                     {

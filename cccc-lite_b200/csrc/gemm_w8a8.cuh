@@ -55,12 +55,20 @@ static __global__ void __launch_bounds__(256) absmax_bf16_rows_kernel(const uint
 // back for each of the first n_inv rows (the linear reads one per token); pass n_inv = 1 for a single word.
 static __global__ void __launch_bounds__(256) quantise_activations_kernel(const uint16_t* __restrict__ X, unsigned int ld, unsigned int cols,
     unsigned int rows, uint8_t* __restrict__ Q, unsigned int ldq, const float* __restrict__ absmax, float fwd_static, float inv_static,
-    float* __restrict__ inv_out, unsigned int n_inv, bool pdl)
+    float* __restrict__ inv_out, unsigned int n_inv, bool pdl, bool src_is_e4m3)
 {
     if (pdl)
     {
         pdl_launch_dependents();
         pdl_wait();
+    }
+    if (src_is_e4m3)
+    {
+        // the activations are E4M3 already (ld in bytes): they are only moved into the padded rows the linear reads
+        const unsigned int r = blockIdx.y, i = blockIdx.x * 256 + threadIdx.x;
+        if (blockIdx.x == 0 && threadIdx.x == 0 && r < n_inv) { inv_out[r] = inv_static; }
+        if (i < cols) { Q[(size_t)r * ldq + i] = r < rows ? reinterpret_cast<const uint8_t*>(X)[(size_t)r * ld + i] : (uint8_t)0; }
+        return;
     }
     float fwd = fwd_static, inv = inv_static;
     if (fwd_static == 0.f)
@@ -77,11 +85,13 @@ static __global__ void __launch_bounds__(256) quantise_activations_kernel(const 
 
 // The linear.  Returns the C-ABI code, -1 for what this path does not serve (more than 32 tokens, K % 128 != 0,
 // unaligned operands, a workspace that is too small).
+// x_is_e4m3: X holds E4M3 bytes (ldx in bytes) whose multiplier back is act_scale (> 0); y_e4m3: Y receives E4M3 bytes.
 static int launch_w8a8(const GemvScratch* ws, const void* W, float w_inv_scale, const void* X, float act_scale, void* Y, unsigned int N_out,
     unsigned int M, unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta,
-    cudaStream_t stream, unsigned int flags)
+    cudaStream_t stream, unsigned int flags, bool x_is_e4m3 = false, bool y_e4m3 = false)
 {
-    if (M == 0 || M > (unsigned int)W8A8_MAX_TOKENS || !native_supported(DT_E4M3, N_out, M, K, ldw, ldx) || !sk_al16(W) || act_scale < 0.f) { return -1; }
+    if (M == 0 || M > (unsigned int)W8A8_MAX_TOKENS || !native_supported(DT_E4M3, N_out, M, K, ldw, x_is_e4m3 ? 8u : ldx) || !sk_al16(W) || act_scale < 0.f) { return -1; }
+    if (x_is_e4m3 && !(act_scale > 0.f)) { return -1; }
     const unsigned int bnp = M <= 16 ? 16u : 32u;
     NativeParams np;
     memset(&np, 0, sizeof(np));
@@ -89,7 +99,7 @@ static int launch_w8a8(const GemvScratch* ws, const void* W, float w_inv_scale, 
     np.status = ws->status;
     np.M = M;
     np.K = K;
-    np.out_f32 = (flags & 4u) ? 1u : ((flags & 8u) ? 2u : 0u);
+    np.out_f32 = y_e4m3 ? 3u : ((flags & 4u) ? 1u : ((flags & 8u) ? 2u : 0u));
     np.counters = ws->counters;
     np.nkb = K / NK_BK;
     np.tiles = (N_out + NK_BM - 1) / NK_BM;
@@ -122,7 +132,7 @@ static int launch_w8a8(const GemvScratch* ws, const void* W, float w_inv_scale, 
     for (int j = 0; j < PF_MAX_GROUP && ok; j++) { ok = make_map_2d(&tmW.w[j], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, K, N_out, ldw, NK_BK, NK_BM, true); }
     if (!ok) { return -1; }
     const bool pdl = (flags & 1u) != 0;
-    const bool dynamic = act_scale == 0.f;
+    const bool dynamic = act_scale == 0.f && !x_is_e4m3;
     if (dynamic)
     {
         if (cudaMemsetAsync(absmax, 0, sizeof(float), stream) != cudaSuccess) { return w8a8_launch_failed(); }
@@ -144,7 +154,7 @@ static int launch_w8a8(const GemvScratch* ws, const void* W, float w_inv_scale, 
     cfg.numAttrs = q_pdl ? 1 : 0;
     count_launch();
     if (cudaLaunchKernelEx(&cfg, quantise_activations_kernel, (const uint16_t*)X, ldx, K, M, Q, K, (const float*)absmax,
-            dynamic ? 0.f : 1.0f / act_scale, dynamic ? 0.f : act_scale, inv, M, q_pdl)
+            dynamic ? 0.f : 1.0f / act_scale, dynamic ? 0.f : act_scale, inv, M, q_pdl, x_is_e4m3)
         != cudaSuccess)
     {
         return w8a8_launch_failed();

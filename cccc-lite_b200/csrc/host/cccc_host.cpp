@@ -91,7 +91,16 @@ void Cublas::gemm(MatrixTransType TransA, MatrixTransType TransB, int M, int N, 
     const cublasOperation_t opB = TransB == MATRIX_NO_TRANS ? CUBLAS_OP_N : CUBLAS_OP_T;
     if (aQ && bQ)
     {
-        LOG_ERR("Cublas::gemm: both operands quantised (W8A8) is outside this library's path\n");
+        // Both operands E4M3 (cublas_real.h:883-897 -> :754-834): weight as op(A) = A^T, activations as B; BF16 or E4M3 out.
+        if (typeA == FP8_E4M3 && typeB == FP8_E4M3 && (typeC == BFLOAT16 || typeC == FP8_E4M3) && TransA == MATRIX_TRANS && TransB == MATRIX_NO_TRANS
+            && cuda_gemm_fp8_fp8(A, invScaleA, B, invScaleB, C, (int)typeC, (unsigned)M, (unsigned)N, (unsigned)K, (unsigned)lda, (unsigned)ldb,
+                   (unsigned)ldc, 1u, alpha, beta, stream_, 0)
+                == 0)
+        {
+            fused_calls_++;
+            return;
+        }
+        LOG_ERR("Cublas::gemm: both operands quantised is served for E4M3 x E4M3, weight transposed, up to 32 tokens only\n");
         return;
     }
     if (aQ || bQ)

@@ -153,6 +153,14 @@ C_EXPORT int cuda_elementmul_fp8e4m3(const void* A, const void* B, void* R, unsi
 C_EXPORT int cuda_embed_fwd_fp8_to_fp8(const void* ids, const void* W, void* Y, int D, int T, int B, float inv_scale_w);
 C_EXPORT int cuda_embed_fwd_bf16_to_fp8(const void* ids, const void* W, void* Y, int D, int T, int B);
 
+/* Both operands E4M3 already (cccc/cublas_real.h:754-834, the overloads Cublas::gemm takes when typeA and typeB are both
+ * quantised): Y = alpha * w_inv_scale * x_inv_scale * (W . X) with FP32 accumulation; y_type 3 (BF16; beta * Y added) or
+ * 4 (E4M3: the BF16 result re-encoded at scale 1 with the reference's encoder, beta ignored, as there).  X_fp8 is
+ * [M_tokens][ldx] bytes.  Limits and ordering as cuda_gemm_w8a8_bf16 (up to 32 tokens, else -1); flags bit 0 only. */
+C_EXPORT int cuda_gemm_fp8_fp8(const void* W, float w_inv_scale, const void* X_fp8, float x_inv_scale, void* Y, int y_type,
+    unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m,
+    unsigned int ldy_n, float alpha, float beta, void* stream, unsigned int flags);
+
 /* Replaces cuda_bf16_to_fp8e4m3_dynamic (cccc-cuda/cuda_functions.h, cuda_functions.cu:2659-2669), same arguments and bits:
  * absmax of n BF16 values into *d_absmax_tmp, dst = e4m3(src * 448 / absmax), *d_inv_scale_out = absmax / 448 (1 for an
  * all-zero tensor).  On the legacy default stream like the reference's. */

@@ -283,3 +283,49 @@ def test_fp8_embedding_variants_match_the_reference_s_kernels(D):
         outs.append((y8, y16))
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
     assert capi().check_error("fp8 embed") == 0
+
+
+@pytest.mark.parametrize("y_type", [3, 4])
+@pytest.mark.parametrize("N,K,M", [(512, 1024, 1), (4096, 4096, 8), (1000, 2048, 32)])
+def test_both_operands_e4m3_against_the_oracle_and_the_reference(y_type, N, K, M):
+    """cuda_gemm_fp8_fp8: weights and activations E4M3 already, output BF16 (3) or E4M3 (4: the BF16 result re-encoded at
+    scale 1).  Against float64 sums of the decoded operands, and against the reference's own overloads
+    (cccc/cublas_real.h:754-834) through its dispatcher."""
+    import torch
+
+    c = capi()
+    rng = np.random.default_rng(N + M + y_type)
+    W, _, w_inv, _ = O.make_inputs(O.FP8_E4M3, N, K, M, seed=N + M, scaled=True)
+    x_inv = 0.03125
+    Xq = O.float_to_fp8(rng.standard_normal(M * K).astype(np.float32), O.FP8_E4M3, 1.0 / x_inv)
+    wf = O.fp8_to_float(W, O.FP8_E4M3, 1.0).reshape(N, K).astype(np.float64)
+    xf = O.fp8_to_float(Xq, O.FP8_E4M3, 1.0).reshape(M, K).astype(np.float64)
+    y = ((xf @ wf.T) * (float(np.float32(w_inv)) * x_inv)).astype(np.float32)
+    dW, dX = to_dev(W), to_dev(Xq)
+    ours = torch.zeros(M * N, dtype=torch.int16 if y_type == 3 else torch.uint8, device="cuda")
+    assert c.lib().cuda_gemm_fp8_fp8(dW.data_ptr(), w_inv, dX.data_ptr(), x_inv, ours.data_ptr(), y_type, N, M, K, K, K, N, 1, 1.0, 0.0, None, 0) == 0
+    assert c.check_error("fp8 x fp8") == 0
+
+    def check_bytes(got, want_bytes, what):
+        # one E4M3 code is a 6-12 % step: sums that differ in their last bits may land on either side of a
+        # truncation boundary, so a few bytes may differ by one code
+        diff = np.abs(got.astype(np.int16) - want_bytes.astype(np.int16))
+        assert diff.max() <= 1 and np.mean(diff != 0) < 2e-3, (what, int(diff.max()), float(np.mean(diff != 0)))
+
+    if y_type == 3:
+        assert_close(O.bf16_bits_to_f32(from_dev_u16(ours)).reshape(M, N), y, "oracle")
+    else:
+        want = O.float_to_fp8(O.bf16_bits_to_f32(O.f32_to_bf16_bits(y)).reshape(-1), O.FP8_E4M3, 1.0)
+        check_bytes(ours.cpu().numpy(), want, "oracle")
+    R = ref_gemm_lib()
+    if R is None:
+        return
+    ref = torch.zeros(M * N, dtype=torch.int16 if y_type == 3 else torch.uint8, device="cuda")
+    # cccc's call: C(N x M, ldc N) = A^T (weight, lda K) * B (activations, ldb K)
+    rc = R.ref_cublas_gemm(1, 0, N, M, K, 1.0, dW.data_ptr(), O.FP8_E4M3, K, w_inv, dX.data_ptr(), O.FP8_E4M3, K, x_inv, 0.0,
+                           ref.data_ptr(), y_type, N, 0.0, None, None)
+    assert rc == 0
+    if y_type == 3:
+        assert_close(O.bf16_bits_to_f32(from_dev_u16(ours)).reshape(M, N), O.bf16_bits_to_f32(from_dev_u16(ref)).reshape(M, N), "reference")
+    else:
+        check_bytes(ours.cpu().numpy(), ref.cpu().numpy(), "reference")
