@@ -351,6 +351,45 @@ def time_chain(torch, capi, wt, lin, dims, M, wtype, flags, reps, dev, stream):
             "linears_tok_per_s": round(M / ms * 1e3, 1)}
 
 
+def time_w8a8_chain(torch, capi, lin, dims, M, flags, reps, dev, stream, act_scale):
+    """The same chain of linears in the reference's W8A8 mode: the weight bytes read as E4M3, the BF16 activations
+    quantised to E4M3 inside each call (act_scale > 0: static scale; 0: dynamic absmax), one cuda_gemm_w8a8_bf16 per
+    linear (253 calls).  CUDA-graph replay, CUDA events."""
+    bufs = chain_buffers(torch, dims, M, 1, dev)
+    calls = plan_step(capi, lin, bufs, M, 1, False)
+
+    def step():
+        before = capi.launch_count()
+        for c in calls:
+            it = c["items"][0]
+            rc = capi.gemm_w8a8_bf16(it["W"], it["inv"], c["src"], act_scale, it["Y"], it["N"], M, c["K"], alpha=it["alpha"], flags=flags & 1)
+            if rc != 0:
+                raise RuntimeError(f"w8a8 linear {c['name']} failed: {rc}")
+        return capi.launch_count() - before
+
+    with torch.cuda.stream(stream):
+        bufs["x"].normal_()
+        n = step()
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
+            step()
+        for _ in range(5):
+            g.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            g.replay()
+        e1.record(stream)
+        stream.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    b = step_bytes(dims, M, "e5m2")
+    peak = float(load_peaks().get("hbm_gbs", 6650.0))
+    gbs = b / ms / 1e6
+    return {"tokens": M, "act_scale": "static" if act_scale > 0 else "dynamic", "ms_per_step": round(ms, 4), "gbs": round(gbs, 1),
+            "frac": round(gbs / peak, 4), "launches_per_step": n, "linears_tok_per_s": round(M / ms * 1e3, 1)}
+
+
 def decode_step_model(torch, capi, dm, dims, wt, lin, world, rank, M_max, dev, bufs):
     """The whole-model decode step (configuration 5) around the chain's weights: norms, embedding table, RoPE
     tables (cccc/NetCifa.cpp:431-475), and a BF16 KV cache of CONTEXT rows per sequence filled with N(0,1)."""
@@ -652,6 +691,12 @@ def gpu_arm(args):
             if prog is not None:
                 out["run"]["by_launches"] = time_chain(torch, capi, wt, lin, dims, 1, args.wtype, flags, 40, dev, stream)
             out["decode_by_m"] = [time_chain(torch, capi, wt, lin, dims, m, args.wtype, flags, 40, dev, stream) for m in (4, 16, 32)]
+            try:
+                out["w8a8"] = {"workload": "the same 253 linears in the W8A8 mode (weight bytes read as E4M3, activations quantised to E4M3 "
+                                           "inside each call), one call per linear",
+                               "by_m": [time_w8a8_chain(torch, capi, lin, dims, m, flags, 40, dev, stream, a) for m, a in ((1, 0.05), (1, 0.0), (32, 0.05))]}
+            except Exception as e:
+                out["w8a8"] = {"error": f"{type(e).__name__}: {e}"}
             try:
                 out["ref_gpu"] = ref_gpu_probe(torch, capi, dims, dev)
             except Exception as e:
