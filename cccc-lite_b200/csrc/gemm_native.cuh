@@ -1,7 +1,7 @@
 // FP8-weight linear for 1 .. 32 tokens with the weights fed to the tensor cores AS THEY LIE IN MEMORY.
 //
-// The decode kernel turns every weight into BF16 in registers and multiplies it there; at one or two issue
-// slots per weight that arithmetic, not HBM, is what bounds it.  tcgen05.mma kind::f8f6f4 takes E4M3 and E5M2
+// The decode kernel turns every weight into BF16 in registers and multiplies it there; at about four issue
+// slots per weight that arithmetic, not HBM, is what bounds it from a few tokens on (and FP4 at every batch).  tcgen05.mma kind::f8f6f4 takes E4M3 and E5M2
 // operands directly and multiplies them exactly with FP32 accumulation, so here a TMA lane streams the weight
 // bytes into shared memory and the UMMA reads them from there: no thread ever touches a weight.
 //
@@ -13,8 +13,12 @@
 // columns of the UMMA's N dimension; the epilogue adds them and multiplies by 2^-s.  Every product the tensor
 // core forms is therefore the exact product of a weight and a piece of the BF16 activation.
 //
-// Work is dealt out stream-K fashion: the (feature tile, 128-k block) units of the whole launch, in order, are
-// cut into one equal range per CTA of a persistent grid of two CTAs per SM.  A tile that one CTA covers alone
+// With PIECES = 1 the same kernel is the W8A8 linear: the activations are E4M3 themselves, one row per token
+// (gemm_w8a8.cuh).
+//
+// Work: the (feature tile, 128-k block) units of the whole launch, in order, are cut into one range per CTA of a
+// persistent grid (nk_grid: whole tiles when the launch has one to two tiles per SM, equal parts of every tile when
+// it has fewer, equal ranges wherever they fall - stream-K - when it has more).  A tile that one CTA covers alone
 // is finished by it; a tile cut across CTAs leaves FP32 partial tiles in scratch memory and the CTA that
 // arrives last adds them in k order, so the bits do not depend on who was last.
 // Every wait is bounded; on expiry the status word is raised and the CTA stops issuing, frees its TMEM and returns.
