@@ -67,6 +67,7 @@ class WqLinear(C.Structure):
 SYMBOLS["cuda_gemm_wq_bf16_group"] = (_i, [_i, _u, C.POINTER(WqLinear), _vp, _u, _u, _u, _vp, _u])
 SYMBOLS["cuda_gemm_w8a8_bf16"] = (_i, [_vp, _f, _vp, _f, _vp, _u, _u, _u, _u, _u, _u, _u, _f, _f, _vp, _u])
 SYMBOLS["cuda_bf16_to_fp8e4m3_dynamic"] = (_i, [_vp, _vp, _u, _vp, _vp])
+SYMBOLS["cuda_gemm_w8a8_bf16_group"] = (_i, [_u, C.POINTER(WqLinear), _vp, _f, _u, _u, _u, _vp, _u])
 SYMBOLS["cuda_gemm_fp8_fp8"] = (_i, [_vp, _f, _vp, _f, _vp, _i, _u, _u, _u, _u, _u, _u, _u, _f, _f, _vp, _u])
 SYMBOLS["cuda_add_fp8e4m3"] = (_i, [_vp, _vp, _vp, _u, _f, _f, _f])
 SYMBOLS["cuda_addbias_fp8e4m3"] = (_i, [_vp, _vp, _vp, _u, _u, _u, _f, _f])
@@ -178,6 +179,16 @@ def gemm_w8a8_bf16(W, w_inv_scale: float, X, act_scale: float, Y, N: int, M: int
         stream = torch.cuda.current_stream().cuda_stream
     return lib().cuda_gemm_w8a8_bf16(_ptr(W), w_inv_scale, _ptr(X), act_scale, _ptr(Y), N, M, K, K if ldw is None else ldw,
                                      K if ldx is None else ldx, N if ldy_m is None else ldy_m, ldy_n, alpha, beta, stream, flags)
+
+
+def gemm_w8a8_bf16_group(group, X, act_scale: float, M: int, K: int, *, ldx: int | None = None, stream: int | None = None,
+                         flags: int = 0) -> int:
+    """Up to three W8A8 linears sharing X (`group` from make_group) in one call: one quantisation, one launch."""
+    if stream is None:
+        import torch
+
+        stream = torch.cuda.current_stream().cuda_stream
+    return lib().cuda_gemm_w8a8_bf16_group(len(group), group, _ptr(X), act_scale, M, K, K if ldx is None else ldx, stream, flags)
 
 
 def bf16_to_fp8e4m3_dynamic(src, dst, n: int, absmax_tmp, inv_scale_out) -> int:

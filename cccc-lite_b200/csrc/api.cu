@@ -155,8 +155,29 @@ C_EXPORT int cuda_gemm_w8a8_bf16(const void* W, float w_inv_scale, const void* X
         fprintf(stderr, "gemm_w8a8_bf16 kernel launch failed: no workspace on this device\n");
         return 1;
     }
-    return launch_w8a8(&ws->scratch, W, w_inv_scale, X, act_scale, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n, alpha, beta,
-        (cudaStream_t)stream, flags);
+    const W8A8Member m = { W, Y, w_inv_scale, alpha, beta, N_out, ldw, ldy_m, ldy_n };
+    return launch_w8a8(&ws->scratch, &m, 1, X, act_scale, M_tokens, K, ldx, (cudaStream_t)stream, flags);
+}
+
+C_EXPORT int cuda_gemm_w8a8_bf16_group(unsigned int count, const cuda_wq_linear* linears, const void* X, float act_scale, unsigned int M_tokens,
+    unsigned int K, unsigned int ldx, void* stream, unsigned int flags)
+{
+    if (count == 0 || M_tokens == 0) { return 0; }
+    if (!linears || !X || count > (unsigned int)PF_MAX_GROUP) { return -1; }
+    Workspace* ws = workspace();
+    if (!ws)
+    {
+        fprintf(stderr, "gemm_w8a8_bf16 kernel launch failed: no workspace on this device\n");
+        return 1;
+    }
+    W8A8Member m[PF_MAX_GROUP];
+    for (unsigned int j = 0; j < count; j++)
+    {
+        if (linears[j].N_out == 0) { return -1; }
+        m[j] = { linears[j].W, linears[j].Y, linears[j].inv_scale, linears[j].alpha, linears[j].beta, linears[j].N_out, linears[j].ldw,
+            linears[j].ldy_m, linears[j].ldy_n };
+    }
+    return launch_w8a8(&ws->scratch, m, count, X, act_scale, M_tokens, K, ldx, (cudaStream_t)stream, flags);
 }
 
 C_EXPORT int cuda_gemm_fp8_fp8(const void* W, float w_inv_scale, const void* X_fp8, float x_inv_scale, void* Y, int y_type, unsigned int N_out,
@@ -172,8 +193,8 @@ C_EXPORT int cuda_gemm_fp8_fp8(const void* W, float w_inv_scale, const void* X_f
         fprintf(stderr, "gemm_fp8_fp8 kernel launch failed: no workspace on this device\n");
         return 1;
     }
-    return launch_w8a8(&ws->scratch, W, w_inv_scale, X_fp8, x_inv_scale, Y, N_out, M_tokens, K, ldw, ldx, ldy_m, ldy_n, alpha, beta,
-        (cudaStream_t)stream, flags & 1u, true, y_type == DT_E4M3);
+    const W8A8Member m = { W, Y, w_inv_scale, alpha, beta, N_out, ldw, ldy_m, ldy_n };
+    return launch_w8a8(&ws->scratch, &m, 1, X_fp8, x_inv_scale, M_tokens, K, ldx, (cudaStream_t)stream, flags & 1u, true, y_type == DT_E4M3);
 }
 
 C_EXPORT int cuda_bf16_to_fp8e4m3_dynamic(const void* src, void* dst_fp8, unsigned int n, void* d_absmax_tmp, void* d_inv_scale_out)

@@ -83,37 +83,50 @@ static __global__ void __launch_bounds__(256) quantise_activations_kernel(const 
     Q[(size_t)r * ldq + i] = r < rows ? float_to_e4m3(bf16_bits_to_float(X[(size_t)r * ld + i]), fwd) : (uint8_t)0;
 }
 
-// The linear.  Returns the C-ABI code, -1 for what this path does not serve (more than 32 tokens, K % 128 != 0,
-// unaligned operands, a workspace that is too small).
-// x_is_e4m3: X holds E4M3 bytes (ldx in bytes) whose multiplier back is act_scale (> 0); y_e4m3: Y receives E4M3 bytes.
-static int launch_w8a8(const GemvScratch* ws, const void* W, float w_inv_scale, const void* X, float act_scale, void* Y, unsigned int N_out,
-    unsigned int M, unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m, unsigned int ldy_n, float alpha, float beta,
-    cudaStream_t stream, unsigned int flags, bool x_is_e4m3 = false, bool y_e4m3 = false)
+// One member of a W8A8 launch (up to PF_MAX_GROUP members share the activations and their quantisation).
+struct W8A8Member
 {
-    if (M == 0 || M > (unsigned int)W8A8_MAX_TOKENS || !native_supported(DT_E4M3, N_out, M, K, ldw, x_is_e4m3 ? 8u : ldx) || !sk_al16(W) || act_scale < 0.f) { return -1; }
+    const void* W;
+    void* Y;
+    float w_inv_scale, alpha, beta;
+    unsigned int N_out, ldw, ldy_m, ldy_n;
+};
+
+// The linear(s).  Returns the C-ABI code, -1 for what this path does not serve (more than 32 tokens, K % 128 != 0,
+// unaligned operands, more than three members, a workspace that is too small).
+// x_is_e4m3: X holds E4M3 bytes (ldx in bytes) whose multiplier back is act_scale (> 0); y_e4m3: Y receives E4M3 bytes.
+static int launch_w8a8(const GemvScratch* ws, const W8A8Member* mem, unsigned int count, const void* X, float act_scale, unsigned int M,
+    unsigned int K, unsigned int ldx, cudaStream_t stream, unsigned int flags, bool x_is_e4m3 = false, bool y_e4m3 = false)
+{
+    if (count == 0 || count > (unsigned int)PF_MAX_GROUP || M == 0 || M > (unsigned int)W8A8_MAX_TOKENS || act_scale < 0.f) { return -1; }
     if (x_is_e4m3 && !(act_scale > 0.f)) { return -1; }
     const unsigned int bnp = M <= 16 ? 16u : 32u;
     NativeParams np;
     memset(&np, 0, sizeof(np));
-    np.n_seg = 1;
+    np.n_seg = count;
     np.status = ws->status;
     np.M = M;
     np.K = K;
     np.out_f32 = y_e4m3 ? 3u : ((flags & 4u) ? 1u : ((flags & 8u) ? 2u : 0u));
     np.counters = ws->counters;
     np.nkb = K / NK_BK;
-    np.tiles = (N_out + NK_BM - 1) / NK_BM;
-    PrefillSeg& g = np.seg[0];
-    g.W = (const uint8_t*)W;
-    g.Y = (uint16_t*)Y;
-    g.N = N_out;
-    g.ldw = ldw;
-    g.ldy_m = ldy_m;
-    g.ldy_n = ldy_n;
-    g.alpha = alpha;
-    g.beta = beta;
-    g.w_scale = 1.0f;
-    g.post_scale = w_inv_scale;    // both scales multiply the FP32 sums, as cublasLt's scale pointers do
+    for (unsigned int j = 0; j < count; j++)
+    {
+        if (!mem[j].W || !mem[j].Y || !native_supported(DT_E4M3, mem[j].N_out, M, K, mem[j].ldw, x_is_e4m3 ? 8u : ldx) || !sk_al16(mem[j].W)) { return -1; }
+        PrefillSeg& g = np.seg[j];
+        g.W = (const uint8_t*)mem[j].W;
+        g.Y = (uint16_t*)mem[j].Y;
+        g.N = mem[j].N_out;
+        g.ldw = mem[j].ldw;
+        g.ldy_m = mem[j].ldy_m;
+        g.ldy_n = mem[j].ldy_n;
+        g.alpha = mem[j].alpha;
+        g.beta = mem[j].beta;
+        g.w_scale = 1.0f;
+        g.post_scale = mem[j].w_inv_scale;    // both scales multiply the FP32 sums, as cublasLt's scale pointers do
+        g.tile0 = np.tiles;
+        np.tiles += (mem[j].N_out + NK_BM - 1) / NK_BM;
+    }
     const unsigned int grid = nk_grid(np.tiles, np.nkb, 2ull * (unsigned)ws->sm_count);
     // scratch: [0, 1024): the multipliers back (one per token) and, at float 255, the absmax word; then the E4M3 rows; then partial tiles
     unsigned char* sc = reinterpret_cast<unsigned char*>(ws->partials);
@@ -129,7 +142,11 @@ static int launch_w8a8(const GemvScratch* ws, const void* W, float w_inv_scale, 
     StreamWMaps tmW;
     memset(&tmW, 0, sizeof(tmW));
     bool ok = make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Q, K, bnp, K, NK_BK, bnp, true);
-    for (int j = 0; j < PF_MAX_GROUP && ok; j++) { ok = make_map_2d(&tmW.w[j], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, K, N_out, ldw, NK_BK, NK_BM, true); }
+    for (unsigned int j = 0; j < (unsigned int)PF_MAX_GROUP && ok; j++)
+    {
+        const W8A8Member& m = mem[j < count ? j : 0];
+        ok = make_map_2d(&tmW.w[j], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, m.W, K, m.N_out, m.ldw, NK_BK, NK_BM, true);
+    }
     if (!ok) { return -1; }
     const bool pdl = (flags & 1u) != 0;
     const bool dynamic = act_scale == 0.f && !x_is_e4m3;

@@ -153,6 +153,13 @@ C_EXPORT int cuda_elementmul_fp8e4m3(const void* A, const void* B, void* R, unsi
 C_EXPORT int cuda_embed_fwd_fp8_to_fp8(const void* ids, const void* W, void* Y, int D, int T, int B, float inv_scale_w);
 C_EXPORT int cuda_embed_fwd_bf16_to_fp8(const void* ids, const void* W, void* Y, int D, int T, int B);
 
+/* Up to three W8A8 linears that read the same activations (q/k/v, gate/up) as one call: the activations are quantised
+ * once and the members' feature tiles are dealt out together.  Members as for cuda_gemm_wq_bf16_group (blk_scales
+ * unused); the result is that of `count` separate cuda_gemm_w8a8_bf16 calls, bit for bit.  -1 where one of those would
+ * return it, for more than three members, or for a member without outputs. */
+C_EXPORT int cuda_gemm_w8a8_bf16_group(unsigned int count, const cuda_wq_linear* linears, const void* X, float act_scale,
+    unsigned int M_tokens, unsigned int K, unsigned int ldx, void* stream, unsigned int flags);
+
 /* Both operands E4M3 already (cccc/cublas_real.h:754-834, the overloads Cublas::gemm takes when typeA and typeB are both
  * quantised): Y = alpha * w_inv_scale * x_inv_scale * (W . X) with FP32 accumulation; y_type 3 (BF16; beta * Y added) or
  * 4 (E4M3: the BF16 result re-encoded at scale 1 with the reference's encoder, beta ignored, as there).  X_fp8 is

@@ -329,3 +329,29 @@ def test_both_operands_e4m3_against_the_oracle_and_the_reference(y_type, N, K, M
         assert_close(O.bf16_bits_to_f32(from_dev_u16(ours)).reshape(M, N), O.bf16_bits_to_f32(from_dev_u16(ref)).reshape(M, N), "reference")
     else:
         check_bytes(ours.cpu().numpy(), ref.cpu().numpy(), "reference")
+
+
+@pytest.mark.parametrize("act_scale", [0.0, 0.04])
+@pytest.mark.parametrize("M", [1, 12, 32])
+def test_w8a8_group_is_one_quantisation_and_one_launch_with_the_bits_of_separate_calls(act_scale, M):
+    import torch
+
+    c = capi()
+    Ns, K = (512, 128, 160), 1024
+    X = None
+    items, host = [], []
+    for j, N in enumerate(Ns):
+        W, _, inv, Xj = O.make_inputs(O.FP8_E4M3, N, K, M, seed=3 + j, scaled=True)
+        X = Xj if X is None else X
+        host.append((W, inv, N))
+        items.append(dict(W=to_dev(W), S=None, inv=inv, N=N, Y=torch.zeros(M * N, dtype=torch.int16, device="cuda"), alpha=1.0 + 0.5 * j, beta=0.0))
+    dX = to_dev(X)
+    before = c.launch_count()
+    assert c.gemm_w8a8_bf16_group(c.make_group(items, K), dX, act_scale, M, K) == 0 and c.check_error("group") == 0
+    assert c.launch_count() - before == (2 if act_scale > 0 else 3)
+    for it, (W, inv, N) in zip(items, host):
+        sep = torch.zeros(M * N, dtype=torch.int16, device="cuda")
+        assert c.gemm_w8a8_bf16(it["W"], inv, dX, act_scale, sep, N, M, K, alpha=it["alpha"]) == 0 and c.check_error("sep") == 0
+        assert torch.equal(sep, it["Y"])
+        y32, _, _ = O.linear_w8a8(W, inv, X, N, M, K, act_scale=act_scale, alpha=it["alpha"])
+        assert_close(O.bf16_bits_to_f32(from_dev_u16(it["Y"])).reshape(M, N), y32, ("oracle", M, N))
