@@ -73,7 +73,38 @@ static __global__ void __launch_bounds__(256) quantise_activations_kernel(const 
     float fwd = fwd_static, inv = inv_static;
     if (fwd_static == 0.f)
     {
-        const float a = *absmax;
+        float a;
+        if (absmax) { a = *absmax; }
+        else
+        {
+            // a small tensor: every block that quantises finds the largest magnitude itself (eight values per load; the
+            // maximum does not depend on the order), which saves the memset and the absmax launch
+            __shared__ unsigned int warp_max[8];
+            unsigned int m = 0;
+            if (blockIdx.y < rows)
+            {
+                const unsigned int per_row = cols / 8;
+                for (unsigned int j = threadIdx.x; j < rows * per_row; j += 256)
+                {
+                    const uint4 v = *reinterpret_cast<const uint4*>(X + (size_t)(j / per_row) * ld + (size_t)(j % per_row) * 8);
+                    const unsigned int w[4] = { v.x, v.y, v.z, v.w };
+#pragma unroll
+                    for (int q = 0; q < 4; q++)
+                    {
+                        const unsigned int lo = w[q] & 0x7FFFu, hi = (w[q] >> 16) & 0x7FFFu;
+                        if (lo <= 0x7F80u) { m = max(m, lo); }
+                        if (hi <= 0x7F80u) { m = max(m, hi); }
+                    }
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) { m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, o)); }
+            if ((threadIdx.x & 31u) == 0) { warp_max[threadIdx.x >> 5] = m; }
+            __syncthreads();
+#pragma unroll
+            for (int w = 0; w < 8; w++) { m = max(m, warp_max[w]); }
+            a = __uint_as_float(m << 16);
+        }
         fwd = (a > 0.f) ? (448.0f / a) : 1.0f;
         inv = (a > 0.f) ? (a / 448.0f) : 1.0f;
     }
@@ -150,7 +181,9 @@ static int launch_w8a8(const GemvScratch* ws, const W8A8Member* mem, unsigned in
     if (!ok) { return -1; }
     const bool pdl = (flags & 1u) != 0;
     const bool dynamic = act_scale == 0.f && !x_is_e4m3;
-    if (dynamic)
+    // dynamic scale of a small tensor: the quantiser finds the maximum itself (16-byte loads: K and ldx % 8, an aligned base)
+    const bool self_absmax = dynamic && (size_t)M * K <= 16384 && (K % 8) == 0 && (ldx % 8) == 0 && sk_al16(X);
+    if (dynamic && !self_absmax)
     {
         if (cudaMemsetAsync(absmax, 0, sizeof(float), stream) != cudaSuccess) { return w8a8_launch_failed(); }
         unsigned int gx = (K + 255) / 256;
@@ -167,10 +200,10 @@ static int launch_w8a8(const GemvScratch* ws, const W8A8Member* mem, unsigned in
     cfg.attrs = attr;
     cfg.gridDim = dim3((K + 255) / 256, bnp);
     cfg.blockDim = dim3(256);
-    const bool q_pdl = pdl && !dynamic;    // behind the absmax kernel the quantiser is plainly ordered
+    const bool q_pdl = pdl && (!dynamic || self_absmax);    // behind the absmax kernel the quantiser is plainly ordered
     cfg.numAttrs = q_pdl ? 1 : 0;
     count_launch();
-    if (cudaLaunchKernelEx(&cfg, quantise_activations_kernel, (const uint16_t*)X, ldx, K, M, Q, K, (const float*)absmax,
+    if (cudaLaunchKernelEx(&cfg, quantise_activations_kernel, (const uint16_t*)X, ldx, K, M, Q, K, self_absmax ? (const float*)nullptr : (const float*)absmax,
             dynamic ? 0.f : 1.0f / act_scale, dynamic ? 0.f : act_scale, inv, M, q_pdl, x_is_e4m3)
         != cudaSuccess)
     {

@@ -73,7 +73,8 @@ def run(W, w_inv, X, act_scale, N, M, K, Y0=None, **kw):
     dY = to_dev(Y0) if Y0 is not None else torch.zeros(size, dtype=torch.float32 if f32 else torch.int16, device="cuda")
     before = c.launch_count()
     assert c.gemm_w8a8_bf16(dW, w_inv, dX, act_scale, dY, N, M, K, **kw) == 0 and c.check_error("w8a8") == 0
-    assert c.launch_count() - before == (2 if act_scale > 0 else 3)    # (absmax,) quantiser, linear
+    # quantiser, linear; the dynamic scale of more than 16384 activations takes an absmax launch of its own before them
+    assert c.launch_count() - before == (3 if act_scale == 0 and M * K > 16384 else 2)
     return dY.cpu().numpy() if f32 else from_dev_u16(dY)
 
 
@@ -348,7 +349,7 @@ def test_w8a8_group_is_one_quantisation_and_one_launch_with_the_bits_of_separate
     dX = to_dev(X)
     before = c.launch_count()
     assert c.gemm_w8a8_bf16_group(c.make_group(items, K), dX, act_scale, M, K) == 0 and c.check_error("group") == 0
-    assert c.launch_count() - before == (2 if act_scale > 0 else 3)
+    assert c.launch_count() - before == (3 if act_scale == 0 and M * K > 16384 else 2)
     for it, (W, inv, N) in zip(items, host):
         sep = torch.zeros(M * N, dtype=torch.int16, device="cuda")
         assert c.gemm_w8a8_bf16(it["W"], inv, dX, act_scale, sep, N, M, K, alpha=it["alpha"]) == 0 and c.check_error("sep") == 0
