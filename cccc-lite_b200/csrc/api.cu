@@ -17,7 +17,8 @@ void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 // ---- per-device workspace ------------------------------------------------------------------------
 // [0, 256)            status word (+ padding)
 // [256, 256 + 4 KB)   stream-K arrival counters, zero between launches
-// [8 KB, ...)         FP32 partial tiles
+// [8 KB, ...)         FP32 partial tiles; the native kernels' activation pieces; the W8A8 mode's quantised activations
+//                     (tokens x K bytes: 64 MB hold 4096 tokens of K = 16384)
 struct Workspace
 {
     std::atomic<unsigned char*> base{ nullptr };    // published last (release) once `scratch` is complete
@@ -26,7 +27,7 @@ struct Workspace
     GemvScratch scratch;
     unsigned int* status() const { return reinterpret_cast<unsigned int*>(base.load(std::memory_order_acquire)); }
 };
-constexpr size_t kPartialBytes = 16u << 20;
+constexpr size_t kPartialBytes = 64u << 20;
 static Workspace g_ws[kMaxDevices];
 static std::mutex g_ws_mutex;
 
@@ -156,7 +157,7 @@ C_EXPORT int cuda_gemm_w8a8_bf16(const void* W, float w_inv_scale, const void* X
         return 1;
     }
     const W8A8Member m = { W, Y, w_inv_scale, alpha, beta, N_out, ldw, ldy_m, ldy_n };
-    return launch_w8a8(&ws->scratch, &m, 1, X, act_scale, M_tokens, K, ldx, (cudaStream_t)stream, flags);
+    return launch_w8a8(&ws->scratch, &m, 1, X, act_scale, M_tokens, K, ldx, (cudaStream_t)stream, flags, false, false, (flags >> 8) & 3u);
 }
 
 C_EXPORT int cuda_gemm_w8a8_bf16_group(unsigned int count, const cuda_wq_linear* linears, const void* X, float act_scale, unsigned int M_tokens,
@@ -177,7 +178,7 @@ C_EXPORT int cuda_gemm_w8a8_bf16_group(unsigned int count, const cuda_wq_linear*
         m[j] = { linears[j].W, linears[j].Y, linears[j].inv_scale, linears[j].alpha, linears[j].beta, linears[j].N_out, linears[j].ldw,
             linears[j].ldy_m, linears[j].ldy_n };
     }
-    return launch_w8a8(&ws->scratch, m, count, X, act_scale, M_tokens, K, ldx, (cudaStream_t)stream, flags);
+    return launch_w8a8(&ws->scratch, m, count, X, act_scale, M_tokens, K, ldx, (cudaStream_t)stream, flags, false, false, (flags >> 8) & 3u);
 }
 
 C_EXPORT int cuda_gemm_fp8_fp8(const void* W, float w_inv_scale, const void* X_fp8, float x_inv_scale, void* Y, int y_type, unsigned int N_out,
@@ -194,7 +195,7 @@ C_EXPORT int cuda_gemm_fp8_fp8(const void* W, float w_inv_scale, const void* X_f
         return 1;
     }
     const W8A8Member m = { W, Y, w_inv_scale, alpha, beta, N_out, ldw, ldy_m, ldy_n };
-    return launch_w8a8(&ws->scratch, &m, 1, X_fp8, x_inv_scale, M_tokens, K, ldx, (cudaStream_t)stream, flags & 1u, true, y_type == DT_E4M3);
+    return launch_w8a8(&ws->scratch, &m, 1, X_fp8, x_inv_scale, M_tokens, K, ldx, (cudaStream_t)stream, flags & 1u, true, y_type == DT_E4M3, (flags >> 8) & 3u);
 }
 
 C_EXPORT int cuda_bf16_to_fp8e4m3_dynamic(const void* src, void* dst_fp8, unsigned int n, void* d_absmax_tmp, void* d_inv_scale_out)

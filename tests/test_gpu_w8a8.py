@@ -73,8 +73,8 @@ def run(W, w_inv, X, act_scale, N, M, K, Y0=None, **kw):
     dY = to_dev(Y0) if Y0 is not None else torch.zeros(size, dtype=torch.float32 if f32 else torch.int16, device="cuda")
     before = c.launch_count()
     assert c.gemm_w8a8_bf16(dW, w_inv, dX, act_scale, dY, N, M, K, **kw) == 0 and c.check_error("w8a8") == 0
-    # quantiser, linear; the dynamic scale of more than 16384 activations takes an absmax launch of its own before them
-    assert c.launch_count() - before == (3 if act_scale == 0 and M * K > 16384 else 2)
+    # quantiser, linear; the dynamic scale of more than 16384 activations (or 32 tokens) takes an absmax launch of its own before them
+    assert c.launch_count() - before == (3 if act_scale == 0 and (M * K > 16384 or M > 32) else 2)
     return dY.cpu().numpy() if f32 else from_dev_u16(dY)
 
 
@@ -86,6 +86,39 @@ def test_w8a8_linear_matches_oracle(act_scale, N, K, M):
     Y = run(W, w_inv, X, act_scale, N, M, K)
     y32, _, _ = O.linear_w8a8(W, w_inv, X, N, M, K, act_scale=act_scale)
     assert_close(O.bf16_bits_to_f32(Y).reshape(M, N), y32, (N, K, M, act_scale))
+
+
+@pytest.mark.parametrize("fh", [1, 2])
+@pytest.mark.parametrize("act_scale", [0.0, 0.0123])
+@pytest.mark.parametrize("N,K,M", [(256, 128, 33), (1000, 512, 100), (4096, 4096, 256), (1024, 2048, 300), (2500, 1024, 257),
+                                   (100, 12288, 48), (6144, 4096, 1024)])
+def test_w8a8_linear_above_32_tokens_matches_oracle(fh, act_scale, N, K, M):
+    """More than 32 tokens: the CTA-pair kernel, both tile shapes (flags bits 8-9: 256 or 512 features per pair), ragged
+    token and feature edges, TMA-stored tiles."""
+    W, _, w_inv, X = O.make_inputs(O.FP8_E4M3, N, K, M, seed=N + M, scaled=True)
+    Y = run(W, w_inv, X, act_scale, N, M, K, flags=fh << 8)
+    y32, _, _ = O.linear_w8a8(W, w_inv, X, N, M, K, act_scale=act_scale)
+    assert_close(O.bf16_bits_to_f32(Y).reshape(M, N), y32, (N, K, M, act_scale, fh))
+
+
+@pytest.mark.parametrize("fh", [1, 2])
+def test_w8a8_above_32_tokens_float32_strides_and_accumulate(fh):
+    """The element-by-element epilogue of the CTA-pair kernel: float32 output against float64 sums; transposed output with
+    alpha and beta."""
+    N, K, M = 700, 1024, 70
+    W, _, w_inv, X = O.make_inputs(O.FP8_E4M3, N, K, M, seed=5, scaled=True)
+    Yf = run(W, w_inv, X, 0.0, N, M, K, flags=4 | (fh << 8)).reshape(M, N)
+    y32, _, _ = O.linear_w8a8(W, w_inv, X, N, M, K)
+    rms = np.sqrt(np.mean(np.square(y32), axis=1, keepdims=True))
+    assert np.max(np.abs(Yf - y32) / np.maximum(np.abs(y32), rms)) < 1e-5
+    rng = np.random.default_rng(4)
+    Y0 = O.f32_to_bf16_bits(rng.standard_normal((N, M + 3)).astype(np.float32))
+    Y = run(W, w_inv, X, 0.0, N, M, K, Y0=Y0.copy(), alpha=0.25, beta=1.5, ldy_m=1, ldy_n=M + 3, flags=fh << 8)
+    ya, _, _ = O.linear_w8a8(W, w_inv, X, N, M, K, alpha=0.25)
+    got = O.bf16_bits_to_f32(Y[:N * (M + 3)]).reshape(N, M + 3)
+    want = ya.T + 1.5 * O.bf16_bits_to_f32(Y0)[:, :M]
+    assert_close(got[:, :M].T.copy(), want.T.copy(), "alpha beta strides")
+    assert np.array_equal(got[:, M:], O.bf16_bits_to_f32(Y0)[:, M:])
 
 
 def test_w8a8_float32_output_is_the_exact_sum():
@@ -123,14 +156,14 @@ def test_w8a8_refuses_what_it_does_not_serve():
     W = torch.zeros(256 * 256, dtype=torch.uint8, device="cuda")
     X = torch.zeros(64 * 256, dtype=torch.int16, device="cuda")
     Y = torch.zeros(64 * 256, dtype=torch.int16, device="cuda")
-    assert c.gemm_w8a8_bf16(W, 1.0, X, 0.0, Y, 256, 33, 256) == -1       # more than 32 tokens
+    assert c.gemm_w8a8_bf16(W, 1.0, X, 0.0, Y, 256, 33, 256) == 0 and c.check_error("33") == 0    # the CTA-pair kernel
     assert c.gemm_w8a8_bf16(W, 1.0, X, 0.0, Y, 256, 4, 192) == -1        # K % 128
     assert c.gemm_w8a8_bf16(W, 1.0, X, -1.0, Y, 256, 4, 256) == -1       # a negative activation scale
     assert c.gemm_w8a8_bf16(W, 1.0, X, 0.0, Y, 0, 4, 256) == 0           # nothing to do
 
 
 @pytest.mark.parametrize("act_scale", [0.0, 0.02])
-@pytest.mark.parametrize("M", [1, 8, 32])
+@pytest.mark.parametrize("M", [1, 8, 32, 64, 300, 2048])
 def test_w8a8_against_the_reference_s_own_dispatcher(act_scale, M):
     """cccc::Cublas::gemm's typed overload with the activation type set to FP8_E4M3 (cublasLt FP8 x FP8, both scale
     pointers) on the same device buffers."""
@@ -287,7 +320,7 @@ def test_fp8_embedding_variants_match_the_reference_s_kernels(D):
 
 
 @pytest.mark.parametrize("y_type", [3, 4])
-@pytest.mark.parametrize("N,K,M", [(512, 1024, 1), (4096, 4096, 8), (1000, 2048, 32)])
+@pytest.mark.parametrize("N,K,M", [(512, 1024, 1), (4096, 4096, 8), (1000, 2048, 32), (1000, 2048, 70), (2048, 1024, 512)])
 def test_both_operands_e4m3_against_the_oracle_and_the_reference(y_type, N, K, M):
     """cuda_gemm_fp8_fp8: weights and activations E4M3 already, output BF16 (3) or E4M3 (4: the BF16 result re-encoded at
     scale 1).  Against float64 sums of the decoded operands, and against the reference's own overloads
@@ -333,7 +366,7 @@ def test_both_operands_e4m3_against_the_oracle_and_the_reference(y_type, N, K, M
 
 
 @pytest.mark.parametrize("act_scale", [0.0, 0.04])
-@pytest.mark.parametrize("M", [1, 12, 32])
+@pytest.mark.parametrize("M", [1, 12, 32, 130])
 def test_w8a8_group_is_one_quantisation_and_one_launch_with_the_bits_of_separate_calls(act_scale, M):
     import torch
 
@@ -349,7 +382,7 @@ def test_w8a8_group_is_one_quantisation_and_one_launch_with_the_bits_of_separate
     dX = to_dev(X)
     before = c.launch_count()
     assert c.gemm_w8a8_bf16_group(c.make_group(items, K), dX, act_scale, M, K) == 0 and c.check_error("group") == 0
-    assert c.launch_count() - before == (3 if act_scale == 0 and M * K > 16384 else 2)
+    assert c.launch_count() - before == (3 if act_scale == 0 and (M * K > 16384 or M > 32) else 2)
     for it, (W, inv, N) in zip(items, host):
         sep = torch.zeros(M * N, dtype=torch.int16, device="cuda")
         assert c.gemm_w8a8_bf16(it["W"], inv, dX, act_scale, sep, N, M, K, alpha=it["alpha"]) == 0 and c.check_error("sep") == 0
