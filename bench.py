@@ -778,10 +778,36 @@ def prefill_probe(torch, capi, dims, wtype, dev, peaks):
     ms = e0.elapsed_time(e1) / reps
     tf = flops / ms / 1e9
     peak = float(peaks.get("bf16_tflops", 1590.0))
-    return {"workload": "one layer's seven linears as four calls (q+k+v, o, gate+up, down), M=2048 tokens", "ms_per_layer": round(ms, 4),
-            "tflops": round(tf, 1), "peak_tflops": peak, "frac": round(tf / peak, 4),
-            "peak_source": "measured" if "bf16_tflops" in peaks else "fallback",
-            "kernel": "gemm_wq_prefill_pair_kernel (tcgen05, cta_group::2)", "launches": launches}
+    out = {"workload": "one layer's seven linears as four calls (q+k+v, o, gate+up, down), M=2048 tokens", "ms_per_layer": round(ms, 4),
+           "tflops": round(tf, 1), "peak_tflops": peak, "frac": round(tf / peak, 4),
+           "peak_source": "measured" if "bf16_tflops" in peaks else "fallback",
+           "kernel": "gemm_wq_prefill_pair_kernel (tcgen05, cta_group::2)", "launches": launches}
+    if wtype != "fp4":
+        # the same four calls in the W8A8 mode: the weight bytes read as E4M3, the activations quantised to E4M3 inside each
+        # call (static scale, then dynamic), E4M3 x E4M3 on the tensor cores; no FP8 peak is measured on this pool, so TFLOP/s only
+        w8 = {}
+        for label, act_scale in (("static", 0.05), ("dynamic", 0.0)):
+            def layer8():
+                for K, X, grp, _ in calls:
+                    if capi.gemm_w8a8_bf16_group(grp, X, act_scale, M, K) != 0:
+                        raise RuntimeError("W8A8 prefill linear failed")
+            before = capi.launch_count()
+            for _ in range(3):
+                layer8()
+            torch.cuda.synchronize(dev)
+            e0.record()
+            for _ in range(reps):
+                layer8()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            if capi.check_error("W8A8 prefill probe") != 0:
+                raise RuntimeError("W8A8 prefill probe failed")
+            ms8 = e0.elapsed_time(e1) / reps
+            w8[label] = {"ms_per_layer": round(ms8, 4), "tflops": round(flops / ms8 / 1e9, 1)}
+            out["launches"] += capi.launch_count() - before
+        w8["kernel"] = "gemm_w8a8_pair_kernel (tcgen05 kind::f8f6f4, cta_group::2), quantiser included"
+        out["w8a8"] = w8
+    return out
 
 
 def ref_gpu_probe(torch, capi, dims, dev):

@@ -56,26 +56,18 @@ __device__ __forceinline__ float e5m2_to_float(uint32_t b)
     return __uint_as_float((s << 31) | ((e + 112u) << 23) | (m << 21));
 }
 
-// float*scale -> E4M3, truncating, saturating to 0x7E (cuda_functions.cu:2382-2415).
+// float*scale -> E4M3, truncating, saturating to 0x7E (cuda_functions.cu:2382-2415), without branches: from 2^-6 up the
+// code is the float's exponent and top three mantissa bits rebased ((bits >> 20) - 120 * 8, the magnitude clamped to 448
+// first, which also maps 448..inf to 0x7E); below, the subnormal code is the magnitude in units of 2^-9, truncated.
 __device__ __forceinline__ uint8_t float_to_e4m3(float f, float scale)
 {
     f *= scale;
     const uint32_t u = __float_as_uint(f);
-    if ((u & 0x7FFFFFFFu) > 0x7F800000u) { return 0x7Fu; }
-    const uint32_t s = u >> 31;
-    const int fe = (int)((u >> 23) & 0xFFu) - 127;
-    const uint32_t fm = u & 0x7FFFFFu;
-    if (fe > 8 || (fe == 8 && fm >= 0xC00000u)) { return (uint8_t)((s << 7) | 0x7Eu); }
-    const int e8 = fe + 7;
-    if (e8 <= 0)
-    {
-        const int shift = 14 - fe;
-        if (shift >= 32) { return (uint8_t)(s << 7); }
-        return (uint8_t)((s << 7) | (((fm | 0x800000u) >> shift) & 0x7u));
-    }
-    uint32_t m8 = fm >> 20;
-    if (e8 == 15 && m8 == 7u) { m8 = 6u; }
-    return (uint8_t)((s << 7) | ((uint32_t)(e8 & 0xF) << 3) | m8);
+    const uint32_t a = u & 0x7FFFFFFFu;
+    const uint32_t normal = (min(a, 0x43E00000u) >> 20) - 960u;
+    const uint32_t subnormal = (uint32_t)__float2int_rz(__uint_as_float(a) * 512.0f);
+    const uint32_t code = (a >= 0x3C800000u ? normal : subnormal) | ((u >> 24) & 0x80u);
+    return (uint8_t)(a > 0x7F800000u ? 0x7Fu : code);
 }
 
 // float*scale -> E5M2, truncating, saturating to 0x7B (cuda_functions.cu:2694-2725).

@@ -88,20 +88,21 @@ def test_w8a8_linear_matches_oracle(act_scale, N, K, M):
     assert_close(O.bf16_bits_to_f32(Y).reshape(M, N), y32, (N, K, M, act_scale))
 
 
-@pytest.mark.parametrize("fh", [1, 2])
+@pytest.mark.parametrize("fh", [1, 2, 3])
 @pytest.mark.parametrize("act_scale", [0.0, 0.0123])
 @pytest.mark.parametrize("N,K,M", [(256, 128, 33), (1000, 512, 100), (4096, 4096, 256), (1024, 2048, 300), (2500, 1024, 257),
-                                   (100, 12288, 48), (6144, 4096, 1024)])
+                                   (100, 12288, 48), (4096, 4096, 64), (384, 256, 65), (6144, 4096, 1024), (24576, 1024, 2100)])
 def test_w8a8_linear_above_32_tokens_matches_oracle(fh, act_scale, N, K, M):
-    """More than 32 tokens: the CTA-pair kernel, both tile shapes (flags bits 8-9: 256 or 512 features per pair), ragged
-    token and feature edges, TMA-stored tiles."""
+    """More than 32 tokens: the CTA-pair kernels (flags bits 8-9: one tile of 256 or of 512 features per pair, or 3 = the
+    persistent form that walks 256-feature tiles with two accumulators), ragged token and feature edges, TMA-stored
+    tiles; 6144 x 4096 at 1024 and 24576 x 1024 at 2100 tokens give the persistent pairs several tiles each."""
     W, _, w_inv, X = O.make_inputs(O.FP8_E4M3, N, K, M, seed=N + M, scaled=True)
     Y = run(W, w_inv, X, act_scale, N, M, K, flags=fh << 8)
     y32, _, _ = O.linear_w8a8(W, w_inv, X, N, M, K, act_scale=act_scale)
     assert_close(O.bf16_bits_to_f32(Y).reshape(M, N), y32, (N, K, M, act_scale, fh))
 
 
-@pytest.mark.parametrize("fh", [1, 2])
+@pytest.mark.parametrize("fh", [1, 2, 3])
 def test_w8a8_above_32_tokens_float32_strides_and_accumulate(fh):
     """The element-by-element epilogue of the CTA-pair kernel: float32 output against float64 sums; transposed output with
     alpha and beta."""
@@ -119,6 +120,19 @@ def test_w8a8_above_32_tokens_float32_strides_and_accumulate(fh):
     want = ya.T + 1.5 * O.bf16_bits_to_f32(Y0)[:, :M]
     assert_close(got[:, :M].T.copy(), want.T.copy(), "alpha beta strides")
     assert np.array_equal(got[:, M:], O.bf16_bits_to_f32(Y0)[:, M:])
+
+
+@pytest.mark.parametrize("M", [4, 70])
+def test_w8a8_static_scale_that_saturates(M):
+    """A static activation scale below the data's range: about 7 % of the activations clamp to +-448 in the quantiser
+    (and some fall into E4M3's subnormals), which the oracle's encoder models exactly."""
+    N, K = 512, 1024
+    W, _, w_inv, X = O.make_inputs(O.FP8_E4M3, N, K, M, seed=M, scaled=True)
+    q, _ = O.quantise_activations_e4m3(X, act_scale=0.004)
+    assert 0.02 < np.mean((q & 0x7F) == 0x7E) < 0.2
+    Y = run(W, w_inv, X, 0.004, N, M, K)
+    y32, _, _ = O.linear_w8a8(W, w_inv, X, N, M, K, act_scale=0.004)
+    assert_close(O.bf16_bits_to_f32(Y).reshape(M, N), y32, ("saturating", M))
 
 
 def test_w8a8_float32_output_is_the_exact_sum():
@@ -163,7 +177,7 @@ def test_w8a8_refuses_what_it_does_not_serve():
 
 
 @pytest.mark.parametrize("act_scale", [0.0, 0.02])
-@pytest.mark.parametrize("M", [1, 8, 32, 64, 300, 2048])
+@pytest.mark.parametrize("M", [1, 8, 32, 48, 64, 300, 2048])
 def test_w8a8_against_the_reference_s_own_dispatcher(act_scale, M):
     """cccc::Cublas::gemm's typed overload with the activation type set to FP8_E4M3 (cublasLt FP8 x FP8, both scale
     pointers) on the same device buffers."""
