@@ -100,7 +100,7 @@ void Cublas::gemm(MatrixTransType TransA, MatrixTransType TransB, int M, int N, 
             fused_calls_++;
             return;
         }
-        LOG_ERR("Cublas::gemm: both operands quantised is served for E4M3 x E4M3, weight transposed, up to 32 tokens only\n");
+        LOG_ERR("Cublas::gemm: both operands quantised is served for E4M3 x E4M3 with the weight transposed and aligned operands only\n");
         return;
     }
     if (aQ || bQ)
@@ -114,9 +114,9 @@ void Cublas::gemm(MatrixTransType TransA, MatrixTransType TransB, int M, int N, 
             LOG_ERR("Cublas::gemm: quantised weights need BF16 activations and output here (got %d, %d)\n", (int)typeX, (int)typeC);
             return;
         }
-        // W8A8 (cublas_real.h:619-666, :692-739): E4M3 weights with the activation type set to FP8_E4M3.  The decode case
-        // (up to 32 tokens) is one call; anything it does not serve continues as W8A16, which is also where the
-        // reference ends up when its cublasLt call fails.
+        // W8A8 (cublas_real.h:619-666, :692-739): E4M3 weights with the activation type set to FP8_E4M3, one call at any
+        // token count; anything it does not serve (unaligned operands, K % 128) continues as W8A16, which is also where
+        // the reference ends up when its cublasLt call fails.
         if (typeW == FP8_E4M3 && act_data_type_ == FP8_E4M3 && TransA == MATRIX_TRANS && TransB == MATRIX_NO_TRANS)
         {
             const int r = aQ ? cuda_gemm_w8a8_bf16(A, inv, B, act_scale, C, (unsigned)M, (unsigned)N, (unsigned)K, (unsigned)lda, (unsigned)ldb,

@@ -127,9 +127,12 @@ C_EXPORT int cuda_gemm_wq_bf16_group(int w_type, unsigned int count, const cuda_
  *   act_scale == 0: dynamic, one absmax over the whole [M_tokens, K] tensor, q = e4m3(x * 448 / absmax), multiplier back
  *                   absmax / 448 (cccc-cuda/cuda_functions.cu:2611-2669);
  * and Y = alpha * w_inv_scale * multiplier * (W . q) + beta * Y (BF16, or float32 with flags bit 2; bit 3 and bit 0 as
- * cuda_gemm_wq_bf16).  Both operands go into tcgen05.mma kind::f8f6f4 unchanged.  Serves the decode case: up to 32
- * tokens, K % 128 == 0, ldw % 16 == 0, ldx % 8 == 0, 16-byte aligned W and X; anything else returns -1 (the caller keeps
- * its own path).  Shares the device's workspace with cuda_gemm_wq_bf16: same ordering rule. */
+ * cuda_gemm_wq_bf16).  Both operands go into tcgen05.mma kind::f8f6f4 unchanged: up to 32 tokens in a kernel that
+ * streams the weights once over all SMs, above that on CTA pairs (cta_group::2; 256- or 512-feature tiles, or a
+ * persistent form whose epilogue overlaps the next tile; flags bits 8-9 = 1 / 2 / 3 force one of them for tests, 0 lets
+ * the shape decide).  Needs K % 128 == 0, ldw % 16 == 0, ldx % 8 == 0, 16-byte aligned W and X, at most 65535 tokens
+ * and M_tokens * K quantised bytes within the 64 MB workspace; anything else returns -1 (the caller keeps its own
+ * path).  Shares the device's workspace with cuda_gemm_wq_bf16: same ordering rule. */
 C_EXPORT int cuda_gemm_w8a8_bf16(const void* W, float w_inv_scale, const void* X, float act_scale, void* Y, unsigned int N_out,
     unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m, unsigned int ldy_n, float alpha,
     float beta, void* stream, unsigned int flags);
@@ -163,7 +166,7 @@ C_EXPORT int cuda_gemm_w8a8_bf16_group(unsigned int count, const cuda_wq_linear*
 /* Both operands E4M3 already (cccc/cublas_real.h:754-834, the overloads Cublas::gemm takes when typeA and typeB are both
  * quantised): Y = alpha * w_inv_scale * x_inv_scale * (W . X) with FP32 accumulation; y_type 3 (BF16; beta * Y added) or
  * 4 (E4M3: the BF16 result re-encoded at scale 1 with the reference's encoder, beta ignored, as there).  X_fp8 is
- * [M_tokens][ldx] bytes.  Limits and ordering as cuda_gemm_w8a8_bf16 (up to 32 tokens, else -1); flags bit 0 only. */
+ * [M_tokens][ldx] bytes.  Limits and ordering as cuda_gemm_w8a8_bf16; flags bit 0 and bits 8-9 only. */
 C_EXPORT int cuda_gemm_fp8_fp8(const void* W, float w_inv_scale, const void* X_fp8, float x_inv_scale, void* Y, int y_type,
     unsigned int N_out, unsigned int M_tokens, unsigned int K, unsigned int ldw, unsigned int ldx, unsigned int ldy_m,
     unsigned int ldy_n, float alpha, float beta, void* stream, unsigned int flags);
