@@ -16,7 +16,7 @@ M = 4, 16, 32 (`decode_by_m`), the Llama-3.1-8B FP4 block-scale chain at M = 1, 
 prefill GEMMs at M = 2048 (`prefill`), the reference's own GPU path and cuBLAS BF16 on the same
 shapes (`ref_gpu`), and the reference's CPU path on a bounded sample (`cpu_baseline`).  At every N,
 `decode_step` is the whole decode step of the 36-layer model (RMSNorm, q/k norm, RoPE, attention over
-a 4096-row BF16 KV cache, SwiGLU, residuals, lm_head, arg-max) at batch 1 and 32 in tokens per second.
+a 4096-row BF16 KV cache, SwiGLU, residuals, lm_head, arg-max) at batch 1, 8 and 32 in tokens per second.
 
 With N>1 (launched under torchrun, one rank per GPU) the same token is computed tensor-parallel:
 q/k/v/gate/up/lm_head split by output feature, o/down split by input feature with the all-reduce fused
@@ -669,8 +669,8 @@ def gpu_arm(args):
             with torch.cuda.stream(stream):
                 model = decode_step_model(torch, capi, dm, dims, wt, lin, world, rank, 32, dev, bufs)
             steps = {}
-            for mb in (1, 32):
-                steps[f"batch{mb}"] = time_decode_step(torch, dist, capi, model, dims, mb, args.wtype, flags, 30 if mb == 1 else 8, dev, stream,
+            for mb in (1, 8, 32):
+                steps[f"batch{mb}"] = time_decode_step(torch, dist, capi, model, dims, mb, args.wtype, flags, {1: 30, 8: 16}.get(mb, 8), dev, stream,
                                                        world)
             if world == 1:
                 for mb in (1, 2):

@@ -177,9 +177,17 @@ template <int G, int HD>
 static int launch_attn(const AttnDecodeParams& p, int sm_count, int max_smem, cudaStream_t stream, bool pdl)
 {
     auto kernel = attn_decode_kernel<G, HD>;
-    // splits per (sequence, kv head): fill the SMs, at least 64 rows per split, a power of two <= 16
+    // Splits per (sequence, kv head): a power of two <= 16 with at least 64 rows per split.  Two CTAs share an SM, and an
+    // SM streams fastest with both (36 against 24 GB/s), so the splits grow while the CTAs still fit two per SM
+    // (measured at 4096 rows: 4 / 8 / 16 sequences 35 -> 25, 59 -> 38, 107 -> 65 us with 256 CTAs instead of 128);
+    // between one and 1.3 CTAs per SM one more doubling of a small cluster still gains (12 / 24 sequences: 95 -> 63,
+    // 120 -> 107 us), but clusters of 16 only pay while 8 would leave half the SMs empty (2 sequences: 24 us with
+    // 8 splits, 32 with 16).
+    const unsigned long long units = (unsigned long long)p.B * p.Hkv;
     unsigned int S = 1;
-    while (S < 16 && (unsigned long long)p.B * p.Hkv * S * 2 <= (unsigned long long)sm_count + 20 && p.T_max / (S * 2) >= 64) { S *= 2; }
+    while (S < 8 && units * S * 2 <= 2ull * (unsigned long long)sm_count && p.T_max / (S * 2) >= 64) { S *= 2; }
+    if (S == 8 && units * S * 2 <= (unsigned long long)sm_count + 20 && p.T_max / (S * 2) >= 64) { S = 16; }
+    if (S <= 2 && units * S * 10 <= 13ull * (unsigned long long)sm_count && p.T_max / (S * 2) >= 64) { S *= 2; }
     auto smem_bytes = [](unsigned int ts_cap) { return attn_smem_floats<G, HD>(ts_cap) * sizeof(float); };
     while (S < 16 && smem_bytes(attn_ts_cap(p.T_max, S)) > (size_t)max_smem) { S *= 2; }
     static std::atomic<int> max_cluster{ 0 };    // largest cluster size this kernel can be scheduled with (0 = not probed)
