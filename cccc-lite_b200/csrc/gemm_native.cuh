@@ -62,6 +62,7 @@ struct NativeParams
     unsigned int tiles;              // feature tiles of all members
     unsigned int nkb;                // 128-k blocks of one tile
     const float* inv_scale;          // [M]: 2^-s of each token
+    float act_inv;                   // the W8A8 pair kernels' activation multiplier when inv_scale is null (known on the host)
     float* partials;                 // [2 * grid][M][128]
     unsigned int* counters;          // [grid], zero between launches
     const uint16_t* X;               // the BF16 activations and their leading dimension (the form that splits them itself)

@@ -241,6 +241,13 @@ static int launch_w8a8(const GemvScratch* ws, const W8A8Member* mem, unsigned in
     const bool dynamic = act_scale == 0.f && !x_is_e4m3;
     // dynamic scale of a small tensor: the quantiser finds the maximum itself (16-byte loads: K and ldx % 8, an aligned base)
     const bool self_absmax = dynamic && (size_t)M * K <= 16384 && (K % 8) == 0 && (ldx % 8) == 0 && sk_al16(X);
+    if (big && x_is_e4m3 && (ldx % 16) == 0 && sk_al16(X))
+    {
+        // E4M3 activations that TMA can read where they lie: no copy, the multiplier back goes with the launch
+        np.inv_scale = nullptr;
+        np.act_inv = act_scale;
+        return launch_w8a8_pair(np, mem, (const uint8_t*)X, ldx, ws->device, ws->sm_count, pair_fh, stream);
+    }
     if (big && !x_is_e4m3 && (K % 8) == 0 && (ldx % 8) == 0 && sk_al16(X))
     {
         // many tokens: eight values per thread, a grid that fills the GPU a few times over
@@ -257,7 +264,7 @@ static int launch_w8a8(const GemvScratch* ws, const W8A8Member* mem, unsigned in
         quantise_activations_x8_kernel<<<(unsigned int)blocks, 256, 0, stream>>>((const uint16_t*)X, ldx, K, M, Q, absmax, dynamic ? 0.f : 1.0f / act_scale,
             dynamic ? 0.f : act_scale, inv);
         if (cudaPeekAtLastError() != cudaSuccess) { return w8a8_launch_failed(); }
-        return launch_w8a8_pair(np, mem, Q, ws->device, ws->sm_count, pair_fh, stream);
+        return launch_w8a8_pair(np, mem, Q, K, ws->device, ws->sm_count, pair_fh, stream);
     }
     if (dynamic && !self_absmax)
     {
@@ -285,7 +292,7 @@ static int launch_w8a8(const GemvScratch* ws, const W8A8Member* mem, unsigned in
     {
         return w8a8_launch_failed();
     }
-    if (big) { return launch_w8a8_pair(np, mem, Q, ws->device, ws->sm_count, pair_fh, stream); }
+    if (big) { return launch_w8a8_pair(np, mem, Q, K, ws->device, ws->sm_count, pair_fh, stream); }
     auto launch_linear = [&](auto kernel, int smem) -> int {
         static std::atomic<bool> attr_set[2][64];
         const int which = bnp == 16 ? 0 : 1;

@@ -220,7 +220,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(WP_THREADS, 1)
         tc_fence_after();
         const unsigned int quarter = warp & 3u;                   // the TMEM lane quarter this warp may read
         const unsigned int cbeg = ((warp - 2u) >> 2) * (PP_TOKENS / 2);    // two warps per quarter split the token columns
-        const float act_inv = __ldg(p.inv_scale);
+        const float act_inv = p.inv_scale != nullptr ? __ldg(p.inv_scale) : p.act_inv;
         if (ok && n_kblocks > 0 && g.y_tma != 0)
         {
             // BF16 tiles [256 tokens][128 features] in the idle stage memory, then one TMA store each; the store clips
@@ -506,7 +506,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(WP_THREADS, 1)
         bool ok = true;
         const unsigned int quarter = warp & 3u;
         const unsigned int cbeg = ((warp - 2u) >> 2) * (PP_TOKENS / 2);
-        const float act_inv = __ldg(p.inv_scale);
+        const float act_inv = p.inv_scale != nullptr ? __ldg(p.inv_scale) : p.act_inv;
         const uint32_t acc_empty_leader = map_to_cta(acc_empty, 0);
         unsigned int i = 0;
         for (unsigned int t = pair; t < total_tiles; t += n_pairs, i++)
@@ -639,9 +639,10 @@ static int launch_w8a8_pair_fh(const CUtensorMap& tmX, const StreamWMaps& tmW, c
 }
 
 // The launch behind the quantiser for more than 32 tokens.  np carries the members (W, Y, N, ldw, ldy, alpha, beta,
-// post_scale), M, K, out_f32, status and inv_scale; Q is the [M][K] E4M3 activations.  fh: 0 picks the form (wp_pick_fh).
+// post_scale), M, K, out_f32, status and inv_scale (or act_inv); Q is the [M][K] E4M3 activations, rows ldq bytes apart.  fh: 0 picks the form (wp_pick_fh).
 // Returns -1 for what this path does not serve.
-static int launch_w8a8_pair(NativeParams np, const W8A8Member* mem, const uint8_t* Q, int device, int sm_count, unsigned int fh, cudaStream_t stream)
+static int launch_w8a8_pair(NativeParams np, const W8A8Member* mem, const uint8_t* Q, unsigned int ldq, int device, int sm_count, unsigned int fh,
+    cudaStream_t stream)
 {
     if (fh < 1 || fh > 3) { fh = wp_pick_fh(np, sm_count); }
     const bool persistent = fh == 3;    // 256-feature tiles walked by one pair per SM pair
@@ -653,7 +654,7 @@ static int launch_w8a8_pair(NativeParams np, const W8A8Member* mem, const uint8_
     PrefillYMaps tmY;
     memset(&tmW, 0, sizeof(tmW));
     memset(&tmY, 0, sizeof(tmY));
-    bool ok = make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Q, np.K, np.M, np.K, WP_BK, PP_HALF, true);
+    bool ok = make_map_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Q, np.K, np.M, ldq, WP_BK, PP_HALF, true);
     for (unsigned int j = 0; j < (unsigned int)PF_MAX_GROUP && ok; j++)
     {
         const W8A8Member& m = mem[j < np.n_seg ? j : 0];

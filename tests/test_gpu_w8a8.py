@@ -403,3 +403,28 @@ def test_w8a8_group_is_one_quantisation_and_one_launch_with_the_bits_of_separate
         assert torch.equal(sep, it["Y"])
         y32, _, _ = O.linear_w8a8(W, inv, X, N, M, K, act_scale=act_scale, alpha=it["alpha"])
         assert_close(O.bf16_bits_to_f32(from_dev_u16(it["Y"])).reshape(M, N), y32, ("oracle", M, N))
+
+
+def test_e4m3_activations_read_in_place_or_copied_give_the_same_bits():
+    """Above 32 tokens cuda_gemm_fp8_fp8 lets TMA read the E4M3 activations where they lie when their rows are 16-byte
+    aligned; rows 8 bytes off are first moved into the workspace.  Same bits either way."""
+    import torch
+
+    c = capi()
+    N, K, M = 640, 1024, 70
+    rng = np.random.default_rng(2)
+    W, _, w_inv, _ = O.make_inputs(O.FP8_E4M3, N, K, M, seed=1, scaled=True)
+    Xq = O.float_to_fp8(rng.standard_normal(M * K).astype(np.float32), O.FP8_E4M3, 32.0).reshape(M, K)
+    Xpad = np.zeros((M, K + 8), np.uint8)
+    Xpad[:, :K] = Xq
+    dW = to_dev(W)
+    outs = []
+    for X, ldx in ((Xq, K), (Xpad, K + 8)):
+        dX = to_dev(X.reshape(-1))
+        Y = torch.zeros(M * N, dtype=torch.int16, device="cuda")
+        before = c.launch_count()
+        assert c.lib().cuda_gemm_fp8_fp8(dW.data_ptr(), w_inv, dX.data_ptr(), 0.03125, Y.data_ptr(), 3, N, M, K, K, ldx, N, 1, 1.0, 0.0, None, 0) == 0
+        assert c.check_error("fp8 x fp8") == 0
+        assert c.launch_count() - before == (1 if ldx == K else 2)
+        outs.append(Y)
+    assert torch.equal(outs[0], outs[1])
